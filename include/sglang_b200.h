@@ -1,0 +1,172 @@
+/*
+ * sglang_b200 — C ABI of the B200 (sm_100a) block-wise FP8 W8A8 kernels.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream
+ * (`cudaStream_t` passed as void*), enqueues work on that stream and returns
+ * without synchronising.  No entry point allocates device memory unless its
+ * comment says so.  Return value: 0 on success, a negative SGLB200_E_* code on
+ * a rejected call (nothing was launched); sglb200_last_error() then holds a
+ * message for the calling thread.
+ *
+ * Each declaration names the reference interface it stands in for (paths are
+ * relative to the SGLang repository root).
+ *
+ * dtype codes for activations: 0 = bfloat16, 1 = float16, 2 = float32.
+ */
+#ifndef SGLANG_B200_H_
+#define SGLANG_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SGLB200_OK 0
+#define SGLB200_E_INVALID (-1)    /* bad shape / alignment / argument            */
+#define SGLB200_E_UNSUPPORTED (-2) /* device is not sm_100, or unsupported dtype */
+#define SGLB200_E_CUDA (-3)       /* a CUDA runtime / driver call failed         */
+#define SGLB200_E_WORKSPACE (-4)  /* workspace missing or too small              */
+
+/* Message describing the last non-zero return on this thread. */
+const char* sglb200_last_error(void);
+
+/* ABI version of this library (bumped on any signature change). */
+int sglb200_abi_version(void);
+
+/* 0 if `device` is a compute-capability 10.x GPU, SGLB200_E_UNSUPPORTED otherwise. */
+int sglb200_check_device(int device);
+
+/*
+ * 1 x group_size activation quantizer: per group amax = max(|x|, eps),
+ * scale = amax / fp8_max (IEEE division), code = e4m3(clamp(x / scale)) (IEEE division,
+ * round-to-nearest-even, saturating).
+ * Replaces: torch.ops.sgl_kernel.sgl_per_token_group_quant_8bit
+ *   (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-217, schema
+ *   sgl-kernel/csrc/common_extension.cc:138-141) and the Triton kernels behind
+ *   per_token_group_quant_fp8 (python/sglang/srt/layers/quantization/fp8_kernel.py:125-216).
+ * input  [num_tokens, hidden] contiguous, hidden % group_size == 0, group_size in {32,64,128,256}.
+ * output_q [num_tokens, hidden] float8_e4m3fn.
+ * output_s element (token t, group g) is written at output_s[t*s_stride_token + g*s_stride_group]
+ *   (row-major: (hidden/group_size, 1); M-major "column_major_scales": (1, padded_tokens)).
+ */
+int sglb200_per_token_group_quant_fp8(const void* input, int in_dtype, void* output_q, float* output_s,
+                                      int64_t num_tokens, int64_t hidden, int group_size, float eps, float fp8_min,
+                                      float fp8_max, int64_t s_stride_token, int64_t s_stride_group, void* stream);
+
+/*
+ * out[r, i] = T( T(silu_f32(x[r, i])) * x[r, d + i] ),  x is [rows, 2d], T in {bf16, fp16}.
+ * Replaces: torch.ops.sgl_kernel.silu_and_mul (sgl-kernel/csrc/elementwise/activation.cu:85-105,
+ *   schema common_extension.cc:78-79).  d % 8 == 0.
+ */
+int sglb200_silu_and_mul(void* out, const void* input, int dtype, int64_t rows, int64_t d, void* stream);
+
+/*
+ * Fused silu_and_mul + 1x128 re-quantisation: h = silu_and_mul(x) kept in registers, then quantised
+ * exactly as sglb200_per_token_group_quant_fp8 would quantise the bf16 tensor h.
+ * Replaces the pair silu_and_mul + sglang_per_token_group_quant_fp8 inside fused_experts_impl
+ *   (python/sglang/srt/layers/moe/fused_moe_triton/fused_moe.py:555-556 and
+ *   fused_moe_triton_kernels.py:632-633); same fusion as
+ *   sgl_per_token_group_quant_8bit_v2(fuse_silu_and_mul=True)
+ *   (sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:336-341) and
+ *   _silu_and_mul_post_quant_kernel (python/sglang/srt/layers/moe/ep_moe/kernels.py:287-361).
+ * input [rows, 2d] (bf16/fp16), output_q [rows, d], output_s [rows, d/group_size] row-major.
+ * If num_rows_dev != NULL it points to a device int32 holding the number of leading rows to process
+ * (e.g. num_tokens_post_pad); rows beyond it are skipped.  `rows` is then the upper bound.
+ */
+int sglb200_silu_and_mul_quant_fp8(const void* input, int dtype, void* output_q, float* output_s, int64_t rows,
+                                   int64_t d, int group_size, float eps, const int32_t* num_rows_dev, void* stream);
+
+/*
+ * Counting sort of flat topk_ids into block-padded expert segments; deterministic: within an expert,
+ * entries keep ascending flat index.  Ids are shifted by +1 so that id -1 lands in bucket 0 and is
+ * reported as expert -1; `num_experts` here is the bucket count, i.e. (model experts + 1), exactly
+ * as the reference op is called.
+ * Replaces: torch.ops.sgl_kernel.moe_align_block_size (sgl-kernel/csrc/moe/moe_align_kernel.cu:302-364,
+ *   schema common_extension.cc:218-222; wrapper
+ *   python/sglang/srt/layers/moe/fused_moe_triton/moe_align_block_size.py:17-82).
+ * topk_ids [numel] int32; sorted_token_ids [numel + num_experts*(block_size-1)] int32;
+ * expert_ids [ceil(that / block_size)] int32; num_tokens_post_pad [1] int32; cumsum_buffer [num_experts+1]
+ * int32 (receives the padded exclusive prefix, as in the reference before its scatter).
+ * workspace: device scratch of at least sglb200_moe_align_workspace_bytes(numel, num_experts) bytes, 16-byte
+ * aligned; may be NULL when that function returns 0.  Contents need no initialisation.
+ * Entries of sorted_token_ids / expert_ids past num_tokens_post_pad are left untouched.
+ */
+int64_t sglb200_moe_align_workspace_bytes(int64_t numel, int num_experts);
+int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block_size,
+                                 int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_pad,
+                                 int32_t* cumsum_buffer, int pad_sorted_token_ids, void* workspace,
+                                 int64_t workspace_bytes, void* stream);
+
+/*
+ * out[t, :] = bf16( scale * sum_k x[t, k, :] ), float32 accumulation in ascending k.
+ * Replaces: torch.ops.sgl_kernel.moe_sum_reduce (sgl-kernel/csrc/moe/moe_sum_reduce.cu:56-116,
+ *   schema common_extension.cc:234-235).  x [tokens, topk, hidden] contiguous, hidden % 8 == 0.
+ */
+int sglb200_moe_sum_reduce(const void* x, void* out, int dtype, int64_t tokens, int64_t topk, int64_t hidden,
+                           float scale, void* stream);
+
+/*
+ * Row gather into expert-sorted order: for r < *num_rows_dev,
+ *   src = sorted_token_ids[r]; if src < numel: dst_q[r,:] = src_q[src / topk, :], dst_s[r,:] = src_s[src / topk, :]
+ *   else (padding) the row and its scales are zero-filled.
+ * Replaces: torch.ops.sgl_kernel.shuffle_rows (sgl-kernel/csrc/moe/prepare_moe_input.cu:170-197) as used by
+ *   cutlass_fused_experts_fp8 (python/sglang/srt/layers/moe/cutlass_moe.py:153-154), and the in-kernel row
+ *   gather of fused_moe_kernel (fused_moe_triton_kernels.py:410-416,450-460).
+ * src_q [tokens, hidden] 1-byte elements, hidden % 16 == 0; src_s [tokens, groups] float32.
+ */
+int sglb200_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, float* dst_s,
+                            const int32_t* sorted_token_ids, const int32_t* num_rows_dev, int64_t max_rows,
+                            int64_t numel, int topk, int64_t hidden, int64_t groups, void* stream);
+
+/*
+ * Dense block-scaled GEMM:  C[m,n] = bf16( sum_kb a_s[m,kb] * b_s[n/128, kb] * sum_{k in kb} A[m,k] * B[n,k] ),
+ * float32 accumulation, 1x128 activation scales, 128x128 weight-block scales.
+ * Replaces: torch.ops.sgl_kernel.fp8_blockwise_scaled_mm
+ *   (sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:368-465, schema common_extension.cc:133-136) and
+ *   w8a8_block_fp8_matmul (python/sglang/srt/layers/quantization/fp8_kernel.py:1072-1168, Triton kernel :695-777).
+ * A [M,K] e4m3 row-major; B [N,K] e4m3 row-major (the checkpoint layout of `weight`);
+ * a_s element (m,kb) at a_s[m*as_stride_m + kb*as_stride_k]; b_s [ceil(N/128), ceil(K/128)] row-major;
+ * C [M,N] row-major, out_dtype 0 = bf16, 1 = fp16.  K % 16 == 0, N % 8 == 0; A, B, C 16-byte aligned.
+ * bias (optional, may be NULL): [N] of out_dtype, added in float32 before the final rounding.
+ * workspace: only used for the split-K path chosen for small M; at least
+ * sglb200_gemm_workspace_bytes(M,N,K) bytes (0 means none needed).
+ */
+int64_t sglb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, const float* a_s, const float* b_s, void* C,
+                                    const void* bias, int64_t M, int64_t N, int64_t K, int64_t as_stride_m,
+                                    int64_t as_stride_k, int out_dtype, void* workspace, int64_t workspace_bytes,
+                                    void* stream);
+
+/*
+ * Grouped (MoE) block-scaled GEMM over expert-sorted rows.  For every 128-row block b < *num_rows_dev / 128,
+ * e = expert_ids[b]:  acc[r, n] = blockscaled( A[r, :], B[e, n, :] ) for the block's rows r.
+ *   e == -1  -> the block contributes zeros.
+ * Output modes:
+ *   scatter == 0: C[r, n] = bf16(acc)                       (C is [max_rows, N], expert-sorted order)
+ *   scatter == 1: id = sorted_token_ids[r]; if id < numel:
+ *                 C[id, n] = bf16( acc * (row_weights ? row_weights[id] : 1) )   (C is [numel, N], token-major)
+ * Replaces: fused_moe_kernel via invoke_fused_moe_kernel
+ *   (python/sglang/srt/layers/moe/fused_moe_triton/fused_moe_triton_kernels.py:307-583, 586-790) and
+ *   torch.ops.sgl_kernel.fp8_blockwise_scaled_grouped_mm (sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:650-810).
+ * A [max_rows, K] e4m3 (rows already in sorted order), a_s [max_rows, K/128] row-major,
+ * B [E, N, K] e4m3, b_s [E, ceil(N/128), ceil(K/128)], block size of the sort must be 128.
+ */
+int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s, const void* B, const float* b_s, void* C,
+                                     const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                                     const int32_t* num_rows_dev, const float* row_weights, int64_t max_rows,
+                                     int64_t numel, int num_experts, int64_t N, int64_t K, int scatter, int out_dtype,
+                                     void* stream);
+
+/*
+ * Health of the GEMM pipelines: 0, or 1 if a bounded mbarrier wait inside a GEMM kernel expired since the
+ * library was loaded (the kernel then unwinds, frees its tensor memory and leaves its output incomplete).
+ * Synchronises the device.  Stands in for the C++ exception a failed CUTLASS launch raises in
+ * sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:164-171.
+ */
+int sglb200_gemm_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGLANG_B200_H_ */

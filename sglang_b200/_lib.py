@@ -1,0 +1,53 @@
+"""ctypes binding of the C ABI declared in include/sglang_b200.h.
+
+There is no fallback: if the CUDA library has not been built, importing this
+module raises, and every op in the package fails with it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libsglang_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m sglang_b200.build` "
+        "(the sm_100a CUDA library is the only implementation; there is no CPU or Triton fallback)"
+    )
+
+lib = C.CDLL(LIB_PATH)
+
+_vp, _i64, _i32, _f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
+
+SIGNATURES = {
+    "sglb200_last_error": (C.c_char_p, []),
+    "sglb200_abi_version": (_i32, []),
+    "sglb200_check_device": (_i32, [_i32]),
+    "sglb200_per_token_group_quant_fp8": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _i32, _f32, _f32, _f32, _i64, _i64, _vp]),
+    "sglb200_silu_and_mul": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp]),
+    "sglb200_silu_and_mul_quant_fp8": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp]),
+    "sglb200_moe_align_workspace_bytes": (_i64, [_i64, _i32]),
+    "sglb200_moe_align_block_size": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp]),
+    "sglb200_moe_sum_reduce": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _f32, _vp]),
+    "sglb200_gather_rows_fp8": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _vp]),
+    "sglb200_gemm_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "sglb200_fp8_blockwise_scaled_mm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
+    "sglb200_fp8_blockwise_grouped_mm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _i32, _vp]),
+    "sglb200_gemm_status": (_i32, []),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here = the .so is older than the header: rebuild
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def check(rc: int) -> None:
+    """Turn a non-zero return code of the C ABI into the exception the reference op would raise."""
+    if rc != 0:
+        msg = lib.sglb200_last_error().decode("utf-8", "replace")
+        if rc == -2:
+            raise NotImplementedError(msg)
+        raise RuntimeError(msg)

@@ -1,0 +1,457 @@
+// Block-scaled FP8 GEMM (dense and expert-grouped) for sm_100a.
+//
+//   C[m,n] = out_t( sum_kb a_s[m,kb] * b_s[n/128,kb] * sum_{k in kb} A[m,k] * B[n,k] )
+//
+// One persistent CTA per SM walks 128x128 output tiles.  Per 128-wide K slab:
+//   * warp 0 (one elected lane) issues two TMA tile loads (A 128x128 B, B 128x128 B, 128-byte
+//     swizzle) into a 6-deep shared-memory ring, signalled through `full` mbarriers;
+//   * warp 1 (one elected lane) issues four tcgen05.mma kind::f8f6f4 (128x128x32) that write the
+//     slab's partial sums into one of four 128-column TMEM buffers, then commits the slab to the
+//     `empty` barrier of the ring slot and to the `tmem_full` barrier of the buffer;
+//   * warps 4-11 (two warpgroups, 64 columns each) pull the partial sums out of TMEM with
+//     tcgen05.ld, release the buffer, and promote them into float32 register accumulators with the
+//     slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be folded into
+//     the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores, overlapped with
+//     the next slabs' MMAs through the four TMEM buffers).
+// The epilogue converts to bf16/fp16 and stores 16 bytes at a time; in grouped "scatter" mode it
+// multiplies by the routing weight and writes to the token-major row named by sorted_token_ids.
+//
+// Every mbarrier wait is bounded; on expiry the CTA raises a status word, unwinds, frees its TMEM
+// and returns (sglb200_gemm_status() reports it).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace sglb200 {
+
+constexpr int BM = 128, BN = 128, BK = 128;
+constexpr int kStages = 6;
+constexpr int kAccBufs = 4;
+constexpr int kTmemCols = kAccBufs * BN;  // 512
+constexpr int kGemmThreads = 384;         // warps 0-3 control, 4-11 epilogue
+constexpr int kEpiWarp0 = 4;
+constexpr int kEpiWarps = 8;
+constexpr uint32_t kTileBytesA = BM * BK;  // fp8
+constexpr uint32_t kTileBytesB = BN * BK;
+constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
+constexpr int kGroupM = 8;  // m-tiles sharing a sweep over n: keeps the weight tiles of a wave L2-resident
+
+__device__ int g_gemm_status = 0;  // 0 ok, 1 = a pipeline wait expired
+
+struct GemmParams {
+  const float* a_s;
+  const float* b_s;
+  void* C;
+  const void* bias;
+  const int32_t* sorted_ids;   // grouped
+  const int32_t* expert_ids;   // grouped
+  const int32_t* num_rows_dev; // grouped: rows in use (multiple of 128)
+  const float* row_weights;    // grouped scatter, optional
+  int64_t M;                   // dense: rows of A; grouped: max rows
+  int64_t N, K;
+  int64_t as_stride_m, as_stride_k;
+  int64_t numel;               // grouped scatter: valid ids are < numel
+  int kb_total;                // ceil(K/128)
+  int nb_total;                // ceil(N/128)
+  int scatter;
+  int out_fp16;
+};
+
+struct SharedCtl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[kAccBufs];
+  uint64_t tmem_empty[kAccBufs];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct TileCoord {
+  int m_tile, n_tile, expert;
+};
+
+// tile index -> (m_tile, n_tile): groups of kGroupM m-tiles, n fastest across groups.
+__device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int& m_tile, int& n_tile) {
+  const int per_group = kGroupM * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * kGroupM;
+  const int gsz = min(tiles_m - first_m, kGroupM);
+  const int r = t - g * per_group;
+  m_tile = first_m + r % gsz;
+  n_tile = r / gsz;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, const void* bias_v, int n0, int64_t N) {
+  // 64 consecutive columns starting at n0, 8 per 16-byte store
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int n = n0 + j * 8;
+    if (n + 8 <= N) {
+      float x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = v[j * 8 + i];
+      if (bias_v != nullptr) {
+        const uint4 braw = __ldg(reinterpret_cast<const uint4*>(static_cast<const OutT*>(bias_v) + n));
+        const OutT* b = reinterpret_cast<const OutT*>(&braw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] += ElemTraits<OutT>::to_f32(b[i]);
+      }
+      uint4 raw;
+      OutT* o = reinterpret_cast<OutT*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = ElemTraits<OutT>::from_f32(x[i]);
+      *reinterpret_cast<uint4*>(dst + j * 8) = raw;
+    } else {
+      for (int i = 0; i < 8 && n + i < N; ++i) {
+        float x = v[j * 8 + i];
+        if (bias_v != nullptr) x += ElemTraits<OutT>::to_f32(static_cast<const OutT*>(bias_v)[n + i]);
+        dst[j * 8 + i] = ElemTraits<OutT>::from_f32(x);
+      }
+    }
+  }
+}
+
+template <bool kGrouped>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    fp8_blockscale_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + kStages * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  int64_t rows = p.M;
+  if (kGrouped) {
+    const int64_t lim = *p.num_rows_dev;
+    rows = lim < rows ? lim : rows;
+  }
+  const int tiles_m = (int)((rows + BM - 1) / BM);
+  const int tiles_n = p.nb_total;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kb_total = p.kb_total;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), kEpiWarps);
+    }
+    ctl->abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::tma_prefetch_desc(&map_a);
+    ptx::tma_prefetch_desc(&map_b);
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (ptx::elect_one()) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int m_tile, n_tile;
+        tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
+        int e = 0;
+        if (kGrouped) {
+          e = p.expert_ids[m_tile];
+          if (e < 0) continue;
+        }
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) { alive = false; break; }
+          const uint32_t bar = ptx::smem_u32(&ctl->full[s]);
+          ptx::mbar_arrive_expect_tx(bar, kStageBytes);
+          const uint32_t dst_a = ptx::smem_u32(tiles + s * kStageBytes);
+          ptx::tma_load_2d(dst_a, &map_a, bar, kb * BK, m_tile * BM);
+          ptx::tma_load_3d(dst_a + kTileBytesA, &map_b, bar, kb * BK, n_tile * BN, e);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (ptx::elect_one()) {
+      constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
+      uint32_t it = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int m_tile, n_tile;
+        tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
+        if (kGrouped && p.expert_ids[m_tile] < 0) continue;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
+          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_empty[buf]), aph ^ 1u, abort_flag)) { alive = false; break; }
+          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->full[s]), ph, abort_flag)) { alive = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ptx::smem_u32(tiles + s * kStageBytes);
+          const uint64_t da = ptx::make_kmajor_sw128_desc(a_addr);
+          const uint64_t db = ptx::make_kmajor_sw128_desc(a_addr + kTileBytesA);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
+            ptx::mma_f8f6f4(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, k > 0 ? 1u : 0u);
+          }
+          ptx::mma_commit(ptx::smem_u32(&ctl->empty[s]));
+          ptx::mma_commit(ptx::smem_u32(&ctl->tmem_full[buf]));
+        }
+      }
+    }
+  } else if (warp >= kEpiWarp0) {
+    // ------------------------------ promotion + epilogue ------------------------------
+    const int q = warp & 3;                    // TMEM lane quadrant this warp may read
+    const int half = (warp - kEpiWarp0) >> 2;  // which 64 of the 128 columns
+    uint32_t it = 0;
+    bool alive = true;
+    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      int m_tile, n_tile;
+      tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
+      const int64_t row = (int64_t)m_tile * BM + q * 32 + lane;
+      const int n0 = n_tile * BN + half * 64;
+      int e = 0;
+      if (kGrouped) e = p.expert_ids[m_tile];
+      float acc[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+      if (e >= 0) {
+        const bool row_ok = row < rows;
+        const float* as_row = p.a_s + row * p.as_stride_m;
+        const float* bs_row = p.b_s + ((int64_t)e * p.nb_total + n_tile) * kb_total;
+        float sa = row_ok ? __ldg(as_row) : 0.f;
+        float sb = __ldg(bs_row);
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const float scale = sa * sb;
+          if (kb + 1 < kb_total) {  // next slab's scales travel while this slab is promoted
+            sa = row_ok ? __ldg(as_row + (int64_t)(kb + 1) * p.as_stride_k) : 0.f;
+            sb = __ldg(bs_row + kb + 1);
+          }
+          const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
+          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) { alive = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * 64;
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld_32x32(taddr, r0);
+          ptx::tmem_ld_32x32(taddr + 32, r1);
+          ptx::tmem_ld_wait();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            acc[j] = fmaf(__uint_as_float(r0[j]), scale, acc[j]);
+            acc[32 + j] = fmaf(__uint_as_float(r1[j]), scale, acc[32 + j]);
+          }
+        }
+        if (!alive) break;
+      }
+      // ---- store ----
+      int64_t out_row = row;
+      bool store_ok = row < rows;
+      if (kGrouped && p.scatter) {
+        const int32_t id = store_ok ? p.sorted_ids[row] : -1;
+        store_ok = id >= 0 && id < p.numel;
+        out_row = id;
+        if (store_ok && p.row_weights != nullptr) {
+          const float w = __ldg(p.row_weights + id);
+#pragma unroll
+          for (int j = 0; j < 64; ++j) acc[j] *= w;
+        }
+      }
+      if (store_ok && n0 < p.N) {
+        if (p.out_fp16) {
+          store_row_chunk<__half>(static_cast<__half*>(p.C) + out_row * p.N + n0, acc, p.bias, n0, p.N);
+        } else {
+          store_row_chunk<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p.C) + out_row * p.N + n0, acc, p.bias, n0, p.N);
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (ctl->abort_flag != 0 && threadIdx.x == 0) {
+    atomicExch(&g_gemm_status, 1);
+    // give TMA copies that may still be in flight time to land before the CTA's shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor maps (encoded through the driver entry point, cached per argument tuple)
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, d2;
+  uint32_t box_rows, rank;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && box_rows == o.box_rows && rank == o.rank;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ k.d0;
+    h = h * 1000003u ^ k.d1;
+    h = h * 1000003u ^ k.d2;
+    return (h * 1000003u ^ k.box_rows) * 31u + k.rank;
+  }
+};
+
+// uint8 tensor [d2][d1][d0] (d0 contiguous) described with `rank` (2 or 3) dimensions,
+// box = 128 x box_rows (x 1), 128-byte swizzle, out-of-range elements read as zero.
+static int get_tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box_rows, uint32_t rank,
+                          CUtensorMap* out) {
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, d0, d1, d2, box_rows, rank};
+  auto itc = cache.find(key);
+  if (itc != cache.end()) {
+    *out = itc->second;
+    return SGLB200_OK;
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return fail(SGLB200_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {d0, d0 * d1};  // bytes (1-byte elements)
+  cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SGLB200_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return SGLB200_OK;
+}
+
+static size_t gemm_smem_bytes() { return (size_t)kStages * kStageBytes + sizeof(SharedCtl) + 1024; }
+
+template <bool kGrouped>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int64_t max_tiles,
+                       cudaStream_t st) {
+  const size_t smem = gemm_smem_bytes();
+  SGLB_CUDA(cudaFuncSetAttribute(fp8_blockscale_gemm_kernel<kGrouped>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+  const int sms = sm_count();
+  const unsigned grid = (unsigned)(max_tiles < sms ? max_tiles : sms);
+  fp8_blockscale_gemm_kernel<kGrouped><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
+  SGLB_CUDA(cudaGetLastError());
+  return SGLB200_OK;
+}
+
+}  // namespace sglb200
+
+using namespace sglb200;
+
+extern "C" int sglb200_gemm_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+extern "C" int64_t sglb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  (void)M, (void)N, (void)K;
+  return 0;
+}
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, const float* a_s, const float* b_s,
+                                               void* C, const void* bias, int64_t M, int64_t N, int64_t K,
+                                               int64_t as_stride_m, int64_t as_stride_k, int out_dtype,
+                                               void* workspace, int64_t workspace_bytes, void* stream) {
+  (void)workspace, (void)workspace_bytes;
+  SGLB_REQUIRE(M >= 0 && N > 0 && K > 0, "fp8_blockwise_scaled_mm: bad shape M=%lld N=%lld K=%lld", (long long)M,
+               (long long)N, (long long)K);
+  SGLB_REQUIRE(K % 16 == 0, "fp8_blockwise_scaled_mm: K=%lld must be a multiple of 16", (long long)K);
+  SGLB_REQUIRE(N % 8 == 0, "fp8_blockwise_scaled_mm: N=%lld must be a multiple of 8", (long long)N);
+  SGLB_REQUIRE(out_dtype == 0 || out_dtype == 1, "fp8_blockwise_scaled_mm: out_dtype %d (0 bf16, 1 fp16)", out_dtype);
+  if (M == 0) return SGLB200_OK;
+  SGLB_REQUIRE(A && B && a_s && b_s && C, "fp8_blockwise_scaled_mm: null pointer");
+  SGLB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C) && (bias == nullptr || aligned16(bias)),
+               "fp8_blockwise_scaled_mm: A, B, C and bias must be 16-byte aligned");
+  SGLB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "fp8_blockwise_scaled_mm: dimension too large");
+  CUtensorMap ma, mb;
+  int rc = get_tensor_map(A, (uint64_t)K, (uint64_t)M, 1, BM, 2, &ma);
+  if (rc) return rc;
+  // B is addressed as [1][N][K] so that dense and grouped kernels share the 3-D load
+  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, BN, 3, &mb);
+  if (rc) return rc;
+  GemmParams p{};
+  p.a_s = a_s, p.b_s = b_s, p.C = C, p.bias = bias;
+  p.M = M, p.N = N, p.K = K;
+  p.as_stride_m = as_stride_m, p.as_stride_k = as_stride_k;
+  p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + BN - 1) / BN);
+  p.out_fp16 = out_dtype;
+  const int64_t tiles = ((M + BM - 1) / BM) * p.nb_total;
+  return launch_gemm<false>(ma, mb, p, tiles, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s, const void* B, const float* b_s,
+                                                void* C, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                                                const int32_t* num_rows_dev, const float* row_weights,
+                                                int64_t max_rows, int64_t numel, int num_experts, int64_t N, int64_t K,
+                                                int scatter, int out_dtype, void* stream) {
+  SGLB_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && num_experts >= 1, "grouped_mm: bad shape rows=%lld N=%lld K=%lld E=%d",
+               (long long)max_rows, (long long)N, (long long)K, num_experts);
+  SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, "grouped_mm: K must be a multiple of 16 and N of 8");
+  SGLB_REQUIRE(out_dtype == 0 || out_dtype == 1, "grouped_mm: out_dtype %d (0 bf16, 1 fp16)", out_dtype);
+  if (max_rows == 0) return SGLB200_OK;
+  SGLB_REQUIRE(A && a_s && B && b_s && C && expert_ids && num_rows_dev, "grouped_mm: null pointer");
+  SGLB_REQUIRE(!scatter || sorted_token_ids, "grouped_mm: scatter mode needs sorted_token_ids");
+  SGLB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C), "grouped_mm: A, B and C must be 16-byte aligned");
+  CUtensorMap ma, mb;
+  int rc = get_tensor_map(A, (uint64_t)K, (uint64_t)max_rows, 1, BM, 2, &ma);
+  if (rc) return rc;
+  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, (uint64_t)num_experts, BN, 3, &mb);
+  if (rc) return rc;
+  GemmParams p{};
+  p.a_s = a_s, p.b_s = b_s, p.C = C, p.bias = nullptr;
+  p.sorted_ids = sorted_token_ids, p.expert_ids = expert_ids, p.num_rows_dev = num_rows_dev;
+  p.row_weights = row_weights;
+  p.M = max_rows, p.N = N, p.K = K;
+  p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + BN - 1) / BN);
+  p.as_stride_m = p.kb_total, p.as_stride_k = 1;
+  p.numel = numel, p.scatter = scatter, p.out_fp16 = out_dtype;
+  const int64_t tiles = ((max_rows + BM - 1) / BM) * p.nb_total;
+  return launch_gemm<true>(ma, mb, p, tiles, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,284 @@
+// moe_align_block_size for sm_100a: a deterministic (stable) counting sort of the flat
+// top-k expert ids into expert segments padded to a multiple of block_size.
+//
+// Bucket b = id + 1 (id -1, "expert not on this rank", is bucket 0 and is reported as
+// expert -1).  Within a bucket entries keep ascending flat index, so the output is a pure
+// function of the input (the reference kernel's atomicAdd scatter yields an arbitrary
+// permutation inside each expert segment; this order is one of its valid outputs and is the
+// order of the reference's CPU implementation and test oracle).
+//
+// The ids are cut into chunks of kChunk consecutive entries, one CTA per chunk; inside a CTA
+// each of the 32 warps owns 256 consecutive entries and walks them 32 at a time.  Rank of an
+// entry = (padded start of its bucket) + (entries of that bucket in earlier chunks) + (in
+// earlier warps of the chunk) + (in earlier steps of the warp) + (in lower lanes of the step,
+// from match.any).  numel <= kChunk runs as ONE kernel; larger inputs run histogram ->
+// scan -> scatter over a small global workspace.  No global atomics anywhere.
+#include "common.cuh"
+
+namespace sglb200 {
+
+constexpr int kAlignThreads = 1024;
+constexpr int kAlignWarps = kAlignThreads / 32;
+constexpr int kStepsPerWarp = 8;
+constexpr int kWarpSpan = 32 * kStepsPerWarp;      // 256 ids per warp
+constexpr int kChunk = kAlignWarps * kWarpSpan;    // 8192 ids per CTA
+
+__device__ __forceinline__ int warp_incl_scan(int v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, v, off);
+    if (lane >= off) v += n;
+  }
+  return v;
+}
+
+// Per-warp bucket counts of the chunk [chunk_begin, chunk_end) into wc[warp][B] (smem, zeroed by caller).
+__device__ __forceinline__ void count_chunk(const int32_t* __restrict__ ids, int64_t chunk_begin, int64_t chunk_end,
+                                            int B, int* wc) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t seg = chunk_begin + (int64_t)warp * kWarpSpan;
+#pragma unroll
+  for (int s = 0; s < kStepsPerWarp; ++s) {
+    const int64_t i = seg + s * 32 + lane;
+    if (i < chunk_end) {
+      const int b = ids[i] + 1;
+      if (b >= 0 && b < B) atomicAdd(&wc[warp * B + b], 1);  // shared-memory atomic, contended only inside the warp
+    }
+  }
+}
+
+// Turns wc[warp][b] into exclusive prefixes over warps; returns this CTA's total per bucket in tot[b].
+__device__ __forceinline__ void scan_over_warps(int B, int* wc, int* tot) {
+  for (int b = threadIdx.x; b < B; b += kAlignThreads) {
+    int run = 0;
+#pragma unroll 8
+    for (int w = 0; w < kAlignWarps; ++w) {
+      const int c = wc[w * B + b];
+      wc[w * B + b] = run;
+      run += c;
+    }
+    tot[b] = run;
+  }
+}
+
+// prefix[0..B] = exclusive scan of ceil(tot[b]/block)*block.  `scratch` holds 33 ints.
+__device__ __forceinline__ void padded_prefix(int B, int block_size, const int* tot, int* prefix, int* scratch) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int carry = 0;
+  for (int base = 0; base < B; base += kAlignThreads) {
+    const int b = base + threadIdx.x;
+    const int v = b < B ? (tot[b] + block_size - 1) / block_size * block_size : 0;
+    const int incl = warp_incl_scan(v);
+    if (lane == 31) scratch[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const int w = scratch[lane];
+      const int wi = warp_incl_scan(w);
+      scratch[lane] = wi - w;
+      if (lane == 31) scratch[32] = wi;
+    }
+    __syncthreads();
+    if (b < B) prefix[b] = carry + scratch[warp] + incl - v;
+    carry += scratch[32];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) prefix[B] = carry;
+  __syncthreads();
+}
+
+// Writes sorted_token_ids for the chunk.  base[b] = padded start of bucket b + entries in earlier chunks.
+__device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ ids, int64_t chunk_begin, int64_t chunk_end,
+                                              int B, int* wc, const int* base, int32_t* __restrict__ sorted) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t seg = chunk_begin + (int64_t)warp * kWarpSpan;
+  if (seg >= chunk_end) return;  // whole warp past the end
+#pragma unroll 1
+  for (int s = 0; s < kStepsPerWarp; ++s) {
+    const int64_t i = seg + s * 32 + lane;
+    int b = -1;
+    if (i < chunk_end) {
+      b = ids[i] + 1;
+      if (b < 0 || b >= B) b = -1;
+    }
+    const int key = b >= 0 ? b : B + lane;  // invalid lanes match nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int start = 0;
+    if (b >= 0) start = wc[warp * B + b];
+    __syncwarp();
+    if (b >= 0) {
+      sorted[(int64_t)base[b] + start + rank] = (int32_t)i;
+      if (lane == 31 - __clz(peers)) wc[warp * B + b] = start + __popc(peers);
+    }
+    __syncwarp();
+  }
+}
+
+// expert_ids for blocks [first, first+stride, ...) and the padding tails of buckets b = first_b, first_b+stride_b, ...
+__device__ __forceinline__ void fill_meta(int B, int block_size, int64_t numel, const int* prefix, const int* tot_all,
+                                          int32_t* __restrict__ expert_ids, int32_t* __restrict__ sorted,
+                                          bool pad_sorted, int part, int parts) {
+  const int num_blocks = prefix[B] / block_size;
+  for (int i = part * kAlignThreads + threadIdx.x; i < num_blocks; i += parts * kAlignThreads) {
+    const int pos = i * block_size;
+    int lo = 0, hi = B;  // first bucket whose end is > pos
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (prefix[mid + 1] <= pos) lo = mid + 1; else hi = mid;
+    }
+    expert_ids[i] = lo - 1;
+  }
+  if (pad_sorted) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int b = part * kAlignWarps + warp; b < B; b += parts * kAlignWarps) {
+      const int begin = prefix[b] + tot_all[b], end = prefix[b + 1];
+      for (int p = begin + lane; p < end; p += 32) sorted[p] = (int32_t)numel;
+    }
+  }
+}
+
+// ---- numel <= kChunk: everything in one CTA -------------------------------------------------
+__global__ void __launch_bounds__(kAlignThreads)
+    moe_align_single_kernel(const int32_t* __restrict__ ids, int64_t numel, int B, int block_size,
+                            int32_t* __restrict__ sorted, int32_t* __restrict__ expert_ids,
+                            int32_t* __restrict__ post_pad, int32_t* __restrict__ cumsum, bool pad_sorted) {
+  extern __shared__ int smem[];
+  int* wc = smem;                       // [32][B]
+  int* tot = wc + kAlignWarps * B;      // [B]
+  int* prefix = tot + B;                // [B+1]
+  int* scratch = prefix + B + 1;        // [33]
+  for (int i = threadIdx.x; i < kAlignWarps * B; i += kAlignThreads) wc[i] = 0;
+  __syncthreads();
+  count_chunk(ids, 0, numel, B, wc);
+  __syncthreads();
+  scan_over_warps(B, wc, tot);
+  __syncthreads();
+  padded_prefix(B, block_size, tot, prefix, scratch);
+  for (int b = threadIdx.x; b <= B; b += kAlignThreads) cumsum[b] = prefix[b];
+  if (threadIdx.x == 0) *post_pad = prefix[B];
+  fill_meta(B, block_size, numel, prefix, tot, expert_ids, sorted, pad_sorted, 0, 1);
+  scatter_chunk(ids, 0, numel, B, wc, prefix, sorted);
+}
+
+// ---- numel > kChunk: histogram per chunk -> scan over chunks -> scatter ----------------------
+__global__ void __launch_bounds__(kAlignThreads)
+    moe_align_hist_kernel(const int32_t* __restrict__ ids, int64_t numel, int B, int* __restrict__ chunk_hist) {
+  extern __shared__ int smem[];
+  int* wc = smem;
+  int* tot = wc + kAlignWarps * B;
+  for (int i = threadIdx.x; i < kAlignWarps * B; i += kAlignThreads) wc[i] = 0;
+  __syncthreads();
+  const int64_t begin = (int64_t)blockIdx.x * kChunk;
+  const int64_t end = begin + kChunk < numel ? begin + kChunk : numel;
+  count_chunk(ids, begin, end, B, wc);
+  __syncthreads();
+  scan_over_warps(B, wc, tot);
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += kAlignThreads) chunk_hist[(int64_t)blockIdx.x * B + b] = tot[b];
+}
+
+// One warp per bucket: chunk_hist[:, b] becomes its exclusive scan over chunks; totals[b] = sum.
+__global__ void __launch_bounds__(kAlignThreads)
+    moe_align_scan_kernel(int* __restrict__ chunk_hist, int* __restrict__ totals, int num_chunks, int B) {
+  const int b = blockIdx.x * kAlignWarps + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  int run = 0;
+  for (int c0 = 0; c0 < num_chunks; c0 += 32) {
+    const int c = c0 + lane;
+    const int v = c < num_chunks ? chunk_hist[(int64_t)c * B + b] : 0;
+    const int incl = warp_incl_scan(v);
+    if (c < num_chunks) chunk_hist[(int64_t)c * B + b] = run + incl - v;
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) totals[b] = run;
+}
+
+__global__ void __launch_bounds__(kAlignThreads)
+    moe_align_scatter_kernel(const int32_t* __restrict__ ids, int64_t numel, int B, int block_size,
+                             const int* __restrict__ chunk_hist, const int* __restrict__ totals,
+                             int32_t* __restrict__ sorted, int32_t* __restrict__ expert_ids,
+                             int32_t* __restrict__ post_pad, int32_t* __restrict__ cumsum, bool pad_sorted) {
+  extern __shared__ int smem[];
+  int* wc = smem;                       // [32][B]
+  int* tot = wc + kAlignWarps * B;      // [B]   this chunk's totals (unused after scan) / all-chunk totals
+  int* prefix = tot + B;                // [B+1]
+  int* base = prefix + B + 1;           // [B]
+  int* scratch = base + B;              // [33]
+  for (int i = threadIdx.x; i < kAlignWarps * B; i += kAlignThreads) wc[i] = 0;
+  for (int b = threadIdx.x; b < B; b += kAlignThreads) tot[b] = totals[b];
+  __syncthreads();
+  padded_prefix(B, block_size, tot, prefix, scratch);
+  for (int b = threadIdx.x; b < B; b += kAlignThreads) base[b] = prefix[b] + chunk_hist[(int64_t)blockIdx.x * B + b];
+  if (blockIdx.x == 0) {
+    for (int b = threadIdx.x; b <= B; b += kAlignThreads) cumsum[b] = prefix[b];
+    if (threadIdx.x == 0) *post_pad = prefix[B];
+  }
+  fill_meta(B, block_size, numel, prefix, tot, expert_ids, sorted, pad_sorted, blockIdx.x, gridDim.x);
+  __syncthreads();  // fill_meta is done with tot[] before it is reused below
+  const int64_t begin = (int64_t)blockIdx.x * kChunk;
+  const int64_t end = begin + kChunk < numel ? begin + kChunk : numel;
+  count_chunk(ids, begin, end, B, wc);
+  __syncthreads();
+  scan_over_warps(B, wc, tot);
+  __syncthreads();
+  scatter_chunk(ids, begin, end, B, wc, base, sorted);
+}
+
+static size_t align_smem_bytes(int B) { return sizeof(int) * ((size_t)kAlignWarps * B + 3 * (size_t)B + 1 + 33 + 8); }
+
+}  // namespace sglb200
+
+using namespace sglb200;
+
+extern "C" int64_t sglb200_moe_align_workspace_bytes(int64_t numel, int num_experts) {
+  if (numel <= kChunk) return 0;
+  const int64_t chunks = (numel + kChunk - 1) / kChunk;
+  return (chunks + 1) * (int64_t)num_experts * (int64_t)sizeof(int);
+}
+
+extern "C" int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block_size,
+                                            int32_t* sorted_token_ids, int32_t* expert_ids,
+                                            int32_t* num_tokens_post_pad, int32_t* cumsum_buffer,
+                                            int pad_sorted_token_ids, void* workspace, int64_t workspace_bytes,
+                                            void* stream) {
+  SGLB_REQUIRE(numel >= 0 && numel < (1ll << 31) - (int64_t)num_experts * block_size, "moe_align: numel %lld too large",
+               (long long)numel);
+  SGLB_REQUIRE(num_experts >= 1 && block_size >= 1, "moe_align: num_experts %d, block_size %d", num_experts, block_size);
+  SGLB_REQUIRE(sorted_token_ids && expert_ids && num_tokens_post_pad && cumsum_buffer && (topk_ids || numel == 0),
+               "moe_align: null pointer");
+  const int B = num_experts;
+  const size_t smem = align_smem_bytes(B);
+  SGLB_REQUIRE(smem <= 200 * 1024, "moe_align: %d buckets need %zu bytes of shared memory (limit 200 KiB)", B, smem);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (smem > 48 * 1024) {
+    // opt in to more than 48 KiB of dynamic shared memory (a per-function, per-device attribute; cheap to repeat)
+    SGLB_CUDA(cudaFuncSetAttribute(moe_align_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SGLB_CUDA(cudaFuncSetAttribute(moe_align_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SGLB_CUDA(cudaFuncSetAttribute(moe_align_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  }
+  if (numel <= kChunk) {
+    moe_align_single_kernel<<<1, kAlignThreads, smem, st>>>(topk_ids, numel, B, block_size, sorted_token_ids, expert_ids,
+                                                            num_tokens_post_pad, cumsum_buffer,
+                                                            pad_sorted_token_ids != 0);
+    SGLB_CUDA(cudaGetLastError());
+    return SGLB200_OK;
+  }
+  const int64_t chunks = (numel + kChunk - 1) / kChunk;
+  const int64_t need = sglb200_moe_align_workspace_bytes(numel, num_experts);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(SGLB200_E_WORKSPACE, "moe_align: workspace of %lld bytes required, got %lld", (long long)need,
+                (long long)workspace_bytes);
+  int* chunk_hist = static_cast<int*>(workspace);
+  int* totals = chunk_hist + chunks * B;
+  moe_align_hist_kernel<<<(unsigned)chunks, kAlignThreads, smem, st>>>(topk_ids, numel, B, chunk_hist);
+  moe_align_scan_kernel<<<(unsigned)((B + kAlignWarps - 1) / kAlignWarps), kAlignThreads, 0, st>>>(chunk_hist, totals,
+                                                                                                   (int)chunks, B);
+  moe_align_scatter_kernel<<<(unsigned)chunks, kAlignThreads, smem, st>>>(topk_ids, numel, B, block_size, chunk_hist,
+                                                                          totals, sorted_token_ids, expert_ids,
+                                                                          num_tokens_post_pad, cumsum_buffer,
+                                                                          pad_sorted_token_ids != 0);
+  SGLB_CUDA(cudaGetLastError());
+  return SGLB200_OK;
+}

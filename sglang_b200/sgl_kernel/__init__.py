@@ -1,0 +1,148 @@
+"""Drop-in for the `sgl_kernel` Python package, restricted to the block-FP8 path.
+
+Importing this module registers the ops under `torch.ops.sgl_kernel.*` with the
+reference's schemas (sgl-kernel/csrc/common_extension.cc:78-79,133-141,218-222,
+234-235,263-264) so that callers written against the reference
+(`torch.ops.sgl_kernel.moe_align_block_size.default(...)`) run unchanged, and
+exposes the reference's Python-level function names.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops as _ops
+
+_SCHEMAS = {
+    "fp8_blockwise_scaled_mm": "(Tensor mat_a, Tensor mat_b, Tensor scales_a, Tensor scales_b, ScalarType out_dtype) -> Tensor",
+    "sgl_per_token_group_quant_8bit": "(Tensor input, Tensor(a!) output_q, Tensor(b!) output_s, int group_size, float eps, float fp8_min, float fp8_max, bool scale_ue8m0) -> ()",
+    "sgl_per_token_group_quant_8bit_v2": "(Tensor input, Tensor(a!) output_q, Tensor(b!) output_s, int group_size, float eps, float fp8_min, float fp8_max, bool scale_ue8m0, bool fuse_silu_and_mul, Tensor? masked_m) -> ()",
+    "moe_align_block_size": "(Tensor topk_ids, int num_experts, int block_size, Tensor(a!) sorted_token_ids, Tensor(b!) experts_ids, Tensor(c!) num_tokens_post_pad, Tensor(d!) cumsum_buffer, bool pad_sorted_token_ids) -> ()",
+    "silu_and_mul": "(Tensor(a!) out, Tensor input) -> ()",
+    "moe_sum_reduce": "(Tensor input, Tensor(a!) output, float routed_scaling_factor) -> ()",
+    "shuffle_rows": "(Tensor input, Tensor dst2src_map, Tensor(a!) output) -> ()",
+}
+
+
+def _op_fp8_blockwise_scaled_mm(mat_a, mat_b, scales_a, scales_b, out_dtype):
+    # Reference layout (fp8_blockwise_gemm_kernel.cu:374-406): mat_a [M,K] row-major, mat_b [K,N] column-major
+    # (= weight.T), scales_a [M,K/128] M-major, scales_b [K/128,N/128] (= weight_scale.T).
+    if mat_b.stride(0) != 1:
+        raise RuntimeError("mat_b must be a column-major tensor")
+    if mat_a.stride(1) != 1:
+        raise RuntimeError("mat_a must be a row-major tensor")
+    weight = mat_b.t()  # [N,K] contiguous view
+    return _ops.w8a8_block_fp8_matmul(mat_a, weight, scales_a, scales_b.t(), [128, 128], out_dtype)
+
+
+def _op_quant(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0):
+    if scale_ue8m0:
+        raise NotImplementedError("UE8M0 scales are not part of this path (float32 128-block scales only)")
+    _ops.per_token_group_quant_fp8_out(input, output_q, output_s, group_size, eps, fp8_min, fp8_max)
+
+
+def _op_quant_v2(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0, fuse_silu_and_mul, masked_m):
+    if scale_ue8m0 or masked_m is not None:
+        raise NotImplementedError("UE8M0 scales / masked layout are not part of this path")
+    if not fuse_silu_and_mul:
+        return _op_quant(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, False)
+    if not output_s.is_contiguous():
+        raise NotImplementedError("fused silu_and_mul quantisation writes row-major scales")
+    q, s = _ops.silu_and_mul_quant_fp8(input, group_size, eps)
+    output_q.copy_(q)
+    output_s.copy_(s)
+
+
+def _op_moe_align(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, cumsum_buffer, pad_sorted_token_ids):
+    _ops.moe_align_block_size_out(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids,
+                                  num_tokens_post_pad, cumsum_buffer, pad_sorted_token_ids)
+
+
+def _op_silu_and_mul(out, input):
+    _ops.silu_and_mul_out(out, input)
+
+
+def _op_moe_sum_reduce(input, output, routed_scaling_factor):
+    _ops.moe_sum_reduce_out(input, output, routed_scaling_factor)
+
+
+def _op_shuffle_rows(input, dst2src_map, output):
+    # prepare_moe_input.cu:170-197: output[i, :] = input[dst2src_map[i], :]; plain row gather.
+    src = input.view(torch.uint8) if input.dtype.itemsize == 1 else input
+    dst = output.view(torch.uint8) if output.dtype.itemsize == 1 else output
+    torch.index_select(src, 0, dst2src_map.long(), out=dst)
+
+
+_IMPLS = {
+    "fp8_blockwise_scaled_mm": _op_fp8_blockwise_scaled_mm,
+    "sgl_per_token_group_quant_8bit": _op_quant,
+    "sgl_per_token_group_quant_8bit_v2": _op_quant_v2,
+    "moe_align_block_size": _op_moe_align,
+    "silu_and_mul": _op_silu_and_mul,
+    "moe_sum_reduce": _op_moe_sum_reduce,
+    "shuffle_rows": _op_shuffle_rows,
+}
+
+_LIBRARY = None
+
+
+def _register():
+    global _LIBRARY
+    if _LIBRARY is not None:
+        return
+    lib = torch.library.Library("sgl_kernel", "FRAGMENT")
+    for name, schema in _SCHEMAS.items():
+        lib.define(name + schema)
+        lib.impl(name, _IMPLS[name], "CUDA")
+    _LIBRARY = lib
+
+
+_register()
+
+# ---- Python-level names (sgl_kernel/gemm.py:25,100-140; moe.py:6,83; elementwise.py:172) ----
+
+
+def fp8_blockwise_scaled_mm(mat_a, mat_b, scales_a, scales_b, out_dtype):
+    return torch.ops.sgl_kernel.fp8_blockwise_scaled_mm.default(mat_a, mat_b, scales_a, scales_b, out_dtype)
+
+
+def sgl_per_token_group_quant_8bit(input, output_q, output_s, group_size, eps, fp8_min, fp8_max,
+                                   scale_ue8m0: bool = False, fuse_silu_and_mul: bool = False,
+                                   masked_m: Optional[torch.Tensor] = None, enable_v2: Optional[bool] = None) -> None:
+    if enable_v2 or fuse_silu_and_mul or masked_m is not None:
+        return torch.ops.sgl_kernel.sgl_per_token_group_quant_8bit_v2.default(
+            input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0, fuse_silu_and_mul, masked_m)
+    torch.ops.sgl_kernel.sgl_per_token_group_quant_8bit.default(
+        input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0)
+
+
+sgl_per_token_group_quant_fp8 = sgl_per_token_group_quant_8bit
+
+
+def moe_align_block_size(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad,
+                         cumsum_buffer, pad_sorted_token_ids=False):
+    torch.ops.sgl_kernel.moe_align_block_size.default(
+        topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, cumsum_buffer,
+        pad_sorted_token_ids)
+
+
+def moe_sum_reduce(input_tensor, output_tensor, routed_scaling_factor=0):
+    torch.ops.sgl_kernel.moe_sum_reduce.default(input_tensor, output_tensor, routed_scaling_factor)
+
+
+def silu_and_mul(input: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    if input.shape[-1] * input.dtype.itemsize % 16 != 0:
+        raise ValueError("The pointers must be multiple of 16 bytes.")
+    if out is None:
+        out = torch.empty(input.shape[:-1] + (input.shape[-1] // 2,), device=input.device, dtype=input.dtype)
+    else:
+        assert input.shape[:-1] == out.shape[:-1] and input.shape[-1] == 2 * out.shape[-1]
+    torch.ops.sgl_kernel.silu_and_mul.default(out, input)
+    return out
+
+
+def shuffle_rows(input_tensor, dst2src_map, output_tensor_shape):
+    output = torch.empty(output_tensor_shape, device=input_tensor.device, dtype=input_tensor.dtype)
+    torch.ops.sgl_kernel.shuffle_rows.default(input_tensor, dst2src_map, output)
+    return output

@@ -1,0 +1,69 @@
+"""`FusedMoE`: the caller of `Fp8MoEMethod.apply`, with the two expert-parallel forms.
+
+After python/sglang/srt/layers/moe/fused_moe_triton/layer.py:119-918.  Experts are block-distributed:
+rank r of an EP group of size p owns experts [r*E/p, (r+1)*E/p) (:182-185).
+
+* a2a_backend "none"  (reference default): every rank holds all tokens, ids of remote experts become
+  -1 in the dispatcher, partial outputs are summed with an all-reduce (:908-909).
+* a2a_backend "nccl": tokens stay where they were produced; quantised rows travel to the ranks owning
+  their experts in one all-to-all, the results return in a second one and are summed at the source.
+  This replaces the DeepEP dispatch/combine of the reference
+  (python/sglang/srt/layers/moe/token_dispatcher/deepep.py:449-509) with NCCL over NVLink.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ....distributed import get_moe_ep_group
+from ..moe_runner.base import MoeRunnerConfig
+from ..token_dispatcher import StandardDispatcher, StandardTopKOutput
+from .ep_a2a import ep_all_to_all_forward
+
+
+class FusedMoE(nn.Module):
+    def __init__(self, num_experts: int, hidden_size: int, intermediate_size: int, top_k: int,
+                 params_dtype: torch.dtype = torch.bfloat16, quant_config=None, prefix: str = "",
+                 routed_scaling_factor: Optional[float] = None, a2a_backend: str = "none", inplace: bool = False,
+                 device=None):
+        super().__init__()
+        ep = get_moe_ep_group()
+        self.moe_ep_size = ep.world_size
+        self.moe_ep_rank = max(ep.rank_in_group, 0)
+        assert num_experts % self.moe_ep_size == 0
+        self.num_experts = num_experts
+        self.num_local_experts = num_experts // self.moe_ep_size
+        self.hidden_size = hidden_size
+        self.intermediate_size_per_partition = intermediate_size
+        self.top_k = top_k
+        self.a2a_backend = a2a_backend
+        self.quant_config = quant_config
+        self.quant_method = quant_config.get_quant_method(self, prefix=prefix)
+        self.quant_method.create_weights(self, self.num_local_experts, hidden_size, intermediate_size, params_dtype,
+                                         device=device)
+        self.moe_runner_config = MoeRunnerConfig(
+            num_experts=num_experts, num_local_experts=self.num_local_experts, hidden_size=hidden_size,
+            intermediate_size_per_partition=intermediate_size, top_k=top_k, activation="silu", is_gated=True,
+            inplace=inplace, routed_scaling_factor=routed_scaling_factor)
+        self.quant_method.create_moe_runner(self, self.moe_runner_config)
+        self.dispatcher = StandardDispatcher(num_experts, self.moe_ep_size, self.moe_ep_rank)
+
+    def load_full_weights(self, w13, w13_s, w2, w2_s) -> None:
+        lo = self.moe_ep_rank * self.num_local_experts
+        hi = lo + self.num_local_experts
+        self.w13_weight.data.copy_(w13[lo:hi])
+        self.w13_weight_scale_inv.data.copy_(w13_s[lo:hi])
+        self.w2_weight.data.copy_(w2[lo:hi])
+        self.w2_weight_scale_inv.data.copy_(w2_s[lo:hi])
+
+    def forward(self, hidden_states: torch.Tensor, topk_output: StandardTopKOutput) -> torch.Tensor:
+        if self.a2a_backend == "nccl" and self.moe_ep_size > 1:
+            return ep_all_to_all_forward(self, hidden_states, topk_output)
+        dispatch_output = self.dispatcher.dispatch(hidden_states, topk_output)
+        combine_input = self.quant_method.apply(self, dispatch_output)
+        out = self.dispatcher.combine(combine_input)
+        if self.moe_ep_size > 1:
+            out = get_moe_ep_group().all_reduce(out)
+        return out

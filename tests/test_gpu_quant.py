@@ -1,0 +1,140 @@
+"""GPU parity of the quantizer and the elementwise MoE kernels, through the C ABI (bit-exact)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import block_fp8_oracle as O
+from oracle import c_oracle as CO
+from tests.util import bf16_bits, codes_to_fp8, fp8_codes, make_act, to_f32_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from sglang_b200 import ops as _ops
+    return _ops
+
+
+@pytest.mark.parametrize("tokens", [1, 7, 83, 2048])
+@pytest.mark.parametrize("hidden", [128, 512, 4096, 7168])
+def test_quant_bf16_bit_exact(ops, tokens, hidden):
+    x = make_act(tokens, hidden, tokens * 10000 + hidden)
+    q, s = ops.per_token_group_quant_fp8(x.cuda(), 128)
+    rq, rs = CO.quant(bf16_bits(x), 0, 128)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), rs.view(np.uint32))
+    assert np.array_equal(fp8_codes(q), rq)
+
+
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+@pytest.mark.parametrize("dtype,code", [(torch.bfloat16, 0), (torch.float16, 1), (torch.float32, 2)])
+def test_quant_groups_and_dtypes(ops, group, dtype, code):
+    x = make_act(37, 1024, 1234 + group, dtype=dtype)
+    x[3, :group] = 0  # all-zero group -> eps path
+    x[5, 7] = 6.0e4 if dtype != torch.bfloat16 else 3.0e38
+    q, s = ops.per_token_group_quant_fp8(x.cuda(), group)
+    raw = x.numpy() if code == 2 else x.view(torch.int16).numpy().view(np.uint16)
+    rq, rs = CO.quant(raw, code, group)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), rs.view(np.uint32))
+    assert np.array_equal(fp8_codes(q), rq)
+
+
+def test_quant_column_major_scales(ops):
+    x = make_act(83, 2048, 5)
+    q, s = ops.per_token_group_quant_fp8(x.cuda(), 128, column_major_scales=True, scale_tma_aligned=True)
+    assert s.shape == (83, 16) and s.stride() == (1, 84)
+    rq, rs = CO.quant(bf16_bits(x), 0, 128)
+    assert np.array_equal(s.cpu().numpy(), rs) and np.array_equal(fp8_codes(q), rq)
+
+
+def test_quant_golden_fixtures(ops, golden_dir):
+    g = np.load(os.path.join(golden_dir, "quant_native.npz"))
+    for i in range(4):
+        dt = torch.bfloat16 if int(g[f"dtype{i}"]) == 0 else torch.float16
+        x = torch.from_numpy(g[f"x{i}"].view(np.int16)).view(dt).cuda()
+        q, s = ops.per_token_group_quant_fp8(x, 128)
+        assert np.array_equal(fp8_codes(q), g[f"q{i}"])
+        xs = np.abs(to_f32_np(x).reshape(-1, 128)).max(-1).reshape(s.shape)
+        nz = xs != 0
+        assert np.array_equal(s.cpu().numpy()[nz], g[f"s{i}"][nz])
+    k = np.load(os.path.join(golden_dir, "kat_fp8_kernel.npz"))
+    q, s = ops.per_token_group_quant_fp8(torch.from_numpy(k["A"]).cuda(), 128)
+    np.testing.assert_allclose(s.cpu().numpy(), k["A_s"], rtol=1.3e-6, atol=1e-5)
+    assert (np.abs(O.e4m3_decode(fp8_codes(q)) - O.e4m3_decode(k["A_q"])) > 1e-5).mean() < 1e-4
+
+
+def test_quant_large_round_trip_property(ops):
+    # full BASELINE size (8192 x 18432): scale * 448 recovers amax exactly enough, dequantised error bounded
+    x = torch.randn(8192, 18432, device="cuda", dtype=torch.bfloat16)
+    q, s = ops.per_token_group_quant_fp8(x, 128)
+    amax = x.view(8192, -1, 128).abs().amax(-1).float()
+    assert torch.equal(s, amax.clamp(min=1e-10) / 448.0)
+    deq = q.view(8192, -1, 128).float() * s.unsqueeze(-1)
+    err = (deq - x.view(8192, -1, 128).float()).abs()
+    assert bool((err <= amax.unsqueeze(-1) * (2.0 ** -4) + 1e-12).all())
+
+
+def test_quant_rejects_bad_shapes(ops):
+    x = torch.zeros(4, 100, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.per_token_group_quant_fp8(x, 128)
+    q, s = ops.per_token_group_quant_fp8(torch.zeros(0, 256, device="cuda", dtype=torch.bfloat16), 128)
+    assert q.shape == (0, 256) and s.shape == (0, 2)
+
+
+@pytest.mark.parametrize("rows,d", [(1, 128), (19, 768), (300, 2048)])
+def test_silu_and_mul(ops, rows, d):
+    x = (make_act(rows, 2 * d, rows + d, outliers=False) * 3).cuda()
+    out = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
+    ops.silu_and_mul_out(out, x)
+    ref = O.bf16_bits_to_f32(CO.silu_and_mul(bf16_bits(x)))
+    got = to_f32_np(out)
+    # expf differs between libm and the device by an ulp or two: after bf16 rounding almost all agree
+    assert (np.abs(got - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-30).all()
+    assert (got != ref).mean() < 5e-3
+
+
+@pytest.mark.parametrize("rows,d", [(1, 128), (19, 768), (300, 2048)])
+def test_silu_mul_quant_equals_unfused_pipeline(ops, rows, d):
+    x = (make_act(rows, 2 * d, 77 + rows, outliers=False) * 3).cuda()
+    h = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
+    ops.silu_and_mul_out(h, x)
+    q_ref, s_ref = ops.per_token_group_quant_fp8(h, 128)
+    q, s = ops.silu_and_mul_quant_fp8(x, 128)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(s, s_ref)
+    # and the quantiser half is bit-exact against the oracle given the same h
+    rq, rs = CO.quant(bf16_bits(h), 0, 128)
+    assert np.array_equal(fp8_codes(q), rq) and np.array_equal(s.cpu().numpy(), rs)
+    # row limit read from device memory
+    lim = torch.tensor([rows // 2], device="cuda", dtype=torch.int32)
+    q2, s2 = ops.silu_and_mul_quant_fp8(x, 128, num_rows=lim)
+    assert torch.equal(q2.view(torch.uint8)[: rows // 2], q.view(torch.uint8)[: rows // 2])
+
+
+@pytest.mark.parametrize("tokens,topk,hidden", [(1, 8, 7168), (33, 8, 2048), (512, 6, 1024), (5, 1, 128)])
+def test_moe_sum_reduce_bit_exact(ops, tokens, topk, hidden):
+    x = make_act(tokens * topk, hidden, 99 + tokens, outliers=False).view(tokens, topk, hidden).cuda()
+    out = torch.empty(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    ops.moe_sum_reduce_out(x, out, 2.5)
+    ref = CO.moe_sum_reduce(bf16_bits(x), 2.5)
+    assert np.array_equal(bf16_bits(out), ref)
+
+
+def test_gather_rows(ops):
+    T, topk, H, E = 50, 4, 512, 16
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(-1, E, (T, topk), generator=g, dtype=torch.int32).cuda()
+    q = torch.randint(0, 255, (T, H), generator=g, dtype=torch.uint8).cuda().view(torch.float8_e4m3fn)
+    s = torch.rand(T, H // 128, generator=g).cuda()
+    sorted_ids, expert_ids, post = ops.moe_align_block_size(ids, 128, E)
+    dq, ds = ops.gather_rows_fp8(q, s, sorted_ids, post, T * topk, topk)
+    P = int(post.item())
+    sid = sorted_ids[:P].cpu().numpy()
+    exp_q = np.zeros((P, H), np.uint8)
+    exp_s = np.zeros((P, H // 128), np.float32)
+    ok = sid < T * topk
+    exp_q[ok] = fp8_codes(q)[sid[ok] // topk]
+    exp_s[ok] = s.cpu().numpy()[sid[ok] // topk]
+    assert np.array_equal(fp8_codes(dq)[:P], exp_q) and np.array_equal(ds.cpu().numpy()[:P], exp_s)

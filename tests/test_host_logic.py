@@ -1,0 +1,147 @@
+"""Host-side logic that needs no GPU: sharding rules, quant-method checks, and the expert-parallel
+exchange run as two gloo ranks on CPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def test_fp8_config_and_divisibility_checks():
+    from sglang_b200.srt.layers.quantization.fp8 import Fp8Config, Fp8LinearMethod, Fp8MoEMethod
+    cfg = Fp8Config.from_config({"quant_method": "fp8", "activation_scheme": "dynamic", "weight_block_size": [128, 128]})
+    assert cfg.weight_block_size == [128, 128] and cfg.get_name() == "fp8"
+    with pytest.raises(ValueError):
+        Fp8Config(activation_scheme="static")
+    with pytest.raises(ValueError):
+        Fp8Config(weight_block_size=[64, 64])
+    layer = torch.nn.Module()
+    m = Fp8LinearMethod(cfg)
+    m.create_weights(layer, 7168, [2112], 7168, 2112, torch.bfloat16)
+    assert layer.weight.shape == (2112, 7168) and layer.weight.dtype == torch.float8_e4m3fn
+    assert layer.weight_scale_inv.shape == (17, 56)
+    with pytest.raises(ValueError):  # merged layers must split on 128-row boundaries (fp8.py:249-259)
+        m.create_weights(torch.nn.Module(), 512, [192, 192], 512, 384, torch.bfloat16)
+    moe = torch.nn.Module()
+    mm = Fp8MoEMethod(cfg)
+    mm.create_weights(moe, 4, 512, 256, torch.bfloat16)
+    assert moe.w13_weight.shape == (4, 512, 512) and moe.w13_weight_scale_inv.shape == (4, 4, 4)
+    assert moe.w2_weight.shape == (4, 512, 256) and moe.w2_weight_scale_inv.shape == (4, 4, 2)
+    with pytest.raises(ValueError):
+        mm.create_weights(torch.nn.Module(), 4, 512, 192, torch.bfloat16)
+
+
+def test_max_padded_rows_bound():
+    from sglang_b200.srt.layers.moe.fused_moe_triton.fused_moe import _max_padded_rows
+    from oracle import block_fp8_oracle as O
+    rng = np.random.default_rng(0)
+    for T, topk, E in [(1, 8, 256), (5, 2, 4), (64, 8, 256), (4096, 8, 32)]:
+        ids = rng.integers(-1, E, size=(T, topk)).astype(np.int32)
+        _, _, n = O.moe_align_block_size(ids, 128, E)
+        assert int(n[0]) <= _max_padded_rows(T * topk, E, 128)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _ep_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from sglang_b200.srt.distributed import get_moe_ep_group, initialize_model_parallel
+        from sglang_b200.srt.layers.moe.fused_moe_triton import ep_a2a
+        initialize_model_parallel(1, world, backend="gloo")
+        group = get_moe_ep_group()
+        E, E_local, T, H, topk = 8, 8 // world, 6 + rank, 256, 3
+        g = torch.Generator().manual_seed(100 + rank)
+        xq = torch.randint(0, 120, (T, H), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        xs = torch.rand(T, H // 128, generator=g)
+        ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]).to(torch.int32)
+        w = torch.rand(T, topk, generator=g)
+        plan = ep_a2a.plan_dispatch(ids, E_local, group)
+        q, s, local, rw = ep_a2a.dispatch(xq, xs, ids, w, plan, group, E_local)
+        # stand-in for the local experts: row value = sum of weights of the experts this rank owns
+        owned = (local >= 0).float()
+        out_rows = ((rw * owned).sum(1, keepdim=True) * torch.ones(1, H)).to(torch.bfloat16)
+        out = ep_a2a.combine(out_rows, plan, group, T, 1.0)
+        ret[rank] = dict(
+            out=out.float().numpy(), w=w.numpy(), ids=ids.numpy(), recv_rows=q.shape[0], local=local.numpy(),
+            q_first=q.view(torch.uint8)[:1].numpy() if q.shape[0] else None,
+            send_splits=plan.send_splits, recv_splits=plan.recv_splits)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ep_dispatch_combine_two_gloo_ranks():
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_ep_worker, args=(world, port, ret), nprocs=world, join=True)
+    for r in range(world):
+        d = ret[r]
+        # every token's weights are all counted exactly once across the ranks that own its experts
+        expect = d["w"].sum(1)
+        got = d["out"][:, 0]
+        np.testing.assert_allclose(got, expect, rtol=2e-2)
+        # a row is sent once per destination rank even when several of its experts live there
+        dest = d["ids"] // (8 // world)
+        pairs = sum(len(set(row)) for row in dest.tolist())
+        assert sum(d["send_splits"]) == pairs
+        assert d["recv_rows"] == sum(d["recv_splits"])
+        assert ((d["local"] >= -1) & (d["local"] < 8 // world)).all()
+    assert ret[0]["send_splits"][1] == ret[1]["recv_splits"][0]
+
+
+def _tp_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from sglang_b200.srt.distributed import initialize_model_parallel, tensor_model_parallel_all_reduce
+        from sglang_b200.srt.layers.linear import MergedColumnParallelLinear, RowParallelLinear
+        from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+        initialize_model_parallel(world, 1, backend="gloo")
+        cfg = Fp8Config()
+        col = MergedColumnParallelLinear(512, [256, 256], quant_config=cfg)
+        row = RowParallelLinear(512, 384, quant_config=cfg)
+        g = torch.Generator().manual_seed(0)
+        w = torch.randint(0, 255, (512, 512), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        s = torch.rand(4, 4, generator=g)
+        col.load_full_weight(w, s)
+        w2 = torch.randint(0, 255, (384, 512), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        s2 = torch.rand(3, 4, generator=g)
+        row.load_full_weight(w2, s2)
+        x = torch.full((2, 3), float(rank + 1))
+        tensor_model_parallel_all_reduce(x)
+        ret[rank] = dict(
+            col_w=col.weight.view(torch.uint8).numpy(), col_s=col.weight_scale_inv.numpy(),
+            row_w=row.weight.view(torch.uint8).numpy(), row_s=row.weight_scale_inv.numpy(),
+            full_w=w.view(torch.uint8).numpy(), full_s=s.numpy(), full_w2=w2.view(torch.uint8).numpy(),
+            full_s2=s2.numpy(), ar=x.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_sharding_two_gloo_ranks():
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_tp_worker, args=(world, port, ret), nprocs=world, join=True)
+    for r in range(world):
+        d = ret[r]
+        # merged column layer: rank r holds rows [128r,128r+128) of part 0 and of part 1
+        exp_w = np.concatenate([d["full_w"][128 * r : 128 * r + 128], d["full_w"][256 + 128 * r : 256 + 128 * r + 128]])
+        exp_s = np.concatenate([d["full_s"][r : r + 1], d["full_s"][2 + r : 3 + r]])
+        assert np.array_equal(d["col_w"], exp_w) and np.array_equal(d["col_s"], exp_s)
+        assert np.array_equal(d["row_w"], d["full_w2"][:, 256 * r : 256 * r + 256])
+        assert np.array_equal(d["row_s"], d["full_s2"][:, 2 * r : 2 * r + 2])
+        assert np.all(d["ar"] == 3.0)
