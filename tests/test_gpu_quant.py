@@ -70,7 +70,8 @@ def test_quant_large_round_trip_property(ops):
     x = torch.randn(8192, 18432, device="cuda", dtype=torch.bfloat16)
     q, s = ops.per_token_group_quant_fp8(x, 128)
     amax = x.view(8192, -1, 128).abs().amax(-1).float()
-    assert torch.equal(s, amax.clamp(min=1e-10) / 448.0)
+    # tensor / tensor is a true IEEE division on the device (tensor / python-scalar becomes a reciprocal multiply)
+    assert torch.equal(s, amax.clamp(min=1e-10) / torch.full_like(amax, 448.0))
     deq = q.view(8192, -1, 128).float() * s.unsqueeze(-1)
     err = (deq - x.view(8192, -1, 128).float()).abs()
     assert bool((err <= amax.unsqueeze(-1) * (2.0 ** -4) + 1e-12).all())
