@@ -1,0 +1,386 @@
+"""Benchmark of the block-FP8 W8A8 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--sections main,moe,tp]
+
+Workload (BASELINE config 1): the six DeepSeek-V3 dense layers at M = 4096 tokens.  One step = for each
+layer: quantise a bf16 activation [M,K] into 1x128 FP8 groups, then the 128x128 block-scaled GEMM
+against that layer's [N,K] FP8 weight (bf16 out).  Metric: TFLOP/s = sum(2*M*N*K) / time, whole job.
+With N > 1 ranks every rank runs its own batch (weak scaling, no data-path collective); the tensor-
+and expert-parallel layers of configs 2 and 3, which do have collectives, are reported beside it under
+"tp_layer" and "moe_layer".
+
+Inputs are synthetic (seeded N(0,1) activations, N(0,0.02) weights quantised per 128x128 block) with the
+shapes of the DeepSeek-V3 / Llama-3-70B checkpoints, which are not needed.  The per-step working set
+(583 MB of weights + activations + outputs) is larger than the 126 MB L2, so no flush is used.
+
+--impl reference times the reference's own CPU kernels (sgl-kernel fp8_scaled_mm_cpu, compiled into
+oracle/_ref) on the host cores for the same layers on a bounded row sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# (name, N, K) of BASELINE config 1
+DSV3_LAYERS = [
+    ("fused_qkv_a", 2112, 7168), ("q_b", 24576, 1536), ("kv_b", 32768, 512),
+    ("o_proj", 7168, 16384), ("gate_up", 36864, 7168), ("down", 7168, 18432),
+]
+M_TOKENS = 4096
+METRIC = "block-FP8 GEMM TFLOPS (quantize + 128x128 block-scaled GEMM, DeepSeek-V3 dense layers, M=4096)"
+FP8_NOMINAL_TFLOPS = 4500.0
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU side: the reference's own kernels (oracle/_ref) or, failing that, the oracle port
+# ------------------------------------------------------------------------------------------------
+
+
+def _cpu_flags_ok() -> bool:
+    try:
+        flags = open("/proc/cpuinfo").read()
+    except OSError:
+        return False
+    return all(f in flags for f in ("avx512f", "avx512_bf16", "amx_bf16"))
+
+
+def _load_ref_cpu():
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "libsgl_cpu_ref.so")
+    if os.path.exists(so) and _cpu_flags_ok():
+        torch.ops.load_library(so)
+        return "reference"
+    return "port"
+
+
+def cpu_reference_pass(rows: int, steps: int, warmup: int):
+    """Times `steps` passes of the six layers on `rows` tokens on the host cores.  Returns
+    (kind, cores, seconds per pass, flops per pass)."""
+    import numpy as np
+    import torch
+    kind = _load_ref_cpu()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    layers = []
+    for name, N, K in DSV3_LAYERS:
+        x = torch.randn(rows, K, generator=g).bfloat16()
+        wq = torch.randint(0, 0x78, (N, K), generator=g, dtype=torch.uint8)
+        wq = (wq | (torch.randint(0, 2, (N, K), generator=g, dtype=torch.uint8) << 7)).view(torch.float8_e4m3fn)
+        ws = torch.rand((N + 127) // 128, K // 128, generator=g) * 1e-3 + 1e-4
+        if kind == "reference":
+            wq = torch.ops.sgl_cpu_ref.convert_weight_packed(wq)
+        layers.append((x, wq, ws))
+    flops = sum(2.0 * rows * N * K for _, N, K in DSV3_LAYERS)
+
+    def one_pass():
+        for x, wq, ws in layers:
+            if kind == "reference":
+                torch.ops.sgl_cpu_ref.fp8_scaled_mm_cpu(x, wq, ws, [128, 128], None, torch.bfloat16, True)
+            else:
+                from oracle import block_fp8_oracle as O
+                O.block_fp8_linear(x.float().numpy(), wq.view(torch.uint8).numpy(), ws.numpy())
+
+    for _ in range(warmup):
+        one_pass()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_pass()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return kind, cores, dt, flops
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 1024
+    kind, cores, dt, flops = cpu_reference_pass(rows, args.steps, args.warmup)
+    v = flops / dt / 1e12
+    sample = f"{rows} of {M_TOKENS} token rows through all six layers per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations x fp8 weights (W8A16), f32 accumulate",
+        "data": "synthetic", "config": _config(),
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "sgl-kernel fp8_scaled_mm_cpu (AMX brgemm) on the host cores; the CPU path does not quantise activations",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def _config():
+    return {
+        "workload": "BASELINE config 1: DeepSeek-V3 dense block-FP8 layers "
+                    "(N,K) in {(2112,7168),(24576,1536),(32768,512),(7168,16384),(36864,7168),(7168,18432)} at M=4096",
+        "M": M_TOKENS, "block": [128, 128], "group": 128,
+        "l2": "per-step working set (583 MB weights + activations + outputs) exceeds the 126 MB L2; no flush",
+    }
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU side
+# ------------------------------------------------------------------------------------------------
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.idx = device_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.strip().splitlines():
+            f = [c.strip() for c in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def _smi_device_id(local_index: int) -> str:
+    """nvidia-smi id of CUDA device `local_index` (honours CUDA_VISIBLE_DEVICES, indices or UUIDs)."""
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [v.strip() for v in vis.split(",") if v.strip()]
+        if local_index < len(ids):
+            return ids[local_index]
+    return str(local_index)
+
+
+def make_block_fp8_weight(N, K, device, gen, std=0.02, experts=None):
+    """N(0,std) weights quantised per 128x128 block on the device (scale = block amax / 448)."""
+    import torch
+    lead = () if experts is None else (experts,)
+    nb, kb = (N + 127) // 128, (K + 127) // 128
+    w = torch.zeros(*lead, nb * 128, kb * 128, device=device)
+    w[..., :N, :K] = torch.randn(*lead, N, K, device=device, generator=gen) * std
+    blk = w.view(*lead, nb, 128, kb, 128)
+    s = blk.abs().amax(dim=(-3, -1), keepdim=True) / torch.full((), 448.0, device=device)
+    s = torch.where(s == 0, torch.ones_like(s), s)
+    q = (blk / s).clamp(-448, 448).to(torch.float8_e4m3fn).view(*lead, nb * 128, kb * 128)[..., :N, :K].contiguous()
+    return q, s.view(*lead, nb, kb).contiguous()
+
+
+def run_main(args, dist_ctx):
+    import torch
+    from sglang_b200 import ops
+    from sglang_b200.srt.layers.linear import ColumnParallelLinear
+    from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+
+    rank, world, dev = dist_ctx
+    peaks = _peaks()
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    cfg = Fp8Config(weight_block_size=[128, 128])
+    M = args.m_tokens
+    layers = []
+    for name, N, K in DSV3_LAYERS:
+        lin = ColumnParallelLinear(K, N, quant_config=cfg, device=dev)  # tp group of 1 here: full weights
+        wq, ws = make_block_fp8_weight(N, K, dev, gen)
+        lin.weight.data.copy_(wq)
+        lin.weight_scale_inv.data.copy_(ws)
+        del wq, ws
+        x_host = torch.randn(M, K, generator=torch.Generator().manual_seed(rank * 100 + len(layers))).bfloat16().pin_memory()
+        x_dev = x_host.to(dev)
+        y_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+        layers.append(dict(name=name, N=N, K=K, lin=lin, x_host=x_host, x_dev=x_dev, y_host=y_host))
+    torch.cuda.empty_cache()
+    flops_step = sum(2.0 * M * l["N"] * l["K"] for l in layers)
+    stream = torch.cuda.current_stream()
+
+    gemm_ev = []
+
+    def step_resident(record=False):
+        for l in layers:
+            xq, xs = ops.per_token_group_quant_fp8(l["x_dev"], 128)
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            y = ops.w8a8_block_fp8_matmul(xq, l["lin"].weight, xs, l["lin"].weight_scale_inv, [128, 128], torch.bfloat16)
+            if record:
+                e1.record(stream)
+                gemm_ev.append((e0, e1, 2.0 * M * l["N"] * l["K"], l["name"]))
+        return y
+
+    def step_e2e():
+        for l in layers:
+            x = l["x_host"].to(dev, non_blocking=True)
+            y, _ = l["lin"](x)  # Fp8LinearMethod.apply: quantise + block GEMM
+            l["y_host"].copy_(y, non_blocking=True)
+
+    def timed(fn, steps, warmup, **kw):
+        for _ in range(warmup):
+            fn()
+        _barrier(world)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn(**kw)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        _barrier(world)
+        return _max_over_ranks(e0.elapsed_time(e1) / 1e3, world, dev)
+
+    sampler = ClockSampler(_smi_device_id(dev.index))
+    sampler.start()
+    t_res = timed(step_resident, args.steps, args.warmup, record=True)
+    clocks = sampler.stop()
+    t_e2e = timed(step_e2e, args.steps, max(args.warmup, 3))
+    assert ops.gemm_status() == 0, "a GEMM pipeline wait expired during the benchmark"
+
+    # dominant kernel: the block-scaled GEMM.  Per-launch durations from the events recorded in the timed region.
+    gemm_ms = sum(a.elapsed_time(b) for a, b, _, _ in gemm_ev)
+    gemm_flops = sum(f for _, _, f, _ in gemm_ev)
+    achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+    per_layer = {}
+    for a, b, f, n in gemm_ev:
+        d = per_layer.setdefault(n, [0.0, 0.0])
+        d[0] += a.elapsed_time(b)
+        d[1] += f
+    peak = 2.0 * peaks["bf16_sustained"]
+    value = world * flops_step * args.steps / t_res / 1e12
+    e2e = world * flops_step * args.steps / t_e2e / 1e12
+    h2d = sum(l["x_host"].numel() * 2 for l in layers)
+    d2h = sum(l["y_host"].numel() * 2 for l in layers)
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t_res / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3, f32 accumulate, bf16 out", "data": "synthetic",
+        "config": _config(), "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": t_e2e / args.steps * 1e3,
+                "api": "ColumnParallelLinear.forward -> Fp8LinearMethod.apply on pinned host tensors"},
+        "gpu_launches": args.steps * 2 * len(layers),
+        "roofline": {
+            "kernel": "fp8_blockscale_gemm_kernel<false>", "bound": "tensor", "achieved": achieved, "peak": peak,
+            "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": None,
+            "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}): fp8 issues at twice the bf16 rate",
+            "frac_of_nominal_fp8_4500": achieved / FP8_NOMINAL_TFLOPS,
+            "per_layer_tflops": {n: v[1] / (v[0] / 1e3) / 1e12 for n, v in per_layer.items()},
+        },
+    }
+    return line, layers
+
+
+def _barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def _max_over_ranks(seconds, world, dev):
+    if world == 1:
+        return seconds
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([seconds], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--sections", default="main,moe,tp,sweep")
+    ap.add_argument("--cpu-baseline", type=int, default=1)
+    ap.add_argument("--m-tokens", type=int, default=M_TOKENS, help="smaller values are for profiler captures only")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from sglang_b200._lib import check, lib
+    check(lib.sglb200_check_device(local))
+    sections = set(args.sections.split(","))
+
+    cpu = None
+    if rank == 0 and world == 1 and args.cpu_baseline:
+        rows = 1024
+        kind, cores, dt, flops = cpu_reference_pass(rows, 3, 1)
+        cpu = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+               "sample": f"{rows} of {M_TOKENS} token rows through all six layers, 3 timed passes after 1 warm-up"}
+
+    line, layers = run_main(args, (rank, world, dev))
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    del layers
+    torch.cuda.empty_cache()
+    extra = {}
+    try:
+        import bench_sections as bs  # optional extra sections live beside this file
+        extra = bs.run(sections, args, (rank, world, dev), _peaks())
+    except ImportError:
+        pass
+    line.update(extra)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
