@@ -223,6 +223,8 @@ def run_main(args, dist_ctx):
     M = args.m_tokens
     layers = []
     for name, N, K in DSV3_LAYERS:
+        if args.layers and name not in args.layers.split(","):
+            continue
         lin = ColumnParallelLinear(K, N, quant_config=cfg, device=dev)  # tp group of 1 here: full weights
         wq, ws = make_block_fp8_weight(N, K, dev, gen)
         lin.weight.data.copy_(wq)
@@ -335,6 +337,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sections", default="main,moe,tp,sweep")
     ap.add_argument("--cpu-baseline", type=int, default=1)
+    ap.add_argument("--layers", default="", help="comma-separated subset of layer names (profiler captures only)")
     ap.add_argument("--m-tokens", type=int, default=M_TOKENS, help="smaller values are for profiler captures only")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -99,6 +99,24 @@ int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num
                                  int64_t workspace_bytes, void* stream);
 
 /*
+ * moe_align_block_size for callers that cannot allocate device memory when they need the sort: code running
+ * while a CUDA graph is being captured with the allocator frozen, a server whose memory pool is fully committed
+ * to the KV cache, or a host program without torch's allocator.  No counterpart in the reference (its op always
+ * receives a caller-allocated cumsum_buffer).  Same outputs as sglb200_moe_align_block_size; the scratch
+ * (padded prefix + per-chunk histograms, about 0.5 MiB) is a fixed array inside the library image, resident on
+ * every GPU that loads the library until the process exits.
+ * Limits: num_experts (bucket count = experts + 1) <= 1024 and numel <= 1048576; larger calls are rejected with
+ * SGLB200_E_INVALID and launch nothing.
+ * The first call on each device resolves the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call before starting any stream capture.  All calls share the one array, which keeps
+ * the previous call's contents (the kernels overwrite every word before reading it, so nothing needs clearing);
+ * two calls that overlap on the GPU (different streams) race on it.  Calls cudaMalloc / cudaFree never.
+ */
+int sglb200_moe_align_block_size_noalloc(const int32_t* topk_ids, int64_t numel, int num_experts, int block_size,
+                                         int32_t* sorted_token_ids, int32_t* expert_ids,
+                                         int32_t* num_tokens_post_pad, int pad_sorted_token_ids, void* stream);
+
+/*
  * out[t, :] = bf16( scale * sum_k x[t, k, :] ), float32 accumulation in ascending k.
  * Replaces: torch.ops.sgl_kernel.moe_sum_reduce (sgl-kernel/csrc/moe/moe_sum_reduce.cu:56-116,
  *   schema common_extension.cc:234-235).  x [tokens, topk, hidden] contiguous, hidden % 8 == 0.

@@ -13,6 +13,8 @@
 // earlier warps of the chunk) + (in earlier steps of the warp) + (in lower lanes of the step,
 // from match.any).  numel <= kChunk runs as ONE kernel; larger inputs run histogram ->
 // scan -> scatter over a small global workspace.  No global atomics anywhere.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sglb200 {
@@ -281,4 +283,71 @@ extern "C" int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t num
                                                                           pad_sorted_token_ids != 0);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some callers of this library cannot obtain device memory at the moment they need the sort: code
+// running while a stream is being captured into a CUDA graph with the allocator frozen, a serving
+// process whose memory pool has been handed over entirely to the KV cache, or a host program that is
+// not built on torch and has no allocator of its own to ask.  For them the scratch the sort needs (the
+// padded prefix and the per-chunk histograms) lives in a fixed array inside the library image instead
+// of in caller-provided buffers.  Every GPU that loads the library holds this array until exit.
+// ---------------------------------------------------------------------------------------------
+namespace sglb200 {
+
+constexpr int kNoAllocMaxBuckets = 1024;                               // experts + 1
+constexpr int64_t kNoAllocMaxNumel = 1 << 20;                          // flat top-k ids
+constexpr int64_t kNoAllocMaxChunks = kNoAllocMaxNumel / kChunk;       // 128
+constexpr int64_t kNoAllocScratchInts =
+    (kNoAllocMaxBuckets + 1) + (kNoAllocMaxChunks + 1) * kNoAllocMaxBuckets;  // prefix + histograms + totals
+
+static __device__ __align__(256) int g_noalloc_scratch[kNoAllocScratchInts];
+
+// Device address of g_noalloc_scratch for the CURRENT device, resolved once per device.  In host code
+// the array's name is only a handle for the runtime, never a pointer a kernel may dereference.
+static int noalloc_scratch_ptr(int** out) {
+  static std::mutex mu;
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  SGLB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SGLB200_E_INVALID, "moe_align (no-alloc): device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    SGLB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  *out = ptrs[dev];
+  return SGLB200_OK;
+}
+
+}  // namespace sglb200
+
+extern "C" int sglb200_moe_align_block_size_noalloc(const int32_t* topk_ids, int64_t numel, int num_experts,
+                                                    int block_size, int32_t* sorted_token_ids, int32_t* expert_ids,
+                                                    int32_t* num_tokens_post_pad, int pad_sorted_token_ids,
+                                                    void* stream) {
+  if (num_experts > kNoAllocMaxBuckets)
+    return fail(SGLB200_E_INVALID,
+                "moe_align (no-alloc): %d buckets exceed the built-in scratch (at most %d, i.e. %d experts + 1); use "
+                "sglb200_moe_align_block_size with caller-provided buffers",
+                num_experts, kNoAllocMaxBuckets, kNoAllocMaxBuckets - 1);
+  if (numel > kNoAllocMaxNumel)
+    return fail(SGLB200_E_INVALID,
+                "moe_align (no-alloc): %lld ids exceed the built-in scratch (at most %lld); use "
+                "sglb200_moe_align_block_size with caller-provided buffers",
+                (long long)numel, (long long)kNoAllocMaxNumel);
+  int* scratch = nullptr;
+  const int rc = noalloc_scratch_ptr(&scratch);
+  if (rc != SGLB200_OK) return rc;
+  // layout: [0, B+1) padded prefix; then the chunk histograms and totals.  The kernels overwrite every
+  // word they later read, so nothing has to be cleared between calls.
+  int32_t* cumsum = scratch;
+  void* workspace = scratch + (kNoAllocMaxBuckets + 1);
+  const int64_t workspace_bytes = (kNoAllocMaxChunks + 1) * (int64_t)kNoAllocMaxBuckets * (int64_t)sizeof(int);
+  return sglb200_moe_align_block_size(topk_ids, numel, num_experts, block_size, sorted_token_ids, expert_ids,
+                                      num_tokens_post_pad, cumsum, pad_sorted_token_ids, workspace, workspace_bytes,
+                                      stream);
 }
