@@ -1,0 +1,205 @@
+"""Extra sections of bench.py: the per-M GEMM sweep of BASELINE config 1, the tensor-parallel Llama-3-70B
+layer of config 2 and the expert-parallel DeepSeek-V3 MoE layer of config 3.  Each returns a dict that
+bench.py merges into its JSON line.  Times are CUDA-event times on the launching stream, max over ranks.
+"""
+from __future__ import annotations
+
+import torch
+
+SWEEP_M = [1, 16, 64, 256, 1024, 4096, 8192]
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def _max_ms(ms, world, dev):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _time(fn, iters, warmup, world, dev):
+    for _ in range(warmup):
+        fn()
+    _barrier(world)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return _max_ms(e0.elapsed_time(e1) / iters, world, dev)
+
+
+def _fill_weight(dst_q, dst_s, gen, std=0.02, chunk=8):
+    """Random N(0,std) weights quantised per 128x128 block, written expert-chunk by expert-chunk."""
+    from bench import make_block_fp8_weight
+    if dst_q.dim() == 2:
+        q, s = make_block_fp8_weight(dst_q.shape[0], dst_q.shape[1], dst_q.device, gen, std)
+        dst_q.copy_(q)
+        dst_s.copy_(s)
+        return
+    E, N, K = dst_q.shape
+    for e0 in range(0, E, chunk):
+        n = min(chunk, E - e0)
+        q, s = make_block_fp8_weight(N, K, dst_q.device, gen, std, experts=n)
+        dst_q[e0 : e0 + n].copy_(q)
+        dst_s[e0 : e0 + n].copy_(s)
+        del q, s
+
+
+# ------------------------------------------------------------------------------------------------
+# config 1: GEMM sweep over M
+# ------------------------------------------------------------------------------------------------
+
+
+def gemm_sweep(args, ctx, peaks):
+    from bench import DSV3_LAYERS, make_block_fp8_weight
+    from sglang_b200 import ops
+    rank, world, dev = ctx
+    gen = torch.Generator(device=dev).manual_seed(7)
+    out = {}
+    for name, N, K in DSV3_LAYERS:
+        wq, ws = make_block_fp8_weight(N, K, dev, gen)
+        # rotate over enough copies of the weight that successive launches cannot hit L2
+        copies = max(1, -(-2 * L2_BYTES // (N * K)))
+        wqs = [wq] + [wq.clone() for _ in range(copies - 1)]
+        res = {}
+        for M in SWEEP_M:
+            x = torch.randn(M, K, device=dev, generator=gen).bfloat16()
+            xq, xs = ops.per_token_group_quant_fp8(x, 128)
+            state = {"i": 0}
+
+            def run():
+                w = wqs[state["i"] % copies]
+                state["i"] += 1
+                ops.w8a8_block_fp8_matmul(xq, w, xs, ws, [128, 128], torch.bfloat16)
+
+            iters = 20 if M <= 1024 else 10
+            ms = _time(run, iters, 3, world, dev)
+            flops = 2.0 * M * N * K
+            nbytes = M * K + N * K + 2 * M * N + 4 * M * (K // 128) + 4 * ((N + 127) // 128) * (K // 128)
+            res[str(M)] = {"us": ms * 1e3, "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6}
+        out[name] = res
+        del wqs, wq
+        torch.cuda.empty_cache()
+    return {"gemm_sweep": {"unit": "us / TFLOP/s / GB/s (algorithmic bytes)", "l2": "weight copies rotated so that "
+                           "consecutive launches exceed the 126 MB L2", "layers": out,
+                           "hbm_peak_gbs": peaks["hbm_gbs"], "fp8_peak_tflops": 2 * peaks["bf16"]}}
+
+
+# ------------------------------------------------------------------------------------------------
+# config 2: Llama-3-70B-shaped layer, tensor parallel
+# ------------------------------------------------------------------------------------------------
+
+
+def tp_layer(args, ctx, peaks):
+    """QKV (column) -> o_proj (row + all-reduce) -> gate_up (column) -> silu_and_mul -> down (row + all-reduce).
+    Attention itself is not on this path: o_proj is fed a tensor of the attention output's shape."""
+    from sglang_b200 import ops
+    from sglang_b200.srt.distributed import initialize_model_parallel
+    from sglang_b200.srt.layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
+    from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+    rank, world, dev = ctx
+    initialize_model_parallel(world, world)
+    cfg = Fp8Config()
+    H, I, heads, kv_heads, hd = 8192, 28672, 64, 8, 128
+    gen = torch.Generator(device=dev).manual_seed(11 + rank)
+    qkv = QKVParallelLinear(H, hd, heads, kv_heads, quant_config=cfg, device=dev)
+    o_proj = RowParallelLinear(heads * hd, H, quant_config=cfg, device=dev)
+    gate_up = MergedColumnParallelLinear(H, [I, I], quant_config=cfg, device=dev)
+    down = RowParallelLinear(I, H, quant_config=cfg, device=dev)
+    for lin in (qkv, o_proj, gate_up, down):
+        _fill_weight(lin.weight.data, lin.weight_scale_inv.data, gen)
+    flops_per_token = 2.0 * (H * (heads + 2 * kv_heads) * hd + heads * hd * H + H * 2 * I + I * H)
+    res = {}
+    for M in (8, 128, 2048, 8192):
+        x = torch.randn(M, H, device=dev, generator=gen).bfloat16()
+        attn = torch.randn(M, heads * hd // world, device=dev, generator=gen).bfloat16()
+
+        def layer():
+            qkv(x)
+            h, _ = o_proj(attn)
+            gu, _ = gate_up(h)
+            act = torch.empty(M, gu.shape[1] // 2, device=dev, dtype=gu.dtype)
+            ops.silu_and_mul_out(act, gu)
+            down(act)
+
+        ms = _time(layer, 10 if M >= 2048 else 20, 3, world, dev)
+        res[str(M)] = {"ms": ms, "tflops": flops_per_token * M / ms / 1e9, "allreduce_bytes": 2 * M * H * 2}
+    return {"tp_layer": {"config": "BASELINE config 2: Llama-3-70B layer (hidden 8192, inter 28672, 64q/8kv x 128), "
+                                   "QKV + gate_up column-parallel, o_proj + down row-parallel with NCCL all-reduce",
+                         "tp": world, "scaling": "strong", "results": res}}
+
+
+# ------------------------------------------------------------------------------------------------
+# config 3: DeepSeek-V3-shaped MoE layer, expert parallel
+# ------------------------------------------------------------------------------------------------
+
+
+def moe_layer(args, ctx, peaks):
+    from sglang_b200 import ops
+    from sglang_b200.srt.distributed import initialize_model_parallel
+    from sglang_b200.srt.layers.linear import ColumnParallelLinear
+    from sglang_b200.srt.layers.moe.fused_moe_triton.layer import FusedMoE
+    from sglang_b200.srt.layers.moe.token_dispatcher import StandardTopKOutput
+    from sglang_b200.srt.layers.moe.topk import biased_grouped_topk
+    from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+    rank, world, dev = ctx
+    initialize_model_parallel(1, world)
+    cfg = Fp8Config()
+    E, H, I, topk = 256, 7168, 2048, 8
+    gen = torch.Generator(device=dev).manual_seed(23 + rank)
+    moe = FusedMoE(E, H, I, topk, quant_config=cfg, a2a_backend="nccl", device=dev)
+    _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
+    _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
+    # the shared expert is a dense block-FP8 MLP replicated on every rank (models/deepseek_v2.py:826-882)
+    sh_gate_up = ColumnParallelLinear(H, 2 * I, quant_config=cfg, device=dev)
+    sh_down = ColumnParallelLinear(I, H, quant_config=cfg, device=dev)
+    for lin in (sh_gate_up, sh_down):
+        _fill_weight(lin.weight.data, lin.weight_scale_inv.data, gen)
+    res = {}
+    for T in (1, 64, 512, 4096):
+        x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
+        logits = torch.randn(T, E, device=dev, generator=gen)
+        w, ids = biased_grouped_topk(logits, None, topk, True, 8, 4)
+        top = StandardTopKOutput(w, ids, None)
+
+        def layer():
+            routed = moe(x, top)
+            gu, _ = sh_gate_up(x)
+            act = torch.empty(T, I, device=dev, dtype=gu.dtype)
+            ops.silu_and_mul_out(act, gu)
+            shared, _ = sh_down(act)
+            return routed + shared
+
+        ms = _time(layer, 10, 3, world, dev)
+        flops = 6.0 * T * topk * H * I + 6.0 * T * H * I
+        res[str(T)] = {"ms": ms, "tokens_per_s": world * T / ms * 1e3, "tflops_per_gpu": flops / ms / 1e9}
+    return {"moe_layer": {"config": "BASELINE config 3: DeepSeek-V3 MoE, 256 routed experts + 1 shared, hidden 7168, "
+                                    "moe_intermediate 2048, top-8 grouped sigmoid routing (8 groups, top-4), "
+                                    "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine",
+                          "ep": world, "scaling": "weak", "results": res}}
+
+
+def run(sections, args, ctx, peaks):
+    out = {}
+    rank, world, dev = ctx
+    if "sweep" in sections and world == 1:
+        out.update(gemm_sweep(args, ctx, peaks))
+        torch.cuda.empty_cache()
+    if "tp" in sections:
+        out.update(tp_layer(args, ctx, peaks))
+        torch.cuda.empty_cache()
+    if "moe" in sections:
+        out.update(moe_layer(args, ctx, peaks))
+        torch.cuda.empty_cache()
+    return out

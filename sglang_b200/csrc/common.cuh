@@ -68,4 +68,16 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   return r;
 }
 
+// Four float32 -> four e4m3 codes packed little-endian (a in bits 0-7 ... d in bits 24-31).
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
+}
+
 }  // namespace sglb200

@@ -8,11 +8,14 @@
 //   * warp 1 (one elected lane) issues four tcgen05.mma kind::f8f6f4 (128x128x32) that write the
 //     slab's partial sums into one of four 128-column TMEM buffers, then commits the slab to the
 //     `empty` barrier of the ring slot and to the `tmem_full` barrier of the buffer;
-//   * warps 4-11 (two warpgroups, 64 columns each) pull the partial sums out of TMEM with
+//   * warps 4-19 (four warpgroups, 32 columns each) pull the partial sums out of TMEM with
 //     tcgen05.ld, release the buffer, and promote them into float32 register accumulators with the
 //     slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be folded into
 //     the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores, overlapped with
-//     the next slabs' MMAs through the four TMEM buffers).
+//     the next slabs' MMAs through the four TMEM buffers).  Four warps per scheduler hide the
+//     tcgen05.ld round trip of one another.  The activation scales of the tile reach the promotion
+//     warps through shared memory: 16 slabs' worth (128 rows x 16) are fetched with coalesced
+//     128-bit loads while the previous 16 slabs are being promoted.
 // The epilogue converts to bf16/fp16 and stores 16 bytes at a time; in grouped "scatter" mode it
 // multiplies by the routing weight and writes to the token-major row named by sorted_token_ids.
 //
@@ -32,9 +35,12 @@ constexpr int BM = 128, BN = 128, BK = 128;
 constexpr int kStages = 6;
 constexpr int kAccBufs = 4;
 constexpr int kTmemCols = kAccBufs * BN;  // 512
-constexpr int kGemmThreads = 384;         // warps 0-3 control, 4-11 epilogue
+constexpr int kGemmThreads = 640;         // warps 0-3 control, 4-19 promotion + epilogue
 constexpr int kEpiWarp0 = 4;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kEpiCols = BN / (kEpiWarps / 4);  // 32 columns per warp
+constexpr int kScaleChunk = 16;                 // slabs of activation scales staged per shared-memory buffer
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 constexpr uint32_t kTileBytesB = BN * BK;
 constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
@@ -62,6 +68,7 @@ struct GemmParams {
 };
 
 struct SharedCtl {
+  float a_scale[2][kScaleChunk][BM];  // [buffer][slab in chunk][row of the tile]
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t tmem_full[kAccBufs];
@@ -87,9 +94,9 @@ __device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int&
 
 template <typename OutT>
 __device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, const void* bias_v, int n0, int64_t N) {
-  // 64 consecutive columns starting at n0, 8 per 16-byte store
+  // kEpiCols consecutive columns starting at n0, 8 per 16-byte store
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < kEpiCols / 8; ++j) {
     const int n = n0 + j * 8;
     if (n + 8 <= N) {
       float x[8];
@@ -216,51 +223,88 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   } else if (warp >= kEpiWarp0) {
     // ------------------------------ promotion + epilogue ------------------------------
-    const int q = warp & 3;                    // TMEM lane quadrant this warp may read
-    const int half = (warp - kEpiWarp0) >> 2;  // which 64 of the 128 columns
+    // A thread that sees the abort flag keeps walking the same loops (without waiting or touching TMEM) so
+    // that the named barrier below always collects all kEpiThreads arrivals.
+    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
+    const int cgrp = (warp - kEpiWarp0) >> 2;   // which 32 of the 128 columns
+    const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
+    const int row_in_tile = q * 32 + lane;
+    const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
+                            (reinterpret_cast<uintptr_t>(p.a_s) & 15u) == 0;
     uint32_t it = 0;
     bool alive = true;
-    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int m_tile, n_tile;
       tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
-      const int64_t row = (int64_t)m_tile * BM + q * 32 + lane;
-      const int n0 = n_tile * BN + half * 64;
+      const int64_t row = (int64_t)m_tile * BM + row_in_tile;
+      const int n0 = n_tile * BN + cgrp * kEpiCols;
       int e = 0;
       if (kGrouped) e = p.expert_ids[m_tile];
-      float acc[64];
+      float acc[kEpiCols];
 #pragma unroll
-      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+      for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
       if (e >= 0) {
-        const bool row_ok = row < rows;
-        const float* as_row = p.a_s + row * p.as_stride_m;
         const float* bs_row = p.b_s + ((int64_t)e * p.nb_total + n_tile) * kb_total;
-        float sa = row_ok ? __ldg(as_row) : 0.f;
-        float sb = __ldg(bs_row);
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
-          const float scale = sa * sb;
-          if (kb + 1 < kb_total) {  // next slab's scales travel while this slab is promoted
-            sa = row_ok ? __ldg(as_row + (int64_t)(kb + 1) * p.as_stride_k) : 0.f;
-            sb = __ldg(bs_row + kb + 1);
+        const int num_chunks = (kb_total + kScaleChunk - 1) / kScaleChunk;
+        // this thread's share of a chunk of activation scales: 4 values
+        //   vector form : row ep_tid/4, slabs 4*(ep_tid%4) .. +3      (one 128-bit load)
+        //   generic form: row ep_tid%128, slabs 4*(ep_tid/128) .. +3  (coalesced along rows)
+        const int s_row = vec_scales ? (ep_tid >> 2) : (ep_tid & (BM - 1));
+        const int s_kb = vec_scales ? ((ep_tid & 3) << 2) : ((ep_tid >> 7) << 2);
+        const int64_t g_row = (int64_t)m_tile * BM + s_row;
+        float4 sv;
+        auto fetch_scales = [&](int chunk) {
+          const int kb0 = chunk * kScaleChunk + s_kb;
+          sv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (g_row < rows) {
+            const float* src = p.a_s + g_row * p.as_stride_m + (int64_t)kb0 * p.as_stride_k;
+            if (vec_scales && kb0 + 3 < kb_total) {
+              sv = __ldg(reinterpret_cast<const float4*>(src));
+            } else {
+              if (kb0 + 0 < kb_total) sv.x = __ldg(src);
+              if (kb0 + 1 < kb_total) sv.y = __ldg(src + p.as_stride_k);
+              if (kb0 + 2 < kb_total) sv.z = __ldg(src + 2 * p.as_stride_k);
+              if (kb0 + 3 < kb_total) sv.w = __ldg(src + 3 * p.as_stride_k);
+            }
           }
-          const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
-          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) { alive = false; break; }
-          ptx::tc_fence_after();
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * 64;
-          uint32_t r0[32], r1[32];
-          ptx::tmem_ld_32x32(taddr, r0);
-          ptx::tmem_ld_32x32(taddr + 32, r1);
-          ptx::tmem_ld_wait();
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
+        };
+        auto stash_scales = [&](int buf) {
+          ctl->a_scale[buf][s_kb + 0][s_row] = sv.x;
+          ctl->a_scale[buf][s_kb + 1][s_row] = sv.y;
+          ctl->a_scale[buf][s_kb + 2][s_row] = sv.z;
+          ctl->a_scale[buf][s_kb + 3][s_row] = sv.w;
+        };
+        fetch_scales(0);
+        stash_scales(0);
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        for (int c = 0; c < num_chunks; ++c) {
+          if (c + 1 < num_chunks) fetch_scales(c + 1);  // in flight while this chunk is promoted
+          const int kb_end = min(kb_total, (c + 1) * kScaleChunk);
+          float sb = __ldg(bs_row + c * kScaleChunk);
+          for (int kb = c * kScaleChunk; kb < kb_end; ++kb, ++it) {
+            const float scale = ctl->a_scale[c & 1][kb - c * kScaleChunk][row_in_tile] * sb;
+            if (kb + 1 < kb_end) sb = __ldg(bs_row + kb + 1);
+            const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
+            if (alive && !ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) alive = false;
+            alive = __all_sync(0xffffffffu, alive);  // the warp-wide tcgen05.ld below needs a uniform decision
+            if (alive) {
+              ptx::tc_fence_after();
+              const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + cgrp * kEpiCols;
+              uint32_t r[32];
+              ptx::tmem_ld_32x32(taddr, r);
+              ptx::tmem_ld_wait();
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            acc[j] = fmaf(__uint_as_float(r0[j]), scale, acc[j]);
-            acc[32 + j] = fmaf(__uint_as_float(r1[j]), scale, acc[32 + j]);
+              for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r[j]), scale, acc[j]);
+            }
           }
+          if (c + 1 < num_chunks) stash_scales((c + 1) & 1);
+          asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         }
-        if (!alive) break;
       }
+      if (!alive) continue;
       // ---- store ----
       int64_t out_row = row;
       bool store_ok = row < rows;
@@ -271,7 +315,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (store_ok && p.row_weights != nullptr) {
           const float w = __ldg(p.row_weights + id);
 #pragma unroll
-          for (int j = 0; j < 64; ++j) acc[j] *= w;
+          for (int j = 0; j < kEpiCols; ++j) acc[j] *= w;
         }
       }
       if (store_ok && n0 < p.N) {
