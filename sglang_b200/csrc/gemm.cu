@@ -2,20 +2,22 @@
 //
 //   C[m,n] = out_t( sum_kb a_s[m,kb] * b_s[n/128,kb] * sum_{k in kb} A[m,k] * B[n,k] )
 //
-// One persistent CTA per SM walks 128x128 output tiles.  Per 128-wide K slab:
-//   * warp 0 (one elected lane) issues two TMA tile loads (A 128x128 B, B 128x128 B, 128-byte
-//     swizzle) into a 6-deep shared-memory ring, signalled through `full` mbarriers;
-//   * warp 1 (one elected lane) issues four tcgen05.mma kind::f8f6f4 (128x128x32) that write the
-//     slab's partial sums into one of four 128-column TMEM buffers, then commits the slab to the
+// One persistent CTA per SM walks 128x192 output tiles (a 128x128 tile needs 128 B/clk per SM from
+// L2 at full tensor rate, more than the fabric delivers; 128x192 needs 107, and its 64-column
+// thirds never straddle a 128-wide scale block).  Per 128-wide K slab:
+//   * warp 0 (one elected lane) issues two TMA tile loads (A 128 rows x 128 B, B 192 rows x 128 B,
+//     128-byte swizzle) into a 5-deep shared-memory ring, signalled through `full` mbarriers;
+//   * warp 1 (one elected lane) issues four tcgen05.mma kind::f8f6f4 (128x192x32) that write the
+//     slab's partial sums into one of two TMEM buffers, then commits the slab to the
 //     `empty` barrier of the ring slot and to the `tmem_full` barrier of the buffer;
-//   * warps 4-19 (four warpgroups, 32 columns each) pull the partial sums out of TMEM with
+//   * warps 4-15 (three warpgroups, 64 columns each) pull the partial sums out of TMEM with
 //     tcgen05.ld, release the buffer, and promote them into float32 register accumulators with the
 //     slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be folded into
 //     the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores, overlapped with
-//     the next slabs' MMAs through the four TMEM buffers).  Four warps per scheduler hide the
+//     the next slab's MMAs through the two TMEM buffers).  Three warps per scheduler hide the
 //     tcgen05.ld round trip of one another.  The activation scales of the tile reach the promotion
-//     warps through shared memory: 16 slabs' worth (128 rows x 16) are fetched with coalesced
-//     128-bit loads while the previous 16 slabs are being promoted.
+//     warps through shared memory: 12 slabs' worth (128 rows x 12) are fetched with coalesced
+//     128-bit loads while the previous 12 slabs are being promoted.
 // The epilogue converts to bf16/fp16 and stores 16 bytes at a time; in grouped "scatter" mode it
 // multiplies by the routing weight and writes to the token-major row named by sorted_token_ids.
 //
@@ -31,16 +33,18 @@
 
 namespace sglb200 {
 
-constexpr int BM = 128, BN = 128, BK = 128;
-constexpr int kStages = 6;
-constexpr int kAccBufs = 4;
-constexpr int kTmemCols = kAccBufs * BN;  // 512
-constexpr int kGemmThreads = 640;         // warps 0-3 control, 4-19 promotion + epilogue
+constexpr int BM = 128, BN = 192, BK = 128;
+constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
+constexpr int kStages = 5;
+constexpr int kAccBufs = 2;
+constexpr int kAccStride = 256;           // TMEM columns between the two accumulator buffers
+constexpr int kTmemCols = 512;
+constexpr int kGemmThreads = 512;         // warp 0 TMA, warp 1 MMA + TMEM owner, warps 4-15 promotion + epilogue
 constexpr int kEpiWarp0 = 4;
-constexpr int kEpiWarps = 16;
+constexpr int kEpiWarps = 12;
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kEpiCols = BN / (kEpiWarps / 4);  // 32 columns per warp
-constexpr int kScaleChunk = 16;                 // slabs of activation scales staged per shared-memory buffer
+constexpr int kEpiCols = BN / (kEpiWarps / 4);  // 64 columns per warp
+constexpr int kScaleChunk = 12;                 // slabs of activation scales staged per shared-memory buffer
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 constexpr uint32_t kTileBytesB = BN * BK;
 constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
@@ -62,7 +66,8 @@ struct GemmParams {
   int64_t as_stride_m, as_stride_k;
   int64_t numel;               // grouped scatter: valid ids are < numel
   int kb_total;                // ceil(K/128)
-  int nb_total;                // ceil(N/128)
+  int nb_total;                // ceil(N/128): weight scale blocks along N
+  int tiles_n;                 // ceil(N/BN)
   int scatter;
   int out_fp16;
 };
@@ -140,7 +145,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     rows = lim < rows ? lim : rows;
   }
   const int tiles_m = (int)((rows + BM - 1) / BM);
-  const int tiles_n = p.nb_total;
+  const int tiles_n = p.tiles_n;
   const int num_tiles = tiles_m * tiles_n;
   const int kb_total = p.kb_total;
 
@@ -158,7 +163,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     ptx::tma_prefetch_desc(&map_a);
     ptx::tma_prefetch_desc(&map_b);
   }
-  if (warp == 2) {
+  if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -210,7 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t a_addr = ptx::smem_u32(tiles + s * kStageBytes);
           const uint64_t da = ptx::make_kmajor_sw128_desc(a_addr);
           const uint64_t db = ptx::make_kmajor_sw128_desc(a_addr + kTileBytesA);
-          const uint32_t d_tmem = tmem_base + buf * BN;
+          const uint32_t d_tmem = tmem_base + buf * kAccStride;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
@@ -226,7 +231,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // A thread that sees the abort flag keeps walking the same loops (without waiting or touching TMEM) so
     // that the named barrier below always collects all kEpiThreads arrivals.
     const int q = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int cgrp = (warp - kEpiWarp0) >> 2;   // which 32 of the 128 columns
+    const int cgrp = (warp - kEpiWarp0) >> 2;   // which 64 of the 192 columns
     const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
     const int row_in_tile = q * 32 + lane;
     const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
@@ -244,13 +249,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
       for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
       if (e >= 0) {
-        const float* bs_row = p.b_s + ((int64_t)e * p.nb_total + n_tile) * kb_total;
+        // a column group wholly past N still takes part in every hand-shake; its scale index is clamped
+        const int nb = min(n0 / kScaleBlockN, p.nb_total - 1);
+        const float* bs_row = p.b_s + ((int64_t)e * p.nb_total + nb) * kb_total;
         const int num_chunks = (kb_total + kScaleChunk - 1) / kScaleChunk;
         // this thread's share of a chunk of activation scales: 4 values
-        //   vector form : row ep_tid/4, slabs 4*(ep_tid%4) .. +3      (one 128-bit load)
+        //   vector form : row ep_tid/3, slabs 4*(ep_tid%3) .. +3      (one 128-bit load)
         //   generic form: row ep_tid%128, slabs 4*(ep_tid/128) .. +3  (coalesced along rows)
-        const int s_row = vec_scales ? (ep_tid >> 2) : (ep_tid & (BM - 1));
-        const int s_kb = vec_scales ? ((ep_tid & 3) << 2) : ((ep_tid >> 7) << 2);
+        const int s_row = vec_scales ? (ep_tid / 3) : (ep_tid & (BM - 1));
+        const int s_kb = vec_scales ? ((ep_tid % 3) << 2) : ((ep_tid >> 7) << 2);
         const int64_t g_row = (int64_t)m_tile * BM + s_row;
         float4 sv;
         auto fetch_scales = [&](int chunk) {
@@ -289,15 +296,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             alive = __all_sync(0xffffffffu, alive);  // the warp-wide tcgen05.ld below needs a uniform decision
             if (alive) {
               ptx::tc_fence_after();
-              const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + cgrp * kEpiCols;
-              uint32_t r[32];
-              ptx::tmem_ld_32x32(taddr, r);
+              const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kAccStride + cgrp * kEpiCols;
+              // four 16-column pieces through two register sets: the load of piece i+1 is in flight while
+              // piece i is multiplied in (tcgen05.wait::ld waits for every outstanding load of the thread,
+              // so the next load is issued right after the wait)
+              uint32_t ra[16], rb[16];
+              ptx::tmem_ld_32x16(taddr, ra);
+              ptx::tmem_ld_wait();
+              ptx::tmem_ld_32x16(taddr + 16, rb);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] = fmaf(__uint_as_float(ra[j]), scale, acc[j]);
+              ptx::tmem_ld_wait();
+              ptx::tmem_ld_32x16(taddr + 32, ra);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[16 + j] = fmaf(__uint_as_float(rb[j]), scale, acc[16 + j]);
+              ptx::tmem_ld_wait();
+              ptx::tmem_ld_32x16(taddr + 48, rb);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[32 + j] = fmaf(__uint_as_float(ra[j]), scale, acc[32 + j]);
               ptx::tmem_ld_wait();
               ptx::tc_fence_before();
               __syncwarp();
               if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
 #pragma unroll
-              for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r[j]), scale, acc[j]);
+              for (int j = 0; j < 16; ++j) acc[48 + j] = fmaf(__uint_as_float(rb[j]), scale, acc[48 + j]);
             }
           }
           if (c + 1 < num_chunks) stash_scales((c + 1) & 1);
@@ -339,7 +361,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
   __syncthreads();
-  if (warp == 2) {
+  if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -464,9 +486,10 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   p.a_s = a_s, p.b_s = b_s, p.C = C, p.bias = bias;
   p.M = M, p.N = N, p.K = K;
   p.as_stride_m = as_stride_m, p.as_stride_k = as_stride_k;
-  p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + BN - 1) / BN);
+  p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
+  p.tiles_n = (int)((N + BN - 1) / BN);
   p.out_fp16 = out_dtype;
-  const int64_t tiles = ((M + BM - 1) / BM) * p.nb_total;
+  const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
   return launch_gemm<false>(ma, mb, p, tiles, static_cast<cudaStream_t>(stream));
 }
 
@@ -493,9 +516,10 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   p.sorted_ids = sorted_token_ids, p.expert_ids = expert_ids, p.num_rows_dev = num_rows_dev;
   p.row_weights = row_weights;
   p.M = max_rows, p.N = N, p.K = K;
-  p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + BN - 1) / BN);
+  p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
+  p.tiles_n = (int)((N + BN - 1) / BN);
   p.as_stride_m = p.kb_total, p.as_stride_k = 1;
   p.numel = numel, p.scatter = scatter, p.out_fp16 = out_dtype;
-  const int64_t tiles = ((max_rows + BM - 1) / BM) * p.nb_total;
+  const int64_t tiles = ((max_rows + BM - 1) / BM) * p.tiles_n;
   return launch_gemm<true>(ma, mb, p, tiles, static_cast<cudaStream_t>(stream));
 }
