@@ -66,6 +66,9 @@ struct GemmParams {
   int64_t as_stride_m, as_stride_k;
   int64_t numel;               // grouped scatter: valid ids are < numel
   int kb_total;                // ceil(K/128)
+  int splits;                  // split-K: units per output tile (1 = none)
+  int kb_per_split;            // K slabs per unit
+  float* partial;              // split-K: [splits][M][N] float32 partial sums
   int nb_total;                // ceil(N/128): weight scale blocks along N
   int tiles_n;                 // ceil(N/BN)
   int scatter;
@@ -148,6 +151,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int tiles_n = p.tiles_n;
   const int num_tiles = tiles_m * tiles_n;
   const int kb_total = p.kb_total;
+  const int splits = kGrouped ? 1 : p.splits;
+  const int num_units = num_tiles * splits;  // a unit = one output tile x one K range
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -177,7 +182,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (ptx::elect_one()) {
       uint32_t it = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
+        const int t = u / splits, sp = u - t * splits;
+        const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
         int m_tile, n_tile;
         tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
         int e = 0;
@@ -185,7 +192,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           e = p.expert_ids[m_tile];
           if (e < 0) continue;
         }
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_stop; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           if (!ptx::mbar_wait(ptx::smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) { alive = false; break; }
           const uint32_t bar = ptx::smem_u32(&ctl->full[s]);
@@ -202,11 +209,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
       uint32_t it = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
+        const int t = u / splits, sp = u - t * splits;
+        const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
         int m_tile, n_tile;
         tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
         if (kGrouped && p.expert_ids[m_tile] < 0) continue;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_stop; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
           if (!ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_empty[buf]), aph ^ 1u, abort_flag)) { alive = false; break; }
@@ -238,7 +247,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                             (reinterpret_cast<uintptr_t>(p.a_s) & 15u) == 0;
     uint32_t it = 0;
     bool alive = true;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+      const int t = u / splits, sp = u - t * splits;
+      const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
       int m_tile, n_tile;
       tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
       const int64_t row = (int64_t)m_tile * BM + row_in_tile;
@@ -252,7 +263,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // a column group wholly past N still takes part in every hand-shake; its scale index is clamped
         const int nb = min(n0 / kScaleBlockN, p.nb_total - 1);
         const float* bs_row = p.b_s + ((int64_t)e * p.nb_total + nb) * kb_total;
-        const int num_chunks = (kb_total + kScaleChunk - 1) / kScaleChunk;
+        const int num_chunks = (kb_stop - kb_begin + kScaleChunk - 1) / kScaleChunk;
         // this thread's share of a chunk of activation scales: 4 values
         //   vector form : row ep_tid/3, slabs 4*(ep_tid%3) .. +3      (one 128-bit load)
         //   generic form: row ep_tid%128, slabs 4*(ep_tid/128) .. +3  (coalesced along rows)
@@ -261,11 +272,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int64_t g_row = (int64_t)m_tile * BM + s_row;
         float4 sv;
         auto fetch_scales = [&](int chunk) {
-          const int kb0 = chunk * kScaleChunk + s_kb;
+          const int kb0 = kb_begin + chunk * kScaleChunk + s_kb;
           sv = make_float4(0.f, 0.f, 0.f, 0.f);
           if (g_row < rows) {
             const float* src = p.a_s + g_row * p.as_stride_m + (int64_t)kb0 * p.as_stride_k;
-            if (vec_scales && kb0 + 3 < kb_total) {
+            if (vec_scales && kb0 + 3 < kb_total && (kb0 & 3) == 0) {
               sv = __ldg(reinterpret_cast<const float4*>(src));
             } else {
               if (kb0 + 0 < kb_total) sv.x = __ldg(src);
@@ -286,10 +297,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         for (int c = 0; c < num_chunks; ++c) {
           if (c + 1 < num_chunks) fetch_scales(c + 1);  // in flight while this chunk is promoted
-          const int kb_end = min(kb_total, (c + 1) * kScaleChunk);
-          float sb = __ldg(bs_row + c * kScaleChunk);
-          for (int kb = c * kScaleChunk; kb < kb_end; ++kb, ++it) {
-            const float scale = ctl->a_scale[c & 1][kb - c * kScaleChunk][row_in_tile] * sb;
+          const int kb_end = min(kb_stop, kb_begin + (c + 1) * kScaleChunk);
+          const int kb_first = kb_begin + c * kScaleChunk;
+          float sb = __ldg(bs_row + kb_first);
+          for (int kb = kb_first; kb < kb_end; ++kb, ++it) {
+            const float scale = ctl->a_scale[c & 1][kb - kb_first][row_in_tile] * sb;
             if (kb + 1 < kb_end) sb = __ldg(bs_row + kb + 1);
             const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
             if (alive && !ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) alive = false;
@@ -328,6 +340,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       if (!alive) continue;
       // ---- store ----
+      if (!kGrouped && splits > 1) {
+        // split-K: this unit's float32 partial sums; a second kernel adds the units of a tile in a fixed order
+        if (row < rows && n0 < p.N) {
+          float* dst = p.partial + ((int64_t)sp * p.M + row) * p.N + n0;
+#pragma unroll
+          for (int j = 0; j < kEpiCols / 4; ++j) {
+            const int n = n0 + j * 4;
+            if (n + 4 <= p.N)
+              *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+            else
+              for (int i = 0; i < 4 && n + i < p.N; ++i) dst[j * 4 + i] = acc[4 * j + i];
+          }
+        }
+        continue;
+      }
       int64_t out_row = row;
       bool store_ok = row < rows;
       if (kGrouped && p.scatter) {
@@ -365,6 +392,57 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+// Sums the split-K partials of every output element in ascending split order (deterministic), adds the
+// bias and rounds once.  8 outputs per thread.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+    splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
+                         int64_t total8, int64_t MN, int n8_per_row, int splits) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total8) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < splits; ++s) {
+    const float4* src = reinterpret_cast<const float4*>(partial + (int64_t)s * MN + i * 8);
+    const float4 a = __ldg(src), b = __ldg(src + 1);
+    acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
+    acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+  }
+  if (bias != nullptr) {
+    const int n = (int)(i % n8_per_row) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += ElemTraits<OutT>::to_f32(bias[n + j]);
+  }
+  uint4 raw;
+  OutT* o = reinterpret_cast<OutT*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = ElemTraits<OutT>::from_f32(acc[j]);
+  reinterpret_cast<uint4*>(C)[i] = raw;
+}
+
+// Split-K policy for the weight-streaming regime: few output tiles (the grid would leave most SMs idle) and a
+// long K.  The partial sums cost 8*M*N*splits bytes of extra traffic, kept below a quarter of the weight bytes.
+static int choose_splits(int64_t M, int64_t N, int64_t K, int* kb_per_split) {
+  const int kb_total = (int)((K + BK - 1) / BK);
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int sms = sm_count();
+  int splits = 1;
+  // (measured: splitting further, to several units per SM, costs more in partial-sum traffic and per-unit
+  // start-up than it gains in balance)
+  if (tiles * 2 <= sms && kb_total >= 8) {
+    int64_t s = sms / tiles;
+    const int64_t by_traffic = K / (32 * M);
+    if (s > by_traffic) s = by_traffic;
+    if (s > kb_total / 4) s = kb_total / 4;
+    if (s > 16) s = 16;
+    if (s > 1) splits = (int)s;
+  }
+  int per = (kb_total + splits - 1) / splits;
+  per = (per + 3) / 4 * 4;  // keeps the 128-bit loads of the activation scales aligned
+  splits = (kb_total + per - 1) / per;
+  *kb_per_split = per;
+  return splits;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -437,8 +515,14 @@ template <bool kGrouped>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int64_t max_tiles,
                        cudaStream_t st) {
   const size_t smem = gemm_smem_bytes();
-  SGLB_CUDA(cudaFuncSetAttribute(fp8_blockscale_gemm_kernel<kGrouped>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
+  static thread_local bool attr_set[64] = {false};  // the opt-in is per function and per device
+  int dev = 0;
+  SGLB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    SGLB_CUDA(cudaFuncSetAttribute(fp8_blockscale_gemm_kernel<kGrouped>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
   const int sms = sm_count();
   const unsigned grid = (unsigned)(max_tiles < sms ? max_tiles : sms);
   fp8_blockscale_gemm_kernel<kGrouped><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
@@ -457,15 +541,16 @@ extern "C" int sglb200_gemm_status(void) {
 }
 
 extern "C" int64_t sglb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  (void)M, (void)N, (void)K;
-  return 0;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  int per = 0;
+  const int splits = choose_splits(M, N, K, &per);
+  return splits > 1 ? (int64_t)splits * M * N * (int64_t)sizeof(float) : 0;
 }
 
 extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, const float* a_s, const float* b_s,
                                                void* C, const void* bias, int64_t M, int64_t N, int64_t K,
                                                int64_t as_stride_m, int64_t as_stride_k, int out_dtype,
                                                void* workspace, int64_t workspace_bytes, void* stream) {
-  (void)workspace, (void)workspace_bytes;
   SGLB_REQUIRE(M >= 0 && N > 0 && K > 0, "fp8_blockwise_scaled_mm: bad shape M=%lld N=%lld K=%lld", (long long)M,
                (long long)N, (long long)K);
   SGLB_REQUIRE(K % 16 == 0, "fp8_blockwise_scaled_mm: K=%lld must be a multiple of 16", (long long)K);
@@ -489,8 +574,29 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.out_fp16 = out_dtype;
+  int per = 0;
+  int splits = choose_splits(M, N, K, &per);
+  if (splits > 1 && (workspace == nullptr || workspace_bytes < (int64_t)splits * M * N * (int64_t)sizeof(float) ||
+                     !aligned16(workspace)))
+    splits = 1;  // no scratch offered: one unit per tile
+  p.splits = splits;
+  p.kb_per_split = splits > 1 ? per : p.kb_total;
+  p.partial = static_cast<float*>(workspace);
+  if (splits > 1) p.bias = nullptr;  // added by the reduction
   const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
-  return launch_gemm<false>(ma, mb, p, tiles, static_cast<cudaStream_t>(stream));
+  rc = launch_gemm<false>(ma, mb, p, tiles * splits, static_cast<cudaStream_t>(stream));
+  if (rc != SGLB200_OK || splits == 1) return rc;
+  const int64_t total8 = M * N / 8;
+  const unsigned blocks = (unsigned)((total8 + 255) / 256);
+  if (out_dtype == 0)
+    splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        p.partial, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), total8, M * N, (int)(N / 8),
+        splits);
+  else
+    splitk_reduce_kernel<__half><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        p.partial, static_cast<__half*>(C), static_cast<const __half*>(bias), total8, M * N, (int)(N / 8), splits);
+  SGLB_CUDA(cudaGetLastError());
+  return SGLB200_OK;
 }
 
 extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s, const void* B, const float* b_s,
@@ -520,6 +626,7 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.as_stride_m = p.kb_total, p.as_stride_k = 1;
   p.numel = numel, p.scatter = scatter, p.out_fp16 = out_dtype;
+  p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;
   const int64_t tiles = ((max_rows + BM - 1) / BM) * p.tiles_n;
   return launch_gemm<true>(ma, mb, p, tiles, static_cast<cudaStream_t>(stream));
 }

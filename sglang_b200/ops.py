@@ -244,11 +244,14 @@ def w8a8_block_fp8_matmul(
     if bias is not None:
         bias = bias.to(output_dtype).contiguous()
     if M > 0:
+        ws_bytes = lib.sglb200_gemm_workspace_bytes(M, N, K)  # split-K scratch for the small-M regime
+        ws = torch.empty(ws_bytes, device=A.device, dtype=torch.uint8) if ws_bytes else None
         check(
             lib.sglb200_fp8_blockwise_scaled_mm(
                 A.data_ptr(), B.data_ptr(), As2.data_ptr(), Bs.data_ptr(), C.data_ptr(),
                 bias.data_ptr() if bias is not None else None, M, N, K, As2.stride(0), As2.stride(1),
-                0 if output_dtype == torch.bfloat16 else 1, None, 0, _stream(A),
+                0 if output_dtype == torch.bfloat16 else 1, ws.data_ptr() if ws is not None else None, ws_bytes,
+                _stream(A),
             )
         )
     return C
