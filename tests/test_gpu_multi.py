@@ -1,0 +1,109 @@
+"""Two-GPU parity of the tensor-parallel linears and the expert-parallel MoE layer (NCCL).
+Skipped on boxes with a single GPU; the host logic of both is also covered on CPU (gloo) in
+tests/test_host_logic.py."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import block_fp8_oracle as O
+from tests.util import assert_close_fp, codes_to_fp8, make_act, make_weight, to_f32_np
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from sglang_b200.srt.distributed import initialize_model_parallel
+        from sglang_b200.srt.layers.linear import MergedColumnParallelLinear, RowParallelLinear
+        from sglang_b200.srt.layers.moe.fused_moe_triton.layer import FusedMoE
+        from sglang_b200.srt.layers.moe.token_dispatcher import StandardTopKOutput
+        from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+        initialize_model_parallel(world, world)
+        cfg = Fp8Config()
+        # ---- tensor parallel: gate_up (column) -> down (row + all-reduce) on replicated tokens ----
+        H, I, M = 512, 768, 70
+        w1q, w1s = make_weight(2 * I, H, 1)
+        w2q, w2s = make_weight(H, I, 2)
+        x = make_act(M, H, 3, outliers=False)
+        gate_up = MergedColumnParallelLinear(H, [I, I], quant_config=cfg, device=dev)
+        down = RowParallelLinear(I, H, quant_config=cfg, device=dev)
+        gate_up.load_full_weight(codes_to_fp8(w1q, dev), torch.from_numpy(w1s).to(dev))
+        down.load_full_weight(codes_to_fp8(w2q, dev), torch.from_numpy(w2s).to(dev))
+        gu, _ = gate_up(x.to(dev))          # [M, 2I/world]: this rank's slice of gate and of up
+        h = (torch.nn.functional.silu(gu[:, : I // world].float()) * gu[:, I // world :].float()).to(torch.bfloat16)
+        y, _ = down(h)                        # all-reduced
+        # ---- expert parallel with all-to-all dispatch/combine; every rank owns different tokens ----
+        E, Hm, Im, topk, T = 8, 512, 256, 2, 33 + rank
+        w13q, w13s = make_weight(2 * Im, Hm, 5, std=0.05, experts=E)
+        wdq, wds = make_weight(Hm, Im, 6, std=0.05, experts=E)
+        g = torch.Generator().manual_seed(100 + rank)
+        xt = make_act(T, Hm, 7 + rank, outliers=False)
+        tw, ti = torch.topk(torch.softmax(torch.randn(T, E, generator=g), -1), topk)
+        tw = (tw / tw.sum(-1, keepdim=True)).float()
+        ti = ti.to(torch.int32)
+        # the replicate-and-mask form needs every rank to hold the same tokens: all ranks build rank 0's
+        g0 = torch.Generator().manual_seed(100)
+        x0 = make_act(33, Hm, 7, outliers=False)
+        tw0, ti0 = torch.topk(torch.softmax(torch.randn(33, E, generator=g0), -1), topk)
+        tw0 = (tw0 / tw0.sum(-1, keepdim=True)).float()
+        ti0 = ti0.to(torch.int32)
+        outs = {}
+        for backend, (xi, wi, ii) in (("nccl", (xt, tw, ti)), ("none", (x0, tw0, ti0))):
+            moe = FusedMoE(E, Hm, Im, topk, quant_config=cfg, a2a_backend=backend, device=dev)
+            moe.load_full_weights(codes_to_fp8(w13q, dev), torch.from_numpy(w13s).to(dev), codes_to_fp8(wdq, dev),
+                                  torch.from_numpy(wds).to(dev))
+            outs[backend] = moe(xi.to(dev), StandardTopKOutput(wi.to(dev), ii.to(dev), None)).float().cpu().numpy()
+        torch.cuda.synchronize()
+        from sglang_b200 import ops
+        ret[rank] = dict(y=y.float().cpu().numpy(), gu=gu.float().cpu().numpy(), moe_a2a=outs["nccl"],
+                         moe_std=outs["none"], x=to_f32_np(xt), tw=tw.numpy(), ti=ti.numpy(), status=ops.gemm_status())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_and_ep_on_two_gpus():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    H, I, M = 512, 768, 70
+    w1q, w1s = make_weight(2 * I, H, 1)
+    w2q, w2s = make_weight(H, I, 2)
+    x = to_f32_np(make_act(M, H, 3, outliers=False))
+    gu = O.block_fp8_linear(x, w1q, w1s)
+    h = O.bf16_round((gu[:, :I] / (1 + np.exp(-gu[:, :I]))).astype(np.float32) * gu[:, I:])
+    y_ref = O.block_fp8_linear(h, w2q, w2s)
+    E, Hm, Im, topk = 8, 512, 256, 2
+    w13q, w13s = make_weight(2 * Im, Hm, 5, std=0.05, experts=E)
+    wdq, wds = make_weight(Hm, Im, 6, std=0.05, experts=E)
+    for r in range(world):
+        d = ret[r]
+        assert d["status"] == 0
+        # column-parallel slices: rank r holds columns [r*I/2, (r+1)*I/2) of gate and of up
+        lo, hi = r * I // world, (r + 1) * I // world
+        assert_close_fp(d["gu"], np.concatenate([gu[:, lo:hi], gu[:, I + lo : I + hi]], 1))
+        # row-parallel: bf16 partial sums are added by the all-reduce, one extra bf16 rounding per rank
+        assert_close_fp(d["y"], y_ref, rtol=2e-2, atol=2e-2, min_cos=0.9995)
+        ref = O.fused_experts_block_fp8(d["x"], w13q, w13s, wdq, wds, d["tw"], d["ti"], 1.0)
+        assert_close_fp(d["moe_a2a"], ref, rtol=2e-2, atol=2e-2)
+    ref0 = O.fused_experts_block_fp8(ret[0]["x"], w13q, w13s, wdq, wds, ret[0]["tw"], ret[0]["ti"], 1.0)
+    for r in range(world):
+        assert_close_fp(ret[r]["moe_std"], ref0, rtol=2e-2, atol=2e-2)
