@@ -77,6 +77,7 @@ struct GemmParams {
 
 struct SharedCtl {
   float a_scale[2][kScaleChunk][BM];  // [buffer][slab in chunk][row of the tile]
+  float b_scale[2][2][kScaleChunk];   // [buffer][128-row weight block within the tile][slab in chunk]
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t tmem_full[kAccBufs];
@@ -180,7 +181,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (ptx::elect_one()) {
-      uint32_t it = 0;
+      const uint32_t bar_empty0 = ptx::smem_u32(&ctl->empty[0]), bar_full0 = ptx::smem_u32(&ctl->full[0]);
+      const uint32_t tiles0 = ptx::smem_u32(tiles);
+      uint32_t s = 0, ph = 0;
       bool alive = true;
       for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
         const int t = u / splits, sp = u - t * splits;
@@ -192,14 +195,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           e = p.expert_ids[m_tile];
           if (e < 0) continue;
         }
-        for (int kb = kb_begin; kb < kb_stop; ++kb, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) { alive = false; break; }
-          const uint32_t bar = ptx::smem_u32(&ctl->full[s]);
+        // this thread shares its scheduler with promotion warps that always have work: every instruction it
+        // spends per slab delays the loads, so the loop keeps only 32-bit counters that step
+        const int row_a = m_tile * BM, row_b = n_tile * BN;
+        for (int k0 = kb_begin * BK; k0 < kb_stop * BK; k0 += BK) {
+          if (!ptx::mbar_wait_lean(bar_empty0 + s * 8, ph ^ 1u, abort_flag)) { alive = false; break; }
+          const uint32_t bar = bar_full0 + s * 8;
           ptx::mbar_arrive_expect_tx(bar, kStageBytes);
-          const uint32_t dst_a = ptx::smem_u32(tiles + s * kStageBytes);
-          ptx::tma_load_2d(dst_a, &map_a, bar, kb * BK, m_tile * BM);
-          ptx::tma_load_3d(dst_a + kTileBytesA, &map_b, bar, kb * BK, n_tile * BN, e);
+          const uint32_t dst_a = tiles0 + s * kStageBytes;
+          ptx::tma_load_2d(dst_a, &map_a, bar, k0, row_a);
+          ptx::tma_load_3d(dst_a + kTileBytesA, &map_b, bar, k0, row_b, e);
+          if (++s == (uint32_t)kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
       }
     }
@@ -207,31 +216,42 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // ------------------------------ MMA issuer ------------------------------
     if (ptx::elect_one()) {
       constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
-      uint32_t it = 0;
+      // Operand descriptor (K-major, 128-byte swizzle): low word = address/16 | LBO(1) << 16, high word =
+      // SBO(1024/16) | version 1 (bit 46) | layout SWIZZLE_128B (2 at bit 61).  Only the low word changes.
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t desc_lo0 = ((ptx::smem_u32(tiles) & 0x3ffffu) >> 4) | (1u << 16);
+      const uint32_t bar_full0 = ptx::smem_u32(&ctl->full[0]), bar_empty0 = ptx::smem_u32(&ctl->empty[0]);
+      const uint32_t bar_tfull0 = ptx::smem_u32(&ctl->tmem_full[0]), bar_tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
+      uint32_t it = 0, s = 0, ph = 0;
       bool alive = true;
       for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
         const int t = u / splits, sp = u - t * splits;
         const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
-        int m_tile, n_tile;
-        tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
-        if (kGrouped && p.expert_ids[m_tile] < 0) continue;
+        if (kGrouped) {
+          int m_tile, n_tile;
+          tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
+          if (p.expert_ids[m_tile] < 0) continue;
+        }
         for (int kb = kb_begin; kb < kb_stop; ++kb, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
-          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_empty[buf]), aph ^ 1u, abort_flag)) { alive = false; break; }
-          if (!ptx::mbar_wait(ptx::smem_u32(&ctl->full[s]), ph, abort_flag)) { alive = false; break; }
+          const uint32_t buf = it & (kAccBufs - 1), aph = (it / kAccBufs) & 1u;
+          if (!ptx::mbar_wait_lean(bar_tempty0 + buf * 8, aph ^ 1u, abort_flag)) { alive = false; break; }
+          if (!ptx::mbar_wait_lean(bar_full0 + s * 8, ph, abort_flag)) { alive = false; break; }
           ptx::tc_fence_after();
-          const uint32_t a_addr = ptx::smem_u32(tiles + s * kStageBytes);
-          const uint64_t da = ptx::make_kmajor_sw128_desc(a_addr);
-          const uint64_t db = ptx::make_kmajor_sw128_desc(a_addr + kTileBytesA);
+          const uint32_t a_lo = desc_lo0 + s * (kStageBytes >> 4);
+          const uint32_t b_lo = a_lo + (kTileBytesA >> 4);
           const uint32_t d_tmem = tmem_base + buf * kAccStride;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
-            ptx::mma_f8f6f4(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, k > 0 ? 1u : 0u);
+            ptx::mma_f8f6f4(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi), idesc,
+                            k > 0 ? 1u : 0u);
           }
-          ptx::mma_commit(ptx::smem_u32(&ctl->empty[s]));
-          ptx::mma_commit(ptx::smem_u32(&ctl->tmem_full[buf]));
+          ptx::mma_commit(bar_empty0 + s * 8);
+          ptx::mma_commit(bar_tfull0 + buf * 8);
+          if (++s == (uint32_t)kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
       }
     }
@@ -262,7 +282,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (e >= 0) {
         // a column group wholly past N still takes part in every hand-shake; its scale index is clamped
         const int nb = min(n0 / kScaleBlockN, p.nb_total - 1);
-        const float* bs_row = p.b_s + ((int64_t)e * p.nb_total + nb) * kb_total;
+        const int blk_in_tile = nb - min(n_tile * BN / kScaleBlockN, p.nb_total - 1);  // 0 or 1
         const int num_chunks = (kb_stop - kb_begin + kScaleChunk - 1) / kScaleChunk;
         // this thread's share of a chunk of activation scales: 4 values
         //   vector form : row ep_tid/3, slabs 4*(ep_tid%3) .. +3      (one 128-bit load)
@@ -271,6 +291,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int s_kb = vec_scales ? ((ep_tid % 3) << 2) : ((ep_tid >> 7) << 2);
         const int64_t g_row = (int64_t)m_tile * BM + s_row;
         float4 sv;
+        float bv = 0.f;
         auto fetch_scales = [&](int chunk) {
           const int kb0 = kb_begin + chunk * kScaleChunk + s_kb;
           sv = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -285,8 +306,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               if (kb0 + 3 < kb_total) sv.w = __ldg(src + 3 * p.as_stride_k);
             }
           }
+          // weight-block scales of the chunk (a 192-wide tile touches two 128-row blocks): staged as well, so
+          // that the promotion loop has no global load on its critical path
+          if (ep_tid < 2 * kScaleChunk) {
+            const int blk = ep_tid / kScaleChunk, kk = ep_tid - blk * kScaleChunk;
+            const int kbb = kb_begin + chunk * kScaleChunk + kk;
+            const int nbb = min(n_tile * BN / kScaleBlockN + blk, p.nb_total - 1);
+            bv = kbb < kb_total ? __ldg(p.b_s + ((int64_t)e * p.nb_total + nbb) * kb_total + kbb) : 0.f;
+          }
         };
         auto stash_scales = [&](int buf) {
+          if (ep_tid < 2 * kScaleChunk) ctl->b_scale[buf][ep_tid / kScaleChunk][ep_tid % kScaleChunk] = bv;
           ctl->a_scale[buf][s_kb + 0][s_row] = sv.x;
           ctl->a_scale[buf][s_kb + 1][s_row] = sv.y;
           ctl->a_scale[buf][s_kb + 2][s_row] = sv.z;
@@ -299,10 +329,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (c + 1 < num_chunks) fetch_scales(c + 1);  // in flight while this chunk is promoted
           const int kb_end = min(kb_stop, kb_begin + (c + 1) * kScaleChunk);
           const int kb_first = kb_begin + c * kScaleChunk;
-          float sb = __ldg(bs_row + kb_first);
           for (int kb = kb_first; kb < kb_end; ++kb, ++it) {
-            const float scale = ctl->a_scale[c & 1][kb - kb_first][row_in_tile] * sb;
-            if (kb + 1 < kb_end) sb = __ldg(bs_row + kb + 1);
+            const float scale = ctl->a_scale[c & 1][kb - kb_first][row_in_tile] * ctl->b_scale[c & 1][blk_in_tile][kb - kb_first];
             const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
             if (alive && !ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) alive = false;
             alive = __all_sync(0xffffffffu, alive);  // the warp-wide tcgen05.ld below needs a uniform decision
