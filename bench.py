@@ -335,7 +335,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--sections", default="main,moe,tp,sweep")
+    ap.add_argument("--sections", default="main,moe,tp,sweep,hbm")
     ap.add_argument("--cpu-baseline", type=int, default=1)
     ap.add_argument("--layers", default="", help="comma-separated subset of layer names (profiler captures only)")
     ap.add_argument("--m-tokens", type=int, default=M_TOKENS, help="smaller values are for profiler captures only")

@@ -200,11 +200,75 @@ def moe_layer(args, ctx, peaks):
                           "ep": world, "scaling": "weak", "results": res}}
 
 
+# ------------------------------------------------------------------------------------------------
+# the memory-bound kernels of the path: GB/s of algorithmic bytes against the measured HBM copy rate
+# ------------------------------------------------------------------------------------------------
+
+
+def hbm_kernels(args, ctx, peaks):
+    from sglang_b200 import ops
+    rank, world, dev = ctx
+    gen = torch.Generator(device=dev).manual_seed(5)
+    out = {}
+
+    def graph_time(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                fn()
+        ms = _time(g.replay, 3, 1, world, dev) / iters
+        del g
+        return ms
+
+    # 1x128 quantizer at the largest activation of config 1 (8192 x 18432 bf16: 453 MB of traffic per call)
+    M, K = 8192, 18432
+    x = torch.randn(M, K, device=dev, generator=gen).bfloat16()
+    ms = graph_time(lambda: ops.per_token_group_quant_fp8(x, 128))
+    nbytes = M * K * 3 + M * (K // 128) * 4
+    out["per_token_group_quant_fp8"] = {"shape": [M, K], "us": ms * 1e3, "gbs": nbytes / ms / 1e6,
+                                        "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    del x
+    # fused silu_and_mul + quantizer on the config-3 intermediate of 4096 tokens x top-8 (32768 x 4096 bf16)
+    R, I = 32768, 2048
+    y = torch.randn(R, 2 * I, device=dev, generator=gen).bfloat16()
+    ms = graph_time(lambda: ops.silu_and_mul_quant_fp8(y, 128))
+    nbytes = R * (2 * I * 2 + I + (I // 128) * 4)
+    out["silu_and_mul_quant_fp8"] = {"shape": [R, 2 * I], "us": ms * 1e3, "gbs": nbytes / ms / 1e6,
+                                     "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    del y
+    # top-k sum on [4096, 8, 7168]
+    z = torch.randn(4096, 8, 7168, device=dev, generator=gen).bfloat16()
+    o = torch.empty(4096, 7168, device=dev, dtype=torch.bfloat16)
+    ms = graph_time(lambda: ops.moe_sum_reduce_out(z, o, 1.0))
+    nbytes = z.numel() * 2 + o.numel() * 2
+    out["moe_sum_reduce"] = {"shape": [4096, 8, 7168], "us": ms * 1e3, "gbs": nbytes / ms / 1e6,
+                             "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    del z, o
+    # moe_align_block_size: the layer sizes (latency regime) and a bandwidth-regime input (8M tokens x 8)
+    align = {}
+    for name, T, E in (("config3_T4096", 4096, 256), ("config4_T16384", 16384, 128), ("bandwidth_8M_tokens", 8 * 1024 * 1024, 256)):
+        ids = torch.randint(0, E, (T, 8), device=dev, dtype=torch.int32, generator=gen)
+        ms = graph_time(lambda: ops.moe_align_block_size(ids, 128, E), iters=5)
+        post = int(ops.moe_align_block_size(ids, 128, E)[2].item())
+        nbytes = 4 * (ids.numel() + post + post // 128 + 1)
+        align[name] = {"ids": ids.numel(), "experts": E, "us": ms * 1e3, "gbs": nbytes / ms / 1e6,
+                       "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+        del ids
+    out["moe_align_block_size"] = align
+    return {"hbm_kernels": {"unit": "us, GB/s of algorithmic bytes, fraction of MEASURED_PEAKS hbm_gbs", "kernels": out}}
+
+
 def run(sections, args, ctx, peaks):
     out = {}
     rank, world, dev = ctx
     if "sweep" in sections and world == 1:
         out.update(gemm_sweep(args, ctx, peaks))
+        torch.cuda.empty_cache()
+    if "hbm" in sections and world == 1:
+        out.update(hbm_kernels(args, ctx, peaks))
         torch.cuda.empty_cache()
     if "tp" in sections:
         out.update(tp_layer(args, ctx, peaks))

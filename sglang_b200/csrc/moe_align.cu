@@ -7,11 +7,12 @@
 // permutation inside each expert segment; this order is one of its valid outputs and is the
 // order of the reference's CPU implementation and test oracle).
 //
-// The ids are cut into chunks of kChunk consecutive entries, one CTA per chunk; inside a CTA
-// each of the 32 warps owns 256 consecutive entries and walks them 32 at a time.  Rank of an
+// The ids are cut into chunks of consecutive entries, one CTA per chunk (8192 ids, or longer chunks
+// when the input would otherwise need more than two CTAs per SM); inside a CTA each of the 32 warps
+// owns one contiguous span of the chunk and walks it 32 ids at a time.  Rank of an
 // entry = (padded start of its bucket) + (entries of that bucket in earlier chunks) + (in
 // earlier warps of the chunk) + (in earlier steps of the warp) + (in lower lanes of the step,
-// from match.any).  numel <= kChunk runs as ONE kernel; larger inputs run histogram ->
+// from one ballot per id bit).  Up to kSingleMax ids run as ONE kernel; larger inputs run histogram ->
 // scan -> scatter over a small global workspace.  No global atomics anywhere.
 #include <mutex>
 
@@ -21,9 +22,9 @@ namespace sglb200 {
 
 constexpr int kAlignThreads = 1024;
 constexpr int kAlignWarps = kAlignThreads / 32;
-constexpr int kStepsPerWarp = 8;
-constexpr int kWarpSpan = 32 * kStepsPerWarp;      // 256 ids per warp
-constexpr int kChunk = kAlignWarps * kWarpSpan;    // 8192 ids per CTA
+constexpr int kChunk = kAlignWarps * 256;          // 8192 ids per CTA: the shortest chunk of the multi-CTA path
+constexpr int64_t kSingleMax = 8192;               // up to here one CTA sorts everything in one launch (measured cross-over)
+constexpr int kMaxChunks = 296;                    // about two CTAs per SM; longer inputs get longer chunks
 
 __device__ __forceinline__ int warp_incl_scan(int v) {
   const int lane = threadIdx.x & 31;
@@ -35,18 +36,35 @@ __device__ __forceinline__ int warp_incl_scan(int v) {
   return v;
 }
 
+// Lanes of the warp holding the same key, from one ballot per key bit (match.any iterates over the distinct
+// values of the warp, about 30 of them here, and is several times slower).
+__device__ __forceinline__ unsigned peers_of(int key, int nbits) {
+  unsigned peers = 0xffffffffu;
+  for (int k = 0; k < nbits; ++k) {
+    const unsigned set = __ballot_sync(0xffffffffu, (key >> k) & 1);
+    peers &= ((key >> k) & 1) ? set : ~set;
+  }
+  return peers;
+}
+
+constexpr int kBatch = 8;  // steps whose id loads are issued together: hides the load latency of a long span
+
 // Per-warp bucket counts of the chunk [chunk_begin, chunk_end) into wc[warp][B] (smem, zeroed by caller).
 __device__ __forceinline__ void count_chunk(const int32_t* __restrict__ ids, int64_t chunk_begin, int64_t chunk_end,
-                                            int B, int* wc) {
+                                            int span, int B, int* wc) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t seg = chunk_begin + (int64_t)warp * kWarpSpan;
+  const int64_t seg = chunk_begin + (int64_t)warp * span;
+  const int64_t seg_end = seg + span < chunk_end ? seg + span : chunk_end;
+  for (int64_t s0 = seg; s0 < seg_end; s0 += 32 * kBatch) {
+    int v[kBatch];
 #pragma unroll
-  for (int s = 0; s < kStepsPerWarp; ++s) {
-    const int64_t i = seg + s * 32 + lane;
-    if (i < chunk_end) {
-      const int b = ids[i] + 1;
-      if (b >= 0 && b < B) atomicAdd(&wc[warp * B + b], 1);  // shared-memory atomic, contended only inside the warp
+    for (int j = 0; j < kBatch; ++j) {
+      const int64_t i = s0 + j * 32 + lane;
+      v[j] = i < seg_end ? ids[i] + 1 : -1;
     }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      if (v[j] >= 0 && v[j] < B) atomicAdd(&wc[warp * B + v[j]], 1);  // shared-memory atomic, contended only inside the warp
   }
 }
 
@@ -91,29 +109,36 @@ __device__ __forceinline__ void padded_prefix(int B, int block_size, const int* 
 
 // Writes sorted_token_ids for the chunk.  base[b] = padded start of bucket b + entries in earlier chunks.
 __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ ids, int64_t chunk_begin, int64_t chunk_end,
-                                              int B, int* wc, const int* base, int32_t* __restrict__ sorted) {
+                                              int span, int B, int* wc, const int* base, int32_t* __restrict__ sorted) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t seg = chunk_begin + (int64_t)warp * kWarpSpan;
-  if (seg >= chunk_end) return;  // whole warp past the end
-#pragma unroll 1
-  for (int s = 0; s < kStepsPerWarp; ++s) {
-    const int64_t i = seg + s * 32 + lane;
-    int b = -1;
-    if (i < chunk_end) {
-      b = ids[i] + 1;
-      if (b < 0 || b >= B) b = -1;
+  const int64_t seg = chunk_begin + (int64_t)warp * span;
+  const int64_t seg_end = seg + span < chunk_end ? seg + span : chunk_end;
+  const int nbits = 32 - __clz(B + 31);  // keys run up to B + 31
+  for (int64_t s0 = seg; s0 < seg_end; s0 += 32 * kBatch) {  // uniform over the warp
+    int v[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int64_t i = s0 + j * 32 + lane;
+      int b = i < seg_end ? ids[i] + 1 : -1;
+      if (b >= B) b = -1;
+      v[j] = b;
     }
-    const int key = b >= 0 ? b : B + lane;  // invalid lanes match nobody
-    const unsigned peers = __match_any_sync(0xffffffffu, key);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    int start = 0;
-    if (b >= 0) start = wc[warp * B + b];
-    __syncwarp();
-    if (b >= 0) {
-      sorted[(int64_t)base[b] + start + rank] = (int32_t)i;
-      if (lane == 31 - __clz(peers)) wc[warp * B + b] = start + __popc(peers);
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (s0 + j * 32 >= seg_end) break;  // uniform
+      const int b = v[j];
+      const int key = b >= 0 ? b : B + lane;  // invalid lanes match nobody
+      const unsigned peers = peers_of(key, nbits);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      int start = 0;
+      if (b >= 0) start = wc[warp * B + b];
+      __syncwarp();
+      if (b >= 0) {
+        sorted[(int64_t)base[b] + start + rank] = (int32_t)(s0 + j * 32 + lane);
+        if (lane == 31 - __clz(peers)) wc[warp * B + b] = start + __popc(peers);
+      }
+      __syncwarp();
     }
-    __syncwarp();
   }
 }
 
@@ -142,7 +167,7 @@ __device__ __forceinline__ void fill_meta(int B, int block_size, int64_t numel, 
 
 // ---- numel <= kChunk: everything in one CTA -------------------------------------------------
 __global__ void __launch_bounds__(kAlignThreads)
-    moe_align_single_kernel(const int32_t* __restrict__ ids, int64_t numel, int B, int block_size,
+    moe_align_single_kernel(const int32_t* __restrict__ ids, int64_t numel, int span, int B, int block_size,
                             int32_t* __restrict__ sorted, int32_t* __restrict__ expert_ids,
                             int32_t* __restrict__ post_pad, int32_t* __restrict__ cumsum, bool pad_sorted) {
   extern __shared__ int smem[];
@@ -152,7 +177,7 @@ __global__ void __launch_bounds__(kAlignThreads)
   int* scratch = prefix + B + 1;        // [33]
   for (int i = threadIdx.x; i < kAlignWarps * B; i += kAlignThreads) wc[i] = 0;
   __syncthreads();
-  count_chunk(ids, 0, numel, B, wc);
+  count_chunk(ids, 0, numel, span, B, wc);
   __syncthreads();
   scan_over_warps(B, wc, tot);
   __syncthreads();
@@ -160,20 +185,22 @@ __global__ void __launch_bounds__(kAlignThreads)
   for (int b = threadIdx.x; b <= B; b += kAlignThreads) cumsum[b] = prefix[b];
   if (threadIdx.x == 0) *post_pad = prefix[B];
   fill_meta(B, block_size, numel, prefix, tot, expert_ids, sorted, pad_sorted, 0, 1);
-  scatter_chunk(ids, 0, numel, B, wc, prefix, sorted);
+  scatter_chunk(ids, 0, numel, span, B, wc, prefix, sorted);
 }
 
 // ---- numel > kChunk: histogram per chunk -> scan over chunks -> scatter ----------------------
 __global__ void __launch_bounds__(kAlignThreads)
-    moe_align_hist_kernel(const int32_t* __restrict__ ids, int64_t numel, int B, int* __restrict__ chunk_hist) {
+    moe_align_hist_kernel(const int32_t* __restrict__ ids, int64_t numel, int span, int B,
+                          int* __restrict__ chunk_hist) {
   extern __shared__ int smem[];
   int* wc = smem;
   int* tot = wc + kAlignWarps * B;
   for (int i = threadIdx.x; i < kAlignWarps * B; i += kAlignThreads) wc[i] = 0;
   __syncthreads();
-  const int64_t begin = (int64_t)blockIdx.x * kChunk;
-  const int64_t end = begin + kChunk < numel ? begin + kChunk : numel;
-  count_chunk(ids, begin, end, B, wc);
+  const int64_t chunk_len = (int64_t)span * kAlignWarps;
+  const int64_t begin = (int64_t)blockIdx.x * chunk_len;
+  const int64_t end = begin + chunk_len < numel ? begin + chunk_len : numel;
+  count_chunk(ids, begin, end, span, B, wc);
   __syncthreads();
   scan_over_warps(B, wc, tot);
   __syncthreads();
@@ -198,7 +225,7 @@ __global__ void __launch_bounds__(kAlignThreads)
 }
 
 __global__ void __launch_bounds__(kAlignThreads)
-    moe_align_scatter_kernel(const int32_t* __restrict__ ids, int64_t numel, int B, int block_size,
+    moe_align_scatter_kernel(const int32_t* __restrict__ ids, int64_t numel, int span, int B, int block_size,
                              const int* __restrict__ chunk_hist, const int* __restrict__ totals,
                              int32_t* __restrict__ sorted, int32_t* __restrict__ expert_ids,
                              int32_t* __restrict__ post_pad, int32_t* __restrict__ cumsum, bool pad_sorted) {
@@ -219,13 +246,31 @@ __global__ void __launch_bounds__(kAlignThreads)
   }
   fill_meta(B, block_size, numel, prefix, tot, expert_ids, sorted, pad_sorted, blockIdx.x, gridDim.x);
   __syncthreads();  // fill_meta is done with tot[] before it is reused below
-  const int64_t begin = (int64_t)blockIdx.x * kChunk;
-  const int64_t end = begin + kChunk < numel ? begin + kChunk : numel;
-  count_chunk(ids, begin, end, B, wc);
+  const int64_t chunk_len = (int64_t)span * kAlignWarps;
+  const int64_t begin = (int64_t)blockIdx.x * chunk_len;
+  const int64_t end = begin + chunk_len < numel ? begin + chunk_len : numel;
+  count_chunk(ids, begin, end, span, B, wc);
   __syncthreads();
   scan_over_warps(B, wc, tot);
   __syncthreads();
-  scatter_chunk(ids, begin, end, B, wc, base, sorted);
+  scatter_chunk(ids, begin, end, span, B, wc, base, sorted);
+}
+
+// How the ids are cut: number of chunks (CTAs) and ids per warp (a multiple of 32).
+static void align_plan(int64_t numel, int64_t* chunks, int* span) {
+  if (numel <= kSingleMax) {
+    *chunks = 1;
+    const int64_t per_warp = (numel + kAlignWarps - 1) / kAlignWarps;
+    *span = (int)((per_warp + 31) / 32 * 32);
+    if (*span == 0) *span = 32;
+    return;
+  }
+  int64_t c = (numel + kChunk - 1) / kChunk;
+  if (c > kMaxChunks) c = kMaxChunks;
+  int64_t chunk_len = (numel + c - 1) / c;
+  chunk_len = (chunk_len + 1023) / 1024 * 1024;  // 32 warps x a multiple of 32 ids
+  *span = (int)(chunk_len / kAlignWarps);
+  *chunks = (numel + chunk_len - 1) / chunk_len;
 }
 
 static size_t align_smem_bytes(int B) { return sizeof(int) * ((size_t)kAlignWarps * B + 3 * (size_t)B + 1 + 33 + 8); }
@@ -235,8 +280,10 @@ static size_t align_smem_bytes(int B) { return sizeof(int) * ((size_t)kAlignWarp
 using namespace sglb200;
 
 extern "C" int64_t sglb200_moe_align_workspace_bytes(int64_t numel, int num_experts) {
-  if (numel <= kChunk) return 0;
-  const int64_t chunks = (numel + kChunk - 1) / kChunk;
+  if (numel <= kSingleMax) return 0;
+  int64_t chunks = 0;
+  int span = 0;
+  align_plan(numel, &chunks, &span);
   return (chunks + 1) * (int64_t)num_experts * (int64_t)sizeof(int);
 }
 
@@ -260,24 +307,26 @@ extern "C" int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t num
     SGLB_CUDA(cudaFuncSetAttribute(moe_align_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     SGLB_CUDA(cudaFuncSetAttribute(moe_align_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   }
-  if (numel <= kChunk) {
-    moe_align_single_kernel<<<1, kAlignThreads, smem, st>>>(topk_ids, numel, B, block_size, sorted_token_ids, expert_ids,
+  int64_t chunks = 0;
+  int span = 0;
+  align_plan(numel, &chunks, &span);
+  if (chunks == 1) {
+    moe_align_single_kernel<<<1, kAlignThreads, smem, st>>>(topk_ids, numel, span, B, block_size, sorted_token_ids, expert_ids,
                                                             num_tokens_post_pad, cumsum_buffer,
                                                             pad_sorted_token_ids != 0);
     SGLB_CUDA(cudaGetLastError());
     return SGLB200_OK;
   }
-  const int64_t chunks = (numel + kChunk - 1) / kChunk;
   const int64_t need = sglb200_moe_align_workspace_bytes(numel, num_experts);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(SGLB200_E_WORKSPACE, "moe_align: workspace of %lld bytes required, got %lld", (long long)need,
                 (long long)workspace_bytes);
   int* chunk_hist = static_cast<int*>(workspace);
   int* totals = chunk_hist + chunks * B;
-  moe_align_hist_kernel<<<(unsigned)chunks, kAlignThreads, smem, st>>>(topk_ids, numel, B, chunk_hist);
+  moe_align_hist_kernel<<<(unsigned)chunks, kAlignThreads, smem, st>>>(topk_ids, numel, span, B, chunk_hist);
   moe_align_scan_kernel<<<(unsigned)((B + kAlignWarps - 1) / kAlignWarps), kAlignThreads, 0, st>>>(chunk_hist, totals,
                                                                                                    (int)chunks, B);
-  moe_align_scatter_kernel<<<(unsigned)chunks, kAlignThreads, smem, st>>>(topk_ids, numel, B, block_size, chunk_hist,
+  moe_align_scatter_kernel<<<(unsigned)chunks, kAlignThreads, smem, st>>>(topk_ids, numel, span, B, block_size, chunk_hist,
                                                                           totals, sorted_token_ids, expert_ids,
                                                                           num_tokens_post_pad, cumsum_buffer,
                                                                           pad_sorted_token_ids != 0);
@@ -299,7 +348,7 @@ namespace sglb200 {
 
 constexpr int kNoAllocMaxBuckets = 1024;                               // experts + 1
 constexpr int64_t kNoAllocMaxNumel = 1 << 20;                          // flat top-k ids
-constexpr int64_t kNoAllocMaxChunks = kNoAllocMaxNumel / kChunk;       // 128
+constexpr int64_t kNoAllocMaxChunks = kNoAllocMaxNumel / kChunk;       // 128 (align_plan never uses more for 2^20 ids)
 constexpr int64_t kNoAllocScratchInts =
     (kNoAllocMaxBuckets + 1) + (kNoAllocMaxChunks + 1) * kNoAllocMaxBuckets;  // prefix + histograms + totals
 

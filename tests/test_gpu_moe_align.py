@@ -64,6 +64,9 @@ def test_large_input_properties(ops):
     E, block = 256, 128
     ids = rng.integers(0, E, size=(262144, 8)).astype(np.int32)
     _check(ops, ids, block, E)
+    # 3.2M ids with filtered entries: chunks longer than 8192 ids (more than two CTAs per SM otherwise)
+    ids = rng.integers(-1, E, size=(400000, 8)).astype(np.int32)
+    _check(ops, ids, block, E)
 
 
 def test_sgl_kernel_op_surface(ops):
