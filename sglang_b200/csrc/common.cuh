@@ -68,6 +68,11 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   return r;
 }
 
+// silu(x) = x / (1 + e^-x) in float32 with the hardware exponential and reciprocal.  The result is rounded to
+// bf16/fp16 by every caller, so the few-ulp float32 error of the approximations shows only at rounding ties
+// (the unfused and fused activation kernels share this function and stay bit-identical to each other).
+__device__ __forceinline__ float silu_f32(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 // Four float32 -> four e4m3 codes packed little-endian (a in bits 0-7 ... d in bits 24-31).
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
   uint32_t r;

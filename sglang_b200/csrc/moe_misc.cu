@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(256)
   unpack8<T>(ld_nc_16(row + (int64_t)chunks_per_row * 8 + cc * 8), u);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float act = ElemTraits<T>::to_f32(ElemTraits<T>::from_f32(__fdiv_rn(g[i], 1.0f + expf(-g[i]))));
+    const float act = ElemTraits<T>::to_f32(ElemTraits<T>::from_f32(silu_f32(g[i])));
     h[i] = act * u[i];
   }
   reinterpret_cast<uint4*>(out)[c] = pack8<T>(h);

@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(kQuantThreads)
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       // silu in float32, rounded to T, times `up` rounded to T: the reference's two rounding points
-      const float act = ElemTraits<T>::to_f32(ElemTraits<T>::from_f32(__fdiv_rn(g[i], 1.0f + expf(-g[i]))));
+      const float act = ElemTraits<T>::to_f32(ElemTraits<T>::from_f32(silu_f32(g[i])));
       h[i] = ElemTraits<T>::to_f32(ElemTraits<T>::from_f32(act * up[i]));
       amax = fmaxf(amax, fabsf(h[i]));
     }
