@@ -36,14 +36,17 @@ namespace sglb200 {
 constexpr int BM = 128, BN = 192, BK = 128;
 constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 constexpr int kStages = 5;
-constexpr int kAccBufs = 2;
-constexpr int kAccStride = 256;           // TMEM columns between the two accumulator buffers
+constexpr int kSub = 1;                   // column halves of a slab, each handed over through its own TMEM buffer
+constexpr int kSubN = BN / kSub;          // N of one tcgen05.mma
 constexpr int kTmemCols = 512;
+constexpr int kAccBufs = 2 * kSub;        // TMEM accumulator buffers in flight
+constexpr int kAccStride = kTmemCols / kAccBufs;  // TMEM columns between buffers
 constexpr int kGemmThreads = 512;         // warp 0 TMA, warp 1 MMA + TMEM owner, warps 4-15 promotion + epilogue
 constexpr int kEpiWarp0 = 4;
 constexpr int kEpiWarps = 12;
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kEpiCols = BN / (kEpiWarps / 4);  // 64 columns per warp
+constexpr int kEpiCols = kSubN / (kEpiWarps / 4);  // columns of a buffer owned by one warp
+static_assert(kEpiCols % 32 == 0 && (kAccBufs & (kAccBufs - 1)) == 0 && kSubN <= kAccStride, "accumulator layout");
 constexpr int kScaleChunk = 12;                 // slabs of activation scales staged per shared-memory buffer
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 constexpr uint32_t kTileBytesB = BN * BK;
@@ -215,7 +218,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (ptx::elect_one()) {
-      constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
+      constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, kSubN);
       // Operand descriptor (K-major, 128-byte swizzle): low word = address/16 | LBO(1) << 16, high word =
       // SBO(1024/16) | version 1 (bit 46) | layout SWIZZLE_128B (2 at bit 61).  Only the low word changes.
       constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -232,22 +235,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
           if (p.expert_ids[m_tile] < 0) continue;
         }
-        for (int kb = kb_begin; kb < kb_stop; ++kb, ++it) {
-          const uint32_t buf = it & (kAccBufs - 1), aph = (it / kAccBufs) & 1u;
-          if (!ptx::mbar_wait_lean(bar_tempty0 + buf * 8, aph ^ 1u, abort_flag)) { alive = false; break; }
+        for (int kb = kb_begin; kb < kb_stop; ++kb) {
           if (!ptx::mbar_wait_lean(bar_full0 + s * 8, ph, abort_flag)) { alive = false; break; }
-          ptx::tc_fence_after();
           const uint32_t a_lo = desc_lo0 + s * (kStageBytes >> 4);
-          const uint32_t b_lo = a_lo + (kTileBytesA >> 4);
-          const uint32_t d_tmem = tmem_base + buf * kAccStride;
 #pragma unroll
-          for (int k = 0; k < BK / 32; ++k) {
-            // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
-            ptx::mma_f8f6f4(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi), idesc,
-                            k > 0 ? 1u : 0u);
+          for (int h = 0; h < kSub; ++h, ++it) {
+            const uint32_t buf = it & (kAccBufs - 1), aph = (it / kAccBufs) & 1u;
+            if (!ptx::mbar_wait_lean(bar_tempty0 + buf * 8, aph ^ 1u, abort_flag)) { alive = false; break; }
+            ptx::tc_fence_after();
+            // rows h*kSubN.. of the weight tile: whole 8-row swizzle atoms, so only the start address moves
+            const uint32_t b_lo = a_lo + ((kTileBytesA + h * kSubN * BK) >> 4);
+            const uint32_t d_tmem = tmem_base + buf * kAccStride;
+#pragma unroll
+            for (int k = 0; k < BK / 32; ++k) {
+              // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
+              ptx::mma_f8f6f4(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi),
+                              idesc, k > 0 ? 1u : 0u);
+            }
+            ptx::mma_commit(bar_tfull0 + buf * 8);
           }
+          if (!alive) break;
           ptx::mma_commit(bar_empty0 + s * 8);
-          ptx::mma_commit(bar_tfull0 + buf * 8);
           if (++s == (uint32_t)kStages) {
             s = 0;
             ph ^= 1u;
@@ -260,7 +268,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // A thread that sees the abort flag keeps walking the same loops (without waiting or touching TMEM) so
     // that the named barrier below always collects all kEpiThreads arrivals.
     const int q = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int cgrp = (warp - kEpiWarp0) >> 2;   // which 64 of the 192 columns
+    const int cgrp = (warp - kEpiWarp0) >> 2;   // which kEpiCols of every buffer's kSubN columns
     const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
     const int row_in_tile = q * 32 + lane;
     const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
@@ -273,16 +281,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int m_tile, n_tile;
       tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
       const int64_t row = (int64_t)m_tile * BM + row_in_tile;
-      const int n0 = n_tile * BN + cgrp * kEpiCols;
+      // this warp's columns: kEpiCols starting at n_first + h * kSubN for each half h
+      const int n_first = n_tile * BN + cgrp * kEpiCols;
       int e = 0;
       if (kGrouped) e = p.expert_ids[m_tile];
-      float acc[kEpiCols];
+      float acc[kSub][kEpiCols];
 #pragma unroll
-      for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
+      for (int h = 0; h < kSub; ++h)
+#pragma unroll
+        for (int j = 0; j < kEpiCols; ++j) acc[h][j] = 0.f;
       if (e >= 0) {
         // a column group wholly past N still takes part in every hand-shake; its scale index is clamped
-        const int nb = min(n0 / kScaleBlockN, p.nb_total - 1);
-        const int blk_in_tile = nb - min(n_tile * BN / kScaleBlockN, p.nb_total - 1);  // 0 or 1
+        const int nb_tile = min(n_tile * BN / kScaleBlockN, p.nb_total - 1);
+        int blk_in_tile[kSub];  // 0 or 1: kEpiCols-wide groups never straddle a 128-wide scale block
+#pragma unroll
+        for (int h = 0; h < kSub; ++h)
+          blk_in_tile[h] = min((n_first + h * kSubN) / kScaleBlockN, p.nb_total - 1) - nb_tile;
         const int num_chunks = (kb_stop - kb_begin + kScaleChunk - 1) / kScaleChunk;
         // this thread's share of a chunk of activation scales: 4 values
         //   vector form : row ep_tid/3, slabs 4*(ep_tid%3) .. +3      (one 128-bit load)
@@ -329,37 +343,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (c + 1 < num_chunks) fetch_scales(c + 1);  // in flight while this chunk is promoted
           const int kb_end = min(kb_stop, kb_begin + (c + 1) * kScaleChunk);
           const int kb_first = kb_begin + c * kScaleChunk;
-          for (int kb = kb_first; kb < kb_end; ++kb, ++it) {
-            const float scale = ctl->a_scale[c & 1][kb - kb_first][row_in_tile] * ctl->b_scale[c & 1][blk_in_tile][kb - kb_first];
-            const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
-            if (alive && !ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) alive = false;
-            alive = __all_sync(0xffffffffu, alive);  // the warp-wide tcgen05.ld below needs a uniform decision
-            if (alive) {
-              ptx::tc_fence_after();
-              const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kAccStride + cgrp * kEpiCols;
-              // four 16-column pieces through two register sets: the load of piece i+1 is in flight while
-              // piece i is multiplied in (tcgen05.wait::ld waits for every outstanding load of the thread,
-              // so the next load is issued right after the wait)
-              uint32_t ra[16], rb[16];
-              ptx::tmem_ld_32x16(taddr, ra);
-              ptx::tmem_ld_wait();
-              ptx::tmem_ld_32x16(taddr + 16, rb);
+          for (int kb = kb_first; kb < kb_end; ++kb) {
+            const float a_scale = ctl->a_scale[c & 1][kb - kb_first][row_in_tile];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) acc[j] = fmaf(__uint_as_float(ra[j]), scale, acc[j]);
-              ptx::tmem_ld_wait();
-              ptx::tmem_ld_32x16(taddr + 32, ra);
+            for (int h = 0; h < kSub; ++h, ++it) {
+              const float scale = a_scale * ctl->b_scale[c & 1][blk_in_tile[h]][kb - kb_first];
+              const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
+              if (alive && !ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) alive = false;
+              alive = __all_sync(0xffffffffu, alive);  // the warp-wide tcgen05.ld below needs a uniform decision
+              if (alive) {
+                ptx::tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kAccStride + cgrp * kEpiCols;
+                // 32 columns per tcgen05.ld: a warp's time per slab is (pieces x TMEM round trip) + the FMAs, and
+                // that time sits on the hand-off chain MMA -> commit -> promotion -> release that bounds the
+                // kernel, so fewer, wider loads beat 16-column loads double-buffered through two register sets
+                // (tcgen05.wait::ld waits for every outstanding load of the thread, which defeats that overlap).
+                // The buffer goes back to the MMA thread as soon as the last piece is in registers.
+                constexpr int kPieces = kEpiCols / 32;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) acc[16 + j] = fmaf(__uint_as_float(rb[j]), scale, acc[16 + j]);
-              ptx::tmem_ld_wait();
-              ptx::tmem_ld_32x16(taddr + 48, rb);
+                for (int i = 0; i < kPieces; ++i) {
+                  uint32_t r[32];
+                  ptx::tmem_ld_32x32(taddr + 32 * i, r);
+                  ptx::tmem_ld_wait();
+                  if (i + 1 == kPieces) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
+                  }
 #pragma unroll
-              for (int j = 0; j < 16; ++j) acc[32 + j] = fmaf(__uint_as_float(ra[j]), scale, acc[32 + j]);
-              ptx::tmem_ld_wait();
-              ptx::tc_fence_before();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
-#pragma unroll
-              for (int j = 0; j < 16; ++j) acc[48 + j] = fmaf(__uint_as_float(rb[j]), scale, acc[48 + j]);
+                  for (int j = 0; j < 32; ++j)
+                    acc[h][32 * i + j] = fmaf(__uint_as_float(r[j]), scale, acc[h][32 * i + j]);
+                }
+              }
             }
           }
           if (c + 1 < num_chunks) stash_scales((c + 1) & 1);
@@ -370,15 +385,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // ---- store ----
       if (!kGrouped && splits > 1) {
         // split-K: this unit's float32 partial sums; a second kernel adds the units of a tile in a fixed order
-        if (row < rows && n0 < p.N) {
-          float* dst = p.partial + ((int64_t)sp * p.M + row) * p.N + n0;
 #pragma unroll
-          for (int j = 0; j < kEpiCols / 4; ++j) {
-            const int n = n0 + j * 4;
-            if (n + 4 <= p.N)
-              *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-            else
-              for (int i = 0; i < 4 && n + i < p.N; ++i) dst[j * 4 + i] = acc[4 * j + i];
+        for (int h = 0; h < kSub; ++h) {
+          const int n0 = n_first + h * kSubN;
+          if (row < rows && n0 < p.N) {
+            float* dst = p.partial + ((int64_t)sp * p.M + row) * p.N + n0;
+#pragma unroll
+            for (int j = 0; j < kEpiCols / 4; ++j) {
+              const int n = n0 + j * 4;
+              if (n + 4 <= p.N)
+                *reinterpret_cast<float4*>(dst + j * 4) =
+                    make_float4(acc[h][4 * j], acc[h][4 * j + 1], acc[h][4 * j + 2], acc[h][4 * j + 3]);
+              else
+                for (int i = 0; i < 4 && n + i < p.N; ++i) dst[j * 4 + i] = acc[h][4 * j + i];
+            }
           }
         }
         continue;
@@ -392,14 +412,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (store_ok && p.row_weights != nullptr) {
           const float w = __ldg(p.row_weights + id);
 #pragma unroll
-          for (int j = 0; j < kEpiCols; ++j) acc[j] *= w;
+          for (int h = 0; h < kSub; ++h)
+#pragma unroll
+            for (int j = 0; j < kEpiCols; ++j) acc[h][j] *= w;
         }
       }
-      if (store_ok && n0 < p.N) {
-        if (p.out_fp16) {
-          store_row_chunk<__half>(static_cast<__half*>(p.C) + out_row * p.N + n0, acc, p.bias, n0, p.N);
-        } else {
-          store_row_chunk<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p.C) + out_row * p.N + n0, acc, p.bias, n0, p.N);
+#pragma unroll
+      for (int h = 0; h < kSub; ++h) {
+        const int n0 = n_first + h * kSubN;
+        if (store_ok && n0 < p.N) {
+          if (p.out_fp16) {
+            store_row_chunk<__half>(static_cast<__half*>(p.C) + out_row * p.N + n0, acc[h], p.bias, n0, p.N);
+          } else {
+            store_row_chunk<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p.C) + out_row * p.N + n0, acc[h], p.bias, n0,
+                                           p.N);
+          }
         }
       }
     }
