@@ -33,24 +33,39 @@
 
 namespace sglb200 {
 
-constexpr int BM = 128, BN = 192, BK = 128;
+#ifndef SGLB_BN
+#define SGLB_BN 192
+#endif
+constexpr int BM = 128, BN = SGLB_BN, BK = 128;
 constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
-constexpr int kStages = 5;
-constexpr int kSub = 1;                   // column halves of a slab, each handed over through its own TMEM buffer
-constexpr int kSubN = BN / kSub;          // N of one tcgen05.mma
+#ifndef SGLB_STAGES
+#define SGLB_STAGES 4
+#endif
+#ifndef SGLB_EPI_WARPS
+#define SGLB_EPI_WARPS 12
+#endif
+#ifndef SGLB_DUAL
+#define SGLB_DUAL 0
+#endif
+constexpr int kStages = SGLB_STAGES;
 constexpr int kTmemCols = 512;
-constexpr int kAccBufs = 2 * kSub;        // TMEM accumulator buffers in flight
-constexpr int kAccStride = kTmemCols / kAccBufs;  // TMEM columns between buffers
-constexpr int kGemmThreads = 512;         // warp 0 TMA, warp 1 MMA + TMEM owner, warps 4-15 promotion + epilogue
+constexpr int kAccBufs = kTmemCols / BN;  // TMEM accumulator buffers in flight (3 of 160 columns)
+constexpr int kAccStride = BN;            // TMEM columns between buffers
+constexpr int kGemmThreads = 128 + SGLB_EPI_WARPS * 32;  // warp 0 TMA, warp 1 MMA + TMEM owner, warps 4.. promotion + epilogue
 constexpr int kEpiWarp0 = 4;
-constexpr int kEpiWarps = 12;
+constexpr int kEpiWarps = SGLB_EPI_WARPS;
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kEpiCols = kSubN / (kEpiWarps / 4);  // columns of a buffer owned by one warp
-static_assert(kEpiCols % 32 == 0 && (kAccBufs & (kAccBufs - 1)) == 0 && kSubN <= kAccStride, "accumulator layout");
-constexpr int kScaleChunk = 12;                 // slabs of activation scales staged per shared-memory buffer
+constexpr int kEpiCols = 64;              // columns of a buffer owned by one warp (the last group may own fewer)
+static_assert(BN % 32 == 0 && BN <= (kEpiWarps / 4) * kEpiCols && BN > (kEpiWarps / 4 - 1) * kEpiCols &&
+                  kAccBufs * kAccStride <= kTmemCols && BN <= 256,
+              "accumulator layout");
+constexpr int kScaleChunk = kEpiThreads / 32;                 // slabs of activation scales staged per shared-memory buffer
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 constexpr uint32_t kTileBytesB = BN * BK;
 constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
+// Output staging for the TMA store: per column group a [128 rows][64 columns] 2-byte tile in the 128-byte swizzle
+constexpr uint32_t kOutGroupBytes = BM * kEpiCols * 2;
+constexpr uint32_t kOutBytes = (kEpiWarps / 4) * kOutGroupBytes;
 constexpr int kGroupM = 8;  // m-tiles sharing a sweep over n: keeps the weight tiles of a wave L2-resident
 
 __device__ int g_gemm_status = 0;  // 0 ok, 1 = a pipeline wait expired
@@ -76,6 +91,7 @@ struct GemmParams {
   int tiles_n;                 // ceil(N/BN)
   int scatter;
   int out_fp16;
+  int tma_out;                 // rows of C are written with TMA tile stores (map_c is valid)
 };
 
 struct SharedCtl {
@@ -105,8 +121,8 @@ __device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int&
 }
 
 template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, const void* bias_v, int n0, int64_t N) {
-  // kEpiCols consecutive columns starting at n0, 8 per 16-byte store
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, const void* bias_v, int n0, int N) {
+  // up to kEpiCols consecutive columns starting at n0 and ending before N, 8 per 16-byte store
 #pragma unroll
   for (int j = 0; j < kEpiCols / 8; ++j) {
     const int n = n0 + j * 8;
@@ -138,11 +154,12 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, const
 template <bool kGrouped>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     fp8_blockscale_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                               const GemmParams p) {
+                               const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + kStages * kStageBytes);
+  uint8_t* out_stage = tiles + kStages * kStageBytes;
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(out_stage + kOutBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &ctl->abort_flag;
 
@@ -218,14 +235,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (ptx::elect_one()) {
-      constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, kSubN);
+      constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
       // Operand descriptor (K-major, 128-byte swizzle): low word = address/16 | LBO(1) << 16, high word =
       // SBO(1024/16) | version 1 (bit 46) | layout SWIZZLE_128B (2 at bit 61).  Only the low word changes.
       constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
       const uint32_t desc_lo0 = ((ptx::smem_u32(tiles) & 0x3ffffu) >> 4) | (1u << 16);
       const uint32_t bar_full0 = ptx::smem_u32(&ctl->full[0]), bar_empty0 = ptx::smem_u32(&ctl->empty[0]);
       const uint32_t bar_tfull0 = ptx::smem_u32(&ctl->tmem_full[0]), bar_tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
-      uint32_t it = 0, s = 0, ph = 0;
+      uint32_t s = 0, ph = 0, buf = 0, aph = 0;
       bool alive = true;
       for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
         const int t = u / splits, sp = u - t * splits;
@@ -236,29 +253,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (p.expert_ids[m_tile] < 0) continue;
         }
         for (int kb = kb_begin; kb < kb_stop; ++kb) {
+          if (!ptx::mbar_wait_lean(bar_tempty0 + buf * 8, aph ^ 1u, abort_flag)) { alive = false; break; }
           if (!ptx::mbar_wait_lean(bar_full0 + s * 8, ph, abort_flag)) { alive = false; break; }
+          ptx::tc_fence_after();
           const uint32_t a_lo = desc_lo0 + s * (kStageBytes >> 4);
+          const uint32_t b_lo = a_lo + (kTileBytesA >> 4);
+          const uint32_t d_tmem = tmem_base + buf * kAccStride;
 #pragma unroll
-          for (int h = 0; h < kSub; ++h, ++it) {
-            const uint32_t buf = it & (kAccBufs - 1), aph = (it / kAccBufs) & 1u;
-            if (!ptx::mbar_wait_lean(bar_tempty0 + buf * 8, aph ^ 1u, abort_flag)) { alive = false; break; }
-            ptx::tc_fence_after();
-            // rows h*kSubN.. of the weight tile: whole 8-row swizzle atoms, so only the start address moves
-            const uint32_t b_lo = a_lo + ((kTileBytesA + h * kSubN * BK) >> 4);
-            const uint32_t d_tmem = tmem_base + buf * kAccStride;
-#pragma unroll
-            for (int k = 0; k < BK / 32; ++k) {
-              // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
-              ptx::mma_f8f6f4(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi),
-                              idesc, k > 0 ? 1u : 0u);
-            }
-            ptx::mma_commit(bar_tfull0 + buf * 8);
+          for (int k = 0; k < BK / 32; ++k) {
+            // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
+            ptx::mma_f8f6f4(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi), idesc,
+                            k > 0 ? 1u : 0u);
           }
-          if (!alive) break;
           ptx::mma_commit(bar_empty0 + s * 8);
+          ptx::mma_commit(bar_tfull0 + buf * 8);
           if (++s == (uint32_t)kStages) {
             s = 0;
             ph ^= 1u;
+          }
+          if (++buf == (uint32_t)kAccBufs) {
+            buf = 0;
+            aph ^= 1u;
           }
         }
       }
@@ -268,12 +283,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // A thread that sees the abort flag keeps walking the same loops (without waiting or touching TMEM) so
     // that the named barrier below always collects all kEpiThreads arrivals.
     const int q = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int cgrp = (warp - kEpiWarp0) >> 2;   // which kEpiCols of every buffer's kSubN columns
+    const int cgrp = (warp - kEpiWarp0) >> 2;   // column group: columns cgrp*64 .. of the tile (the last group is narrower)
+    constexpr int kPiecesMax = kEpiCols / 32;
+    // when the tile width is a multiple of 64 a warp's 64 columns lie in one 128-wide weight block; otherwise
+    // (160-wide tiles) each 32-column piece looks up its own block
+    constexpr int kScalesPerWarp = (BN % kEpiCols == 0) ? 1 : kPiecesMax;
+    const int my_cols = min(kEpiCols, BN - cgrp * kEpiCols);
+    const int my_pieces = my_cols / 32;         // 32-column TMEM loads per slab for this warp
     const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
     const int row_in_tile = q * 32 + lane;
     const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
                             (reinterpret_cast<uintptr_t>(p.a_s) & 15u) == 0;
-    uint32_t it = 0;
+    const uint32_t bar_tfull0 = ptx::smem_u32(&ctl->tmem_full[0]), bar_tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
+    const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + cgrp * kEpiCols;
+    uint32_t buf = 0, aph = 0;
     bool alive = true;
     for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
       const int t = u / splits, sp = u - t * splits;
@@ -281,28 +304,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int m_tile, n_tile;
       tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
       const int64_t row = (int64_t)m_tile * BM + row_in_tile;
-      // this warp's columns: kEpiCols starting at n_first + h * kSubN for each half h
-      const int n_first = n_tile * BN + cgrp * kEpiCols;
+      const int n0 = n_tile * BN + cgrp * kEpiCols;            // first of this warp's columns
+      const int n_end = (int)min((int64_t)n_tile * BN + BN, p.N);  // one past the tile's last valid column
       int e = 0;
       if (kGrouped) e = p.expert_ids[m_tile];
-      float acc[kSub][kEpiCols];
+      float acc[kEpiCols];
 #pragma unroll
-      for (int h = 0; h < kSub; ++h)
-#pragma unroll
-        for (int j = 0; j < kEpiCols; ++j) acc[h][j] = 0.f;
+      for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
       if (e >= 0) {
-        // a column group wholly past N still takes part in every hand-shake; its scale index is clamped
+        // Weight scales: a tile touches at most two 128-wide blocks; 32-column pieces never straddle one.  A
+        // piece wholly past N still takes part in every hand-shake; its block index is clamped.
         const int nb_tile = min(n_tile * BN / kScaleBlockN, p.nb_total - 1);
-        int blk_in_tile[kSub];  // 0 or 1: kEpiCols-wide groups never straddle a 128-wide scale block
+        int blk_of_piece[kPiecesMax];
 #pragma unroll
-        for (int h = 0; h < kSub; ++h)
-          blk_in_tile[h] = min((n_first + h * kSubN) / kScaleBlockN, p.nb_total - 1) - nb_tile;
+        for (int i = 0; i < kPiecesMax; ++i)
+          blk_of_piece[i] = min((n0 + 32 * i) / kScaleBlockN, p.nb_total - 1) - nb_tile;
         const int num_chunks = (kb_stop - kb_begin + kScaleChunk - 1) / kScaleChunk;
         // this thread's share of a chunk of activation scales: 4 values
         //   vector form : row ep_tid/3, slabs 4*(ep_tid%3) .. +3      (one 128-bit load)
         //   generic form: row ep_tid%128, slabs 4*(ep_tid/128) .. +3  (coalesced along rows)
-        const int s_row = vec_scales ? (ep_tid / 3) : (ep_tid & (BM - 1));
-        const int s_kb = vec_scales ? ((ep_tid % 3) << 2) : ((ep_tid >> 7) << 2);
+        const int s_row = vec_scales ? (ep_tid / (kScaleChunk / 4)) : (ep_tid & (BM - 1));
+        const int s_kb = vec_scales ? ((ep_tid % (kScaleChunk / 4)) << 2) : ((ep_tid >> 7) << 2);
         const int64_t g_row = (int64_t)m_tile * BM + s_row;
         float4 sv;
         float bv = 0.f;
@@ -320,8 +342,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               if (kb0 + 3 < kb_total) sv.w = __ldg(src + 3 * p.as_stride_k);
             }
           }
-          // weight-block scales of the chunk (a 192-wide tile touches two 128-row blocks): staged as well, so
-          // that the promotion loop has no global load on its critical path
+          // weight-block scales of the chunk: staged as well, so that the promotion loop has no global load on
+          // its critical path
           if (ep_tid < 2 * kScaleChunk) {
             const int blk = ep_tid / kScaleChunk, kk = ep_tid - blk * kScaleChunk;
             const int kbb = kb_begin + chunk * kScaleChunk + kk;
@@ -329,76 +351,159 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             bv = kbb < kb_total ? __ldg(p.b_s + ((int64_t)e * p.nb_total + nbb) * kb_total + kbb) : 0.f;
           }
         };
-        auto stash_scales = [&](int buf) {
-          if (ep_tid < 2 * kScaleChunk) ctl->b_scale[buf][ep_tid / kScaleChunk][ep_tid % kScaleChunk] = bv;
-          ctl->a_scale[buf][s_kb + 0][s_row] = sv.x;
-          ctl->a_scale[buf][s_kb + 1][s_row] = sv.y;
-          ctl->a_scale[buf][s_kb + 2][s_row] = sv.z;
-          ctl->a_scale[buf][s_kb + 3][s_row] = sv.w;
+        auto stash_scales = [&](int sbuf) {
+          if (ep_tid < 2 * kScaleChunk) ctl->b_scale[sbuf][ep_tid / kScaleChunk][ep_tid % kScaleChunk] = bv;
+          ctl->a_scale[sbuf][s_kb + 0][s_row] = sv.x;
+          ctl->a_scale[sbuf][s_kb + 1][s_row] = sv.y;
+          ctl->a_scale[sbuf][s_kb + 2][s_row] = sv.z;
+          ctl->a_scale[sbuf][s_kb + 3][s_row] = sv.w;
         };
         fetch_scales(0);
         stash_scales(0);
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         for (int c = 0; c < num_chunks; ++c) {
           if (c + 1 < num_chunks) fetch_scales(c + 1);  // in flight while this chunk is promoted
-          const int kb_end = min(kb_stop, kb_begin + (c + 1) * kScaleChunk);
           const int kb_first = kb_begin + c * kScaleChunk;
-          for (int kb = kb_first; kb < kb_end; ++kb) {
-            const float a_scale = ctl->a_scale[c & 1][kb - kb_first][row_in_tile];
+          const int slabs = min(kb_stop, kb_first + kScaleChunk) - kb_first;
+          // The loop below runs once per slab in each of the 12 warps and competes for issue slots with the TMA
+          // and MMA threads, so it is kept to the FMAs plus a few instructions: shared-memory addresses that
+          // step, one probe of the barrier in the common case, no branch around the arrive.
+          uint32_t a_addr = ptx::smem_u32(&ctl->a_scale[c & 1][0][row_in_tile]);
+          uint32_t b_addr[kScalesPerWarp];
 #pragma unroll
-            for (int h = 0; h < kSub; ++h, ++it) {
-              const float scale = a_scale * ctl->b_scale[c & 1][blk_in_tile[h]][kb - kb_first];
-              const uint32_t buf = it % kAccBufs, aph = (it / kAccBufs) & 1u;
-              if (alive && !ptx::mbar_wait(ptx::smem_u32(&ctl->tmem_full[buf]), aph, abort_flag)) alive = false;
-              alive = __all_sync(0xffffffffu, alive);  // the warp-wide tcgen05.ld below needs a uniform decision
-              if (alive) {
-                ptx::tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kAccStride + cgrp * kEpiCols;
-                // 32 columns per tcgen05.ld: a warp's time per slab is (pieces x TMEM round trip) + the FMAs, and
-                // that time sits on the hand-off chain MMA -> commit -> promotion -> release that bounds the
-                // kernel, so fewer, wider loads beat 16-column loads double-buffered through two register sets
-                // (tcgen05.wait::ld waits for every outstanding load of the thread, which defeats that overlap).
-                // The buffer goes back to the MMA thread as soon as the last piece is in registers.
-                constexpr int kPieces = kEpiCols / 32;
+          for (int i = 0; i < kScalesPerWarp; ++i) b_addr[i] = ptx::smem_u32(&ctl->b_scale[c & 1][blk_of_piece[i]][0]);
+          for (int n = 0; n < slabs; ++n) {
+            const float a_scale = ptx::lds_f32(a_addr);
+            a_addr += BM * 4;
+            float scale[kScalesPerWarp];
 #pragma unroll
-                for (int i = 0; i < kPieces; ++i) {
+            for (int i = 0; i < kScalesPerWarp; ++i) {
+              scale[i] = a_scale * ptx::lds_f32(b_addr[i]);
+              b_addr[i] += 4;
+            }
+            if (alive) {
+              bool ok = ptx::mbar_probe_run(bar_tfull0 + buf * 8, aph);
+              if (!__all_sync(0xffffffffu, ok)) {  // rare: a long wait; the warp-wide tcgen05.ld needs a uniform decision
+                ok = ptx::mbar_wait_slow(bar_tfull0 + buf * 8, aph, abort_flag);
+                alive = __all_sync(0xffffffffu, ok);
+              }
+            }
+            if (alive) {
+              ptx::tc_fence_after();
+              const uint32_t taddr = taddr0 + buf * kAccStride;
+              // 32 columns per tcgen05.ld: a warp's time per slab is (pieces x TMEM round trip) + the FMAs, and
+              // that time sits on the hand-off chain MMA -> commit -> promotion -> release that bounds the
+              // kernel, so fewer, wider loads beat 16-column loads double-buffered through two register sets
+              // (tcgen05.wait::ld waits for every outstanding load of the thread, which defeats that overlap).
+              // The buffer goes back to the MMA thread as soon as the last piece is in registers.
+#if SGLB_DUAL
+              static_assert(kPiecesMax == 2, "dual staging");
+              {
+                uint32_t r0[32], r1[32];
+                ptx::tmem_ld_32x32(taddr, r0);
+                if (my_pieces > 1) ptx::tmem_ld_32x32(taddr + 32, r1);
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r0[j]), scale[0], acc[j]);
+                if (my_pieces > 1) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    acc[32 + j] = fmaf(__uint_as_float(r1[j]), scale[kScalesPerWarp > 1 ? 1 : 0], acc[32 + j]);
+                }
+              }
+#else
+#pragma unroll
+              for (int i = 0; i < kPiecesMax; ++i) {
+                if (i < my_pieces) {  // warp-uniform
                   uint32_t r[32];
                   ptx::tmem_ld_32x32(taddr + 32 * i, r);
                   ptx::tmem_ld_wait();
-                  if (i + 1 == kPieces) {
+                  if (i + 1 == my_pieces) {
                     ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
+                    ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
                   }
 #pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    acc[h][32 * i + j] = fmaf(__uint_as_float(r[j]), scale, acc[h][32 * i + j]);
+                  for (int j = 0; j < 32; ++j) acc[32 * i + j] = fmaf(__uint_as_float(r[j]), scale[kScalesPerWarp > 1 ? i : 0], acc[32 * i + j]);
                 }
               }
+#endif
+            }
+            if (++buf == (uint32_t)kAccBufs) {
+              buf = 0;
+              aph ^= 1u;
             }
           }
           if (c + 1 < num_chunks) stash_scales((c + 1) & 1);
           asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         }
       }
-      if (!alive) continue;
       // ---- store ----
+      if (p.tma_out) {
+        // Rows of C are contiguous: round to the output type, park the warp's 32 x 64 block in shared memory
+        // (128-byte rows, 16-byte chunks XOR-swizzled by the row so that the 32 lanes of a store spread over
+        // all banks) and let one thread of the column group hand the 128 x 64 block to the TMA engine, which
+        // clips it to the tensor.  The store drains while the next tile is being promoted; its source is
+        // reclaimed at the next epilogue.
+        const bool issuer = (q == 0 && lane == 0);
+        if (issuer) ptx::tma_store_wait_read();
+        // (a warp whose wait expired still joins both barriers of its column group; only the data movement is skipped)
+        asm volatile("bar.sync %0, 128;" ::"r"(2 + cgrp) : "memory");
+        if (alive && n0 < n_end) {
+          const uint32_t grp = ptx::smem_u32(out_stage) + cgrp * kOutGroupBytes;
+          const uint32_t row_addr = grp + row_in_tile * 128;
+#pragma unroll
+          for (int j = 0; j < kEpiCols / 8; ++j) {
+            float x[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = acc[j * 8 + i];
+            const int n = n0 + j * 8;
+            if (p.bias != nullptr && n + 8 <= n_end) {
+              const uint4 braw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + n));
+              if (p.out_fp16) {
+                const __half* bb = reinterpret_cast<const __half*>(&braw);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] += __half2float(bb[i]);
+              } else {
+                const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&braw);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] += __bfloat162float(bb[i]);
+              }
+            }
+            uint4 raw;
+            if (p.out_fp16) {
+              __half* o = reinterpret_cast<__half*>(&raw);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = __float2half_rn(x[i]);
+            } else {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&raw);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(x[i]);
+            }
+            ptx::sts_128(row_addr + ((j ^ (row_in_tile & 7)) << 4), raw);
+          }
+          ptx::fence_async_smem();
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(2 + cgrp) : "memory");
+        if (issuer && alive && n0 < n_end) {
+          ptx::tma_store_2d(&map_c, ptx::smem_u32(out_stage) + cgrp * kOutGroupBytes, n0, m_tile * BM);
+          ptx::tma_store_commit();
+        }
+        continue;
+      }
+      if (!alive) continue;
       if (!kGrouped && splits > 1) {
         // split-K: this unit's float32 partial sums; a second kernel adds the units of a tile in a fixed order
+        if (row < rows && n0 < n_end) {
+          float* dst = p.partial + ((int64_t)sp * p.M + row) * p.N + n0;
 #pragma unroll
-        for (int h = 0; h < kSub; ++h) {
-          const int n0 = n_first + h * kSubN;
-          if (row < rows && n0 < p.N) {
-            float* dst = p.partial + ((int64_t)sp * p.M + row) * p.N + n0;
-#pragma unroll
-            for (int j = 0; j < kEpiCols / 4; ++j) {
-              const int n = n0 + j * 4;
-              if (n + 4 <= p.N)
-                *reinterpret_cast<float4*>(dst + j * 4) =
-                    make_float4(acc[h][4 * j], acc[h][4 * j + 1], acc[h][4 * j + 2], acc[h][4 * j + 3]);
-              else
-                for (int i = 0; i < 4 && n + i < p.N; ++i) dst[j * 4 + i] = acc[h][4 * j + i];
-            }
+          for (int j = 0; j < kEpiCols / 4; ++j) {
+            const int n = n0 + j * 4;
+            if (n + 4 <= n_end)
+              *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+            else
+              for (int i = 0; i < 4 && n + i < n_end; ++i) dst[j * 4 + i] = acc[4 * j + i];
           }
         }
         continue;
@@ -412,27 +517,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (store_ok && p.row_weights != nullptr) {
           const float w = __ldg(p.row_weights + id);
 #pragma unroll
-          for (int h = 0; h < kSub; ++h)
-#pragma unroll
-            for (int j = 0; j < kEpiCols; ++j) acc[h][j] *= w;
+          for (int j = 0; j < kEpiCols; ++j) acc[j] *= w;
         }
       }
-#pragma unroll
-      for (int h = 0; h < kSub; ++h) {
-        const int n0 = n_first + h * kSubN;
-        if (store_ok && n0 < p.N) {
-          if (p.out_fp16) {
-            store_row_chunk<__half>(static_cast<__half*>(p.C) + out_row * p.N + n0, acc[h], p.bias, n0, p.N);
-          } else {
-            store_row_chunk<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p.C) + out_row * p.N + n0, acc[h], p.bias, n0,
-                                           p.N);
-          }
+      if (store_ok && n0 < n_end) {
+        if (p.out_fp16) {
+          store_row_chunk<__half>(static_cast<__half*>(p.C) + out_row * p.N + n0, acc, p.bias, n0, n_end);
+        } else {
+          store_row_chunk<__nv_bfloat16>(static_cast<__nv_bfloat16*>(p.C) + out_row * p.N + n0, acc, p.bias, n0, n_end);
         }
       }
     }
   }
 
   // ------------------------------ teardown ------------------------------
+  if (warp >= kEpiWarp0 && (warp & 3) == 0 && lane == 0) ptx::tma_store_wait_read();  // sources stay valid until read
   ptx::tc_fence_before();
   __syncthreads();
   if (ctl->abort_flag != 0 && threadIdx.x == 0) {
@@ -564,11 +663,36 @@ static int get_tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2
   return SGLB200_OK;
 }
 
-static size_t gemm_smem_bytes() { return (size_t)kStages * kStageBytes + sizeof(SharedCtl) + 1024; }
+// Output tensor [rows][N] of 2-byte elements, box = 64 columns x 128 rows, 128-byte swizzle (matches the
+// staging layout written by the epilogue).
+static int get_out_map(const void* ptr, uint64_t N, uint64_t rows, int out_fp16, CUtensorMap* out) {
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, N, rows, (uint64_t)out_fp16, 0, 0};
+  auto itc = cache.find(key);
+  if (itc != cache.end()) {
+    *out = itc->second;
+    return SGLB200_OK;
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return fail(SGLB200_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {N, rows};
+  cuuint64_t strides[1] = {N * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kEpiCols, (cuuint32_t)BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, out_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SGLB200_E_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return SGLB200_OK;
+}
+
+static size_t gemm_smem_bytes() { return (size_t)kStages * kStageBytes + kOutBytes + sizeof(SharedCtl) + 1024; }
 
 template <bool kGrouped>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int64_t max_tiles,
-                       cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const GemmParams& p,
+                       int64_t max_tiles, cudaStream_t st) {
   const size_t smem = gemm_smem_bytes();
   static thread_local bool attr_set[64] = {false};  // the opt-in is per function and per device
   int dev = 0;
@@ -580,7 +704,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   }
   const int sms = sm_count();
   const unsigned grid = (unsigned)(max_tiles < sms ? max_tiles : sms);
-  fp8_blockscale_gemm_kernel<kGrouped><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
+  fp8_blockscale_gemm_kernel<kGrouped><<<grid, kGemmThreads, smem, st>>>(ma, mb, mc, p);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }
@@ -638,8 +762,14 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   p.kb_per_split = splits > 1 ? per : p.kb_total;
   p.partial = static_cast<float*>(workspace);
   if (splits > 1) p.bias = nullptr;  // added by the reduction
+  CUtensorMap mc{};
+  p.tma_out = splits == 1;
+  if (p.tma_out) {
+    rc = get_out_map(C, (uint64_t)N, (uint64_t)M, out_dtype, &mc);
+    if (rc) return rc;
+  }
   const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
-  rc = launch_gemm<false>(ma, mb, p, tiles * splits, static_cast<cudaStream_t>(stream));
+  rc = launch_gemm<false>(ma, mb, mc, p, tiles * splits, static_cast<cudaStream_t>(stream));
   if (rc != SGLB200_OK || splits == 1) return rc;
   const int64_t total8 = M * N / 8;
   const unsigned blocks = (unsigned)((total8 + 255) / 256);
@@ -682,6 +812,12 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   p.as_stride_m = p.kb_total, p.as_stride_k = 1;
   p.numel = numel, p.scatter = scatter, p.out_fp16 = out_dtype;
   p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;
+  CUtensorMap mc{};
+  p.tma_out = !scatter;  // sorted-row output is contiguous; the scatter form writes token-major rows one by one
+  if (p.tma_out) {
+    rc = get_out_map(C, (uint64_t)N, (uint64_t)max_rows, out_dtype, &mc);
+    if (rc) return rc;
+  }
   const int64_t tiles = ((max_rows + BM - 1) / BM) * p.tiles_n;
-  return launch_gemm<true>(ma, mb, p, tiles, static_cast<cudaStream_t>(stream));
+  return launch_gemm<true>(ma, mb, mc, p, tiles, static_cast<cudaStream_t>(stream));
 }

@@ -104,6 +104,41 @@ __device__ __forceinline__ bool mbar_wait_lean(uint32_t bar, uint32_t parity, vo
   return mbar_wait_slow(bar, parity, abort_flag);
 }
 
+// A short run of suspending probes as one asm block (probe + branch per iteration, no flag or clock
+// bookkeeping); false if the phase has not completed by then.  Callers fall back to mbar_wait_slow.
+__device__ __forceinline__ bool mbar_probe_run(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n"
+      "PROBE_LOOP:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra PROBE_DONE;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 p, n, 64;\n\t"
+      "@p bra PROBE_LOOP;\n"
+      "PROBE_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Arrive from the threads whose `pred` is set, without a branch around the instruction.
+__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar),
+      "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // Packed pair of float32 operations (sm_100): d.lo = a.lo*b.lo + d.lo, d.hi = a.hi*b.hi + d.hi in one issue slot.
 __device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
   uint64_t r;
@@ -135,6 +170,23 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+
+// ---- TMA tile store (shared memory -> global, clipped to the tensor's extents) ---------------------
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once every committed store of this thread has finished READING shared memory (the source may be
+// overwritten; the global writes complete on their own).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Orders this thread's ordinary shared-memory writes before later reads by the TMA engine.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void sts_128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 // ---- tensor memory ---------------------------------------------------------------------------
