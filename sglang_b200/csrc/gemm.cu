@@ -47,6 +47,9 @@ constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 #ifndef SGLB_DUAL
 #define SGLB_DUAL 0
 #endif
+#ifndef SGLB_FFMA2
+#define SGLB_FFMA2 0
+#endif
 constexpr int kStages = SGLB_STAGES;
 constexpr int kTmemCols = 512;
 constexpr int kAccBufs = kTmemCols / BN;  // TMEM accumulator buffers in flight (3 of 160 columns)
@@ -219,7 +222,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // spends per slab delays the loads, so the loop keeps only 32-bit counters that step
         const int row_a = m_tile * BM, row_b = n_tile * BN;
         for (int k0 = kb_begin * BK; k0 < kb_stop * BK; k0 += BK) {
-          if (!ptx::mbar_wait_lean(bar_empty0 + s * 8, ph ^ 1u, abort_flag)) { alive = false; break; }
+          if (!ptx::mbar_wait_quiet(bar_empty0 + s * 8, ph ^ 1u)) { *abort_flag = 1; alive = false; break; }
           const uint32_t bar = bar_full0 + s * 8;
           ptx::mbar_arrive_expect_tx(bar, kStageBytes);
           const uint32_t dst_a = tiles0 + s * kStageBytes;
@@ -253,8 +256,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (p.expert_ids[m_tile] < 0) continue;
         }
         for (int kb = kb_begin; kb < kb_stop; ++kb) {
-          if (!ptx::mbar_wait_lean(bar_tempty0 + buf * 8, aph ^ 1u, abort_flag)) { alive = false; break; }
-          if (!ptx::mbar_wait_lean(bar_full0 + s * 8, ph, abort_flag)) { alive = false; break; }
+          if (!ptx::mbar_wait_quiet(bar_tempty0 + buf * 8, aph ^ 1u)) { *abort_flag = 1; alive = false; break; }
+          if (!ptx::mbar_wait_quiet(bar_full0 + s * 8, ph)) { *abort_flag = 1; alive = false; break; }
           ptx::tc_fence_after();
           const uint32_t a_lo = desc_lo0 + s * (kStageBytes >> 4);
           const uint32_t b_lo = a_lo + (kTileBytesA >> 4);
@@ -308,9 +311,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int n_end = (int)min((int64_t)n_tile * BN + BN, p.N);  // one past the tile's last valid column
       int e = 0;
       if (kGrouped) e = p.expert_ids[m_tile];
+#if SGLB_FFMA2
+      uint64_t acc2[kEpiCols / 2];  // pairs of adjacent columns, one packed FMA per pair
+#pragma unroll
+      for (int j = 0; j < kEpiCols / 2; ++j) acc2[j] = 0ull;
+#else
       float acc[kEpiCols];
 #pragma unroll
       for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
+#endif
       if (e >= 0) {
         // Weight scales: a tile touches at most two 128-wide blocks; 32-column pieces never straddle one.  A
         // piece wholly past N still takes part in every hand-shake; its block index is clamped.
@@ -381,12 +390,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               scale[i] = a_scale * ptx::lds_f32(b_addr[i]);
               b_addr[i] += 4;
             }
-            if (alive) {
-              bool ok = ptx::mbar_probe_run(bar_tfull0 + buf * 8, aph);
-              if (!__all_sync(0xffffffffu, ok)) {  // rare: a long wait; the warp-wide tcgen05.ld needs a uniform decision
-                ok = ptx::mbar_wait_slow(bar_tfull0 + buf * 8, aph, abort_flag);
-                alive = __all_sync(0xffffffffu, ok);
-              }
+            // (the 32 lanes probe the same word in the same instruction, so the outcome is uniform across the
+            // warp, as the warp-wide tcgen05.ld below requires)
+            if (alive && !ptx::mbar_wait_quiet(bar_tfull0 + buf * 8, aph)) {
+              *abort_flag = 1;
+              alive = false;
             }
             if (alive) {
               ptx::tc_fence_after();
@@ -424,8 +432,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     ptx::tc_fence_before();
                     ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
                   }
+#if SGLB_FFMA2
+                  const uint32_t sc = __float_as_uint(scale[kScalesPerWarp > 1 ? i : 0]);
+                  const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) ptx::fma_f32x2(acc2[16 * i + j], ptx::pack_f32x2(r[2 * j], r[2 * j + 1]), sc2);
+#else
 #pragma unroll
                   for (int j = 0; j < 32; ++j) acc[32 * i + j] = fmaf(__uint_as_float(r[j]), scale[kScalesPerWarp > 1 ? i : 0], acc[32 * i + j]);
+#endif
                 }
               }
 #endif
@@ -440,6 +455,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
       // ---- store ----
+#if SGLB_FFMA2
+      float acc[kEpiCols];
+#pragma unroll
+      for (int j = 0; j < kEpiCols / 2; ++j) ptx::unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
+#endif
       if (p.tma_out) {
         // Rows of C are contiguous: round to the output type, park the warp's 32 x 64 block in shared memory
         // (128-byte rows, 16-byte chunks XOR-swizzled by the row so that the 32 lanes of a store spread over

@@ -104,23 +104,28 @@ __device__ __forceinline__ bool mbar_wait_lean(uint32_t bar, uint32_t parity, vo
   return mbar_wait_slow(bar, parity, abort_flag);
 }
 
-// A short run of suspending probes as one asm block (probe + branch per iteration, no flag or clock
-// bookkeeping); false if the phase has not completed by then.  Callers fall back to mbar_wait_slow.
-__device__ __forceinline__ bool mbar_probe_run(uint32_t bar, uint32_t parity) {
+// Bounded wait as one asm block: each probe may suspend the thread for up to `kProbeHintNs` (it resumes at
+// once when the phase completes), so a waiting warp spends a couple of instructions per microsecond instead of
+// competing for issue slots with the warps that have work.  Gives up after kProbeLimit probes (tens of
+// milliseconds at the very least, seconds if every probe suspends) and returns false.
+constexpr uint32_t kProbeHintNs = 4000;
+constexpr uint32_t kProbeLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
       "mov.u32 n, 0;\n"
-      "PROBE_LOOP:\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "@p bra PROBE_DONE;\n\t"
+      "QUIET_LOOP:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "@p bra QUIET_DONE;\n\t"
       "add.u32 n, n, 1;\n\t"
-      "setp.lt.u32 p, n, 64;\n\t"
-      "@p bra PROBE_LOOP;\n"
-      "PROBE_DONE:\n\t"
+      "setp.lt.u32 p, n, %4;\n\t"
+      "@p bra QUIET_LOOP;\n\t"
+      "setp.ne.u32 p, 0, 0;\n"
+      "QUIET_DONE:\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kProbeHintNs), "r"(kProbeLimit)
       : "memory");
   return ok != 0;
 }
