@@ -6,20 +6,25 @@
 // L2 at full tensor rate, more than the fabric delivers; 128x192 needs 107, and its 64-column
 // thirds never straddle a 128-wide scale block).  Per 128-wide K slab:
 //   * warp 0 (one elected lane) issues two TMA tile loads (A 128 rows x 128 B, B 192 rows x 128 B,
-//     128-byte swizzle) into a 5-deep shared-memory ring, signalled through `full` mbarriers;
+//     128-byte swizzle) into a 4-deep shared-memory ring, signalled through `full` mbarriers;
 //   * warp 1 (one elected lane) issues four tcgen05.mma kind::f8f6f4 (128x192x32) that write the
 //     slab's partial sums into one of two TMEM buffers, then commits the slab to the
 //     `empty` barrier of the ring slot and to the `tmem_full` barrier of the buffer;
-//   * warps 4-15 (three warpgroups, 64 columns each) pull the partial sums out of TMEM with
-//     tcgen05.ld, release the buffer, and promote them into float32 register accumulators with the
-//     slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be folded into
-//     the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores, overlapped with
-//     the next slab's MMAs through the two TMEM buffers).  Three warps per scheduler hide the
-//     tcgen05.ld round trip of one another.  The activation scales of the tile reach the promotion
-//     warps through shared memory: 12 slabs' worth (128 rows x 12) are fetched with coalesced
-//     128-bit loads while the previous 12 slabs are being promoted.
-// The epilogue converts to bf16/fp16 and stores 16 bytes at a time; in grouped "scatter" mode it
-// multiplies by the routing weight and writes to the token-major row named by sorted_token_ids.
+//   * warps 4-15 (three groups of four, 64 columns each) pull the partial sums out of TMEM with two
+//     32-column tcgen05.ld, release the buffer, and promote them into float32 register accumulators
+//     with the slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be
+//     folded into the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores,
+//     overlapped with the next slab's MMAs through the two TMEM buffers).  The scales of the tile
+//     reach the promotion warps through shared memory: 12 slabs' worth (128 rows x 12, plus the
+//     weight-block scales) are fetched while the previous 12 slabs are being promoted.
+// What bounds the kernel is the instruction issue of the two single-thread roles: every instruction
+// a promotion warp executes (or a waiting warp spends polling) delays the TMA and MMA threads that
+// share its scheduler, so the per-slab loops are kept short and every wait suspends in hardware
+// (mbarrier.try_wait with a time hint) instead of spinning.
+// The epilogue rounds to bf16/fp16, parks the tile in swizzled shared memory and writes it with TMA
+// stores that drain during the next tile; in grouped "scatter" mode it multiplies by the routing
+// weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids, and the
+// split-K form writes float32 partial sums.
 //
 // Every mbarrier wait is bounded; on expiry the CTA raises a status word, unwinds, frees its TMEM
 // and returns (sglb200_gemm_status() reports it).
@@ -43,12 +48,6 @@ constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 #endif
 #ifndef SGLB_EPI_WARPS
 #define SGLB_EPI_WARPS 12
-#endif
-#ifndef SGLB_DUAL
-#define SGLB_DUAL 0
-#endif
-#ifndef SGLB_FFMA2
-#define SGLB_FFMA2 0
 #endif
 constexpr int kStages = SGLB_STAGES;
 constexpr int kTmemCols = 512;
@@ -311,15 +310,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int n_end = (int)min((int64_t)n_tile * BN + BN, p.N);  // one past the tile's last valid column
       int e = 0;
       if (kGrouped) e = p.expert_ids[m_tile];
-#if SGLB_FFMA2
-      uint64_t acc2[kEpiCols / 2];  // pairs of adjacent columns, one packed FMA per pair
-#pragma unroll
-      for (int j = 0; j < kEpiCols / 2; ++j) acc2[j] = 0ull;
-#else
       float acc[kEpiCols];
 #pragma unroll
       for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
-#endif
       if (e >= 0) {
         // Weight scales: a tile touches at most two 128-wide blocks; 32-column pieces never straddle one.  A
         // piece wholly past N still takes part in every hand-shake; its block index is clamped.
@@ -404,24 +397,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               // kernel, so fewer, wider loads beat 16-column loads double-buffered through two register sets
               // (tcgen05.wait::ld waits for every outstanding load of the thread, which defeats that overlap).
               // The buffer goes back to the MMA thread as soon as the last piece is in registers.
-#if SGLB_DUAL
-              static_assert(kPiecesMax == 2, "dual staging");
-              {
-                uint32_t r0[32], r1[32];
-                ptx::tmem_ld_32x32(taddr, r0);
-                if (my_pieces > 1) ptx::tmem_ld_32x32(taddr + 32, r1);
-                ptx::tmem_ld_wait();
-                ptx::tc_fence_before();
-                ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r0[j]), scale[0], acc[j]);
-                if (my_pieces > 1) {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    acc[32 + j] = fmaf(__uint_as_float(r1[j]), scale[kScalesPerWarp > 1 ? 1 : 0], acc[32 + j]);
-                }
-              }
-#else
 #pragma unroll
               for (int i = 0; i < kPiecesMax; ++i) {
                 if (i < my_pieces) {  // warp-uniform
@@ -432,18 +407,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     ptx::tc_fence_before();
                     ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
                   }
-#if SGLB_FFMA2
-                  const uint32_t sc = __float_as_uint(scale[kScalesPerWarp > 1 ? i : 0]);
-                  const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) ptx::fma_f32x2(acc2[16 * i + j], ptx::pack_f32x2(r[2 * j], r[2 * j + 1]), sc2);
-#else
 #pragma unroll
                   for (int j = 0; j < 32; ++j) acc[32 * i + j] = fmaf(__uint_as_float(r[j]), scale[kScalesPerWarp > 1 ? i : 0], acc[32 * i + j]);
-#endif
                 }
               }
-#endif
             }
             if (++buf == (uint32_t)kAccBufs) {
               buf = 0;
@@ -455,11 +422,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
       // ---- store ----
-#if SGLB_FFMA2
-      float acc[kEpiCols];
-#pragma unroll
-      for (int j = 0; j < kEpiCols / 2; ++j) ptx::unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
-#endif
       if (p.tma_out) {
         // Rows of C are contiguous: round to the output type, park the warp's 32 x 64 block in shared memory
         // (128-byte rows, 16-byte chunks XOR-swizzled by the row so that the 32 lanes of a store spread over

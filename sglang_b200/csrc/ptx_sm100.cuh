@@ -1,6 +1,6 @@
 // Inline-PTX wrappers for the Blackwell (sm_100a) features the GEMMs use: mbarriers, TMA tile
-// loads, tensor memory (TMEM) management, tcgen05.mma / commit / ld.  Every spin-wait is
-// bounded: on expiry it records a status word and the caller unwinds; nothing traps.
+// loads and stores, tensor memory (TMEM) management, tcgen05.mma / commit / ld.  Every wait on an
+// mbarrier is bounded: on expiry the caller records a status word and unwinds; nothing traps.
 #pragma once
 #include <cuda.h>
 #include <stdint.h>
@@ -28,81 +28,13 @@ __device__ __forceinline__ void mbar_fence_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
 }
 
 // Bounded wait (about one second of SM clocks).  `abort_flag` (shared memory) is raised by whichever
 // thread gives up first so that every other waiter leaves promptly; returns false when the wait was
 // abandoned.
-constexpr long long kWaitCycleLimit = 2000000000ll;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitCycleLimit) break;
-    }
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-// Non-suspending probe of a phase: used where wake-up latency matters (the MMA issuer and the promotion
-// warps hand TMEM buffers back and forth once per K slab).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded busy-poll; same contract as mbar_wait.
-__device__ __forceinline__ bool mbar_spin_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitCycleLimit) break;
-    }
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-// Out-of-line slow path of mbar_wait_lean: the bounded poll.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  // suspending probes: a waiting warp must not compete for issue slots with the warps that have work
-  return mbar_wait(bar, parity, abort_flag);
-}
-// One probe inline (the common case in a running pipeline: the phase has already completed), the bounded
-// poll out of line, so that hot loops stay a handful of instructions long.
-__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag);
-}
 
 // Bounded wait as one asm block: each probe may suspend the thread for up to `kProbeHintNs` (it resumes at
 // once when the phase completes), so a waiting warp spends a couple of instructions per microsecond instead of
@@ -144,20 +76,11 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
   return v;
 }
 
-// Packed pair of float32 operations (sm_100): d.lo = a.lo*b.lo + d.lo, d.hi = a.hi*b.hi + d.hi in one issue slot.
+// Two 32-bit words as one 64-bit register (shared-memory matrix descriptors are built from halves).
 __device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
   return r;
-}
-__device__ __forceinline__ void fma_f32x2(uint64_t& d, uint64_t a, uint64_t b) {
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
-  uint32_t a, b;
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
-  lo = __uint_as_float(a);
-  hi = __uint_as_float(b);
 }
 
 // ---- TMA tile loads (every CTA fetches its own tiles) ----------------------------------------
@@ -236,97 +159,8 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
-// 32 lanes x 16 consecutive 32-bit columns.
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// ---- CTA pairs (cluster of two CTAs driving one tcgen05.mma.cta_group::2) --------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Every thread of every CTA of the cluster calls this; returns when all have arrived.
-__device__ __forceinline__ void cluster_sync() {
-  __syncwarp();
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Address, in the cluster-wide shared window, of this CTA's shared-memory location `local` as seen in CTA `rank`.
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-  return r;
-}
-// Arrive on an mbarrier given by a cluster-window address (own CTA or the peer).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  // default semantics (release at CTA scope): a cluster-scope release costs a memory barrier per arrival, and
-  // what is handed over here is TMEM, ordered by tcgen05.wait::ld + tcgen05.fence, not generic memory
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// Pair forms of the TMA tile loads: issued by each CTA for its own shared memory, the transaction bytes are
-// credited to the mbarrier at `bar_cluster_addr`, which may live in the peer (the pair's leader).
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0,
-                                                 int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0,
-                                                 int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-// One MMA over both CTAs of the pair (M = 256: rows 0-127 accumulate in the leader's TMEM, 128-255 in the
-// peer's; each CTA supplies its own 128 rows of A and its half of the rows of B at the same shared offsets).
-__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrival, on completion of the pair's MMAs issued so far, on the mbarrier at a cluster-window address.
-__device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
-               : "memory");
-}
-
-// ---- descriptors -----------------------------------------------------------------------------
-// Shared-memory operand descriptor for a K-major tile whose rows are 128 bytes wide and stored with
-// the 128-byte swizzle (what a TMA load with CU_TENSOR_MAP_SWIZZLE_128B produces): 8-row groups are
-// 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor version 1.
-__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
 // Instruction descriptor for kind::f8f6f4: e4m3 x e4m3 (formats 0/0), f32 accumulate (1 at bit 4),
 // both operands K-major, N/8 at bit 17, M/16 at bit 24.
 __host__ __device__ constexpr uint32_t make_idesc_e4m3_f32(int m, int n) {
