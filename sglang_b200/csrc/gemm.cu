@@ -68,7 +68,6 @@ constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
 // Output staging for the TMA store: per column group a [128 rows][64 columns] 2-byte tile in the 128-byte swizzle
 constexpr uint32_t kOutGroupBytes = BM * kEpiCols * 2;
 constexpr uint32_t kOutBytes = (kEpiWarps / 4) * kOutGroupBytes;
-constexpr int kGroupM = 8;  // m-tiles sharing a sweep over n: keeps the weight tiles of a wave L2-resident
 
 __device__ int g_gemm_status = 0;  // 0 ok, 1 = a pipeline wait expired
 
@@ -94,6 +93,7 @@ struct GemmParams {
   int scatter;
   int out_fp16;
   int tma_out;                 // rows of C are written with TMA tile stores (map_c is valid)
+  int group_m;                 // m-tiles per rasterization group
 };
 
 struct SharedCtl {
@@ -111,12 +111,13 @@ struct TileCoord {
   int m_tile, n_tile, expert;
 };
 
-// tile index -> (m_tile, n_tile): groups of kGroupM m-tiles, n fastest across groups.
-__device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int& m_tile, int& n_tile) {
-  const int per_group = kGroupM * tiles_n;
+// tile index -> (m_tile, n_tile): groups of `group_m` m-tiles sweep over n together, m fastest inside a group.
+// The activation rows of a group stay in L2 while the weight matrix streams past them once per group.
+__device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int group_m, int& m_tile, int& n_tile) {
+  const int per_group = group_m * tiles_n;
   const int g = t / per_group;
-  const int first_m = g * kGroupM;
-  const int gsz = min(tiles_m - first_m, kGroupM);
+  const int first_m = g * group_m;
+  const int gsz = min(tiles_m - first_m, group_m);
   const int r = t - g * per_group;
   m_tile = first_m + r % gsz;
   n_tile = r / gsz;
@@ -211,7 +212,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int t = u / splits, sp = u - t * splits;
         const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
         int m_tile, n_tile;
-        tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
+        tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
         int e = 0;
         if (kGrouped) {
           e = p.expert_ids[m_tile];
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
         if (kGrouped) {
           int m_tile, n_tile;
-          tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
+          tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
           if (p.expert_ids[m_tile] < 0) continue;
         }
         for (int kb = kb_begin; kb < kb_stop; ++kb) {
@@ -304,7 +305,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int t = u / splits, sp = u - t * splits;
       const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
       int m_tile, n_tile;
-      tile_coord(t, tiles_m, tiles_n, m_tile, n_tile);
+      tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
       const int64_t row = (int64_t)m_tile * BM + row_in_tile;
       const int n0 = n_tile * BN + cgrp * kEpiCols;            // first of this warp's columns
       const int n_end = (int)min((int64_t)n_tile * BN + BN, p.N);  // one past the tile's last valid column
@@ -670,6 +671,16 @@ static int get_out_map(const void* ptr, uint64_t N, uint64_t rows, int out_fp16,
   return SGLB200_OK;
 }
 
+// m-tiles per rasterization group: as many as keep the group's activation rows (128*K bytes per m-tile) within
+// a quarter of the L2, so that the weights are read from DRAM once per group and the activations once in all.
+static int choose_group_m(int64_t K) {
+  const int64_t budget = 32ll << 20;
+  int64_t g = budget / (BM * K);
+  if (g < 4) g = 4;
+  if (g > 64) g = 64;
+  return (int)g;
+}
+
 static size_t gemm_smem_bytes() { return (size_t)kStages * kStageBytes + kOutBytes + sizeof(SharedCtl) + 1024; }
 
 template <bool kGrouped>
@@ -734,6 +745,7 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   p.as_stride_m = as_stride_m, p.as_stride_k = as_stride_k;
   p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
   p.tiles_n = (int)((N + BN - 1) / BN);
+  p.group_m = choose_group_m(K);
   p.out_fp16 = out_dtype;
   int per = 0;
   int splits = choose_splits(M, N, K, &per);
@@ -791,6 +803,7 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   p.M = max_rows, p.N = N, p.K = K;
   p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
   p.tiles_n = (int)((N + BN - 1) / BN);
+  p.group_m = choose_group_m(K);
   p.as_stride_m = p.kb_total, p.as_stride_k = 1;
   p.numel = numel, p.scatter = scatter, p.out_fp16 = out_dtype;
   p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;
