@@ -304,13 +304,29 @@ def run_main(args, dist_ctx):
         "gpu_launches": args.steps * 2 * len(layers),
         "roofline": {
             "kernel": "fp8_blockscale_gemm_kernel<false>", "bound": "tensor", "achieved": achieved, "peak": peak,
-            "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": None,
+            "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": _gemm_traffic(M, layers),
             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}): fp8 issues at twice the bf16 rate",
             "frac_of_nominal_fp8_4500": achieved / FP8_NOMINAL_TFLOPS,
             "per_layer_tflops": {n: v[1] / (v[0] / 1e3) / 1e12 for n, v in per_layer.items()},
         },
     }
     return line, layers
+
+
+# DRAM bytes (read + write) of the GEMM launches of one step of the default workload, from one ncu capture of
+# `bench.py --steps 1 --warmup 1 --sections main --cpu-baseline 0` (dram__bytes_read.sum + dram__bytes_write.sum
+# of the first six fp8_blockscale_gemm_kernel launches; profiles/gemm_dram_traffic_M4096.md).  Algorithmic bytes
+# of the same six launches: 1 706 MB (weights 583, activations 210, outputs 906, scales 7).
+_GEMM_DRAM_BYTES_PER_STEP_M4096 = {"fused_qkv_a": 48.9e6, "q_b": 188.7e6, "kv_b": 227.4e6, "o_proj": 501.2e6,
+                                   "gate_up": 582.9e6, "down": 717.0e6}
+
+
+def _gemm_traffic(M, layers):
+    """Average DRAM bytes per GEMM launch, or None when the run is not the captured workload."""
+    names = [l["name"] for l in layers]
+    if M != M_TOKENS or any(n not in _GEMM_DRAM_BYTES_PER_STEP_M4096 for n in names):
+        return None
+    return sum(_GEMM_DRAM_BYTES_PER_STEP_M4096[n] for n in names) / len(names)
 
 
 def _barrier(world):

@@ -672,13 +672,15 @@ static int get_out_map(const void* ptr, uint64_t N, uint64_t rows, int out_fp16,
 }
 
 // m-tiles per rasterization group: as many as keep the group's activation rows (128*K bytes per m-tile) within
-// a quarter of the L2, so that the weights are read from DRAM once per group and the activations once in all.
-static int choose_group_m(int64_t K) {
+// a quarter of the L2 (measured: with half of it the streaming weight tiles start evicting the rows), in groups
+// of equal size, so that the weights are read from DRAM once per group and the activations once in all.
+static int choose_group_m(int64_t rows, int64_t K) {
   const int64_t budget = 32ll << 20;
-  int64_t g = budget / (BM * K);
-  if (g < 4) g = 4;
-  if (g > 64) g = 64;
-  return (int)g;
+  int64_t gmax = budget / (BM * K);
+  if (gmax < 4) gmax = 4;
+  const int64_t tiles_m = (rows + BM - 1) / BM;
+  const int64_t groups = (tiles_m + gmax - 1) / gmax;
+  return (int)((tiles_m + groups - 1) / groups);
 }
 
 static size_t gemm_smem_bytes() { return (size_t)kStages * kStageBytes + kOutBytes + sizeof(SharedCtl) + 1024; }
@@ -745,7 +747,7 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   p.as_stride_m = as_stride_m, p.as_stride_k = as_stride_k;
   p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
   p.tiles_n = (int)((N + BN - 1) / BN);
-  p.group_m = choose_group_m(K);
+  p.group_m = choose_group_m(M, K);
   p.out_fp16 = out_dtype;
   int per = 0;
   int splits = choose_splits(M, N, K, &per);
@@ -803,7 +805,7 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   p.M = max_rows, p.N = N, p.K = K;
   p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
   p.tiles_n = (int)((N + BN - 1) / BN);
-  p.group_m = choose_group_m(K);
+  p.group_m = choose_group_m(max_rows, K);
   p.as_stride_m = p.kb_total, p.as_stride_k = 1;
   p.numel = numel, p.scatter = scatter, p.out_fp16 = out_dtype;
   p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;
