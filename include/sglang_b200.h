@@ -117,6 +117,42 @@ int sglb200_moe_align_block_size_noalloc(const int32_t* topk_ids, int64_t numel,
                                          int32_t* num_tokens_post_pad, int pad_sorted_token_ids, void* stream);
 
 /*
+ * Routing (the step before moe_align).  One row of `gating` [rows, num_experts] (dtype 0 bf16, 1 fp16, 2 fp32) per
+ * token; outputs topk_weights [rows, topk] float32 and topk_ids [rows, topk] int32 in pick order (best first; equal
+ * values: lower expert index first).  num_experts <= 1024.
+ *
+ * topk_softmax: v = x; if moe_softcapping != 0: v = tanh(v / cap) * cap; if correction_bias: v += bias[e];
+ *   p = softmax(v); top-k of p; weights = p, divided by their sum when renormalize.
+ *   Replaces torch.ops.sgl_kernel.topk_softmax (sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:601-704,
+ *   schema common_extension.cc:224-227).
+ * topk_sigmoid: c = sigmoid(x) [+ bias[e]]; top-k of c; weights = c - bias[e] (as the reference reports them),
+ *   divided by their sum when renormalize.  Replaces torch.ops.sgl_kernel.topk_sigmoid
+ *   (sgl-kernel/csrc/moe/moe_topk_sigmoid_kernels.cu:60-170, schema common_extension.cc:229-232).
+ * correction_bias: float32 [num_experts] or NULL.
+ */
+int sglb200_topk_softmax(const void* gating, int dtype, int64_t rows, int num_experts, int topk, int renormalize,
+                         float moe_softcapping, const float* correction_bias, float* topk_weights, int32_t* topk_ids,
+                         void* stream);
+int sglb200_topk_sigmoid(const void* gating, int dtype, int64_t rows, int num_experts, int topk, int renormalize,
+                         const float* correction_bias, float* topk_weights, int32_t* topk_ids, void* stream);
+
+/*
+ * DeepSeek-V3 grouped gate.  With T the dtype of `input` and `bias` (same dtype, bias [num_experts]):
+ *   s = T(sigmoid(x)); b = T(s + bias); group score = T(sum of the group's two largest b); the topk_group groups with
+ *   the largest score are kept (equal scores: lower group first); the (topk - num_fused_shared_experts) largest b of
+ *   the kept groups are picked (equal: lower expert first); weights = s / sum(s of the picks), times
+ *   routed_scaling_factor when apply_routed_scaling_factor_on_output.  Fused shared experts fill the last slots
+ *   with ids num_experts, num_experts + 1, .. and weight 1 / routed_scaling_factor (times the factor when applied).
+ * Replaces torch.ops.sgl_kernel.moe_fused_gate (sgl-kernel/csrc/moe/moe_fused_gate.cu:52-260, schema
+ *   common_extension.cc:240-244).  Any group count <= 32 that divides num_experts (the reference wants powers of two
+ *   and at most 32 experts per group).
+ */
+int sglb200_moe_fused_gate(const void* input, const void* bias, int dtype, int64_t rows, int num_experts,
+                           int num_expert_group, int topk_group, int topk, int num_fused_shared_experts,
+                           float routed_scaling_factor, int apply_routed_scaling_factor_on_output, float* topk_weights,
+                           int32_t* topk_ids, void* stream);
+
+/*
  * out[t, :] = bf16( scale * sum_k x[t, k, :] ), float32 accumulation in ascending k.
  * Replaces: torch.ops.sgl_kernel.moe_sum_reduce (sgl-kernel/csrc/moe/moe_sum_reduce.cu:56-116,
  *   schema common_extension.cc:234-235).  x [tokens, topk, hidden] contiguous, hidden % 8 == 0.

@@ -361,3 +361,83 @@ def softmax_topk(logits_f32, topk=8, renormalize=True):
     if renormalize:
         w = w / w.sum(-1, keepdims=True)
     return w.astype(np.float32), ids.astype(np.int32)
+
+
+def _round_to(v_f32, dtype):
+    """float32 values rounded to the arithmetic type of the gate ("f32", "bf16", "f16")."""
+    if dtype == "f32":
+        return v_f32.astype(np.float32)
+    if dtype == "bf16":
+        return bf16_round(v_f32.astype(np.float32))
+    return v_f32.astype(np.float16).astype(np.float32)
+
+
+def _topk_desc(sel, k):
+    """Indices of the k largest entries per row, best first, lower index first on equal values."""
+    return np.argsort(-sel, axis=-1, kind="stable")[:, :k]
+
+
+def moe_fused_gate(x_f32, bias_f32, num_expert_group, topk_group, topk, num_fused_shared_experts=0,
+                   routed_scaling_factor=0.0, apply_routed_scaling_factor_on_output=False, dtype="f32"):
+    """DeepSeek-V3 grouped gate as the reference's kernel computes it (sgl-kernel/csrc/moe/moe_fused_gate.cu:52-260;
+    torch form python/sglang/srt/layers/moe/topk.py:665-738): every score is held in the input type `dtype`.
+    `x_f32` / `bias_f32` hold values already representable in that type.  Picks come out best first."""
+    x = x_f32.astype(np.float32)
+    s = _round_to(np.float32(1.0) / (np.float32(1.0) + np.exp(-x)), dtype)
+    b = _round_to(s + bias_f32.astype(np.float32)[None, :], dtype)
+    T, E = b.shape
+    gs = E // num_expert_group
+    top2 = -np.sort(-b.reshape(T, num_expert_group, gs), axis=-1)[..., :2]
+    gscore = _round_to(top2[..., 0] + top2[..., 1], dtype)
+    keep = _topk_desc(gscore, topk_group)
+    mask = np.zeros((T, num_expert_group), dtype=bool)
+    np.put_along_axis(mask, keep, True, axis=1)
+    sel = np.where(np.repeat(mask, gs, axis=1), b, -np.inf)
+    k_routed = topk - num_fused_shared_experts
+    ids = _topk_desc(sel, k_routed)
+    w = np.take_along_axis(s, ids, axis=1).astype(np.float32)
+    total = np.zeros(T, dtype=np.float32)
+    for j in range(k_routed):  # the kernel adds the picks in order, in float32
+        total = (total + w[:, j]).astype(np.float32)
+    if num_fused_shared_experts:
+        shared_w = (total / np.float32(routed_scaling_factor)).astype(np.float32)
+        w = np.concatenate([w, np.repeat(shared_w[:, None], num_fused_shared_experts, axis=1)], axis=1)
+        shared_ids = np.broadcast_to(E + np.arange(num_fused_shared_experts), (T, num_fused_shared_experts))
+        ids = np.concatenate([ids, shared_ids], axis=1)
+    w = (w / total[:, None]).astype(np.float32)
+    if apply_routed_scaling_factor_on_output:
+        w = (w * np.float32(routed_scaling_factor)).astype(np.float32)
+    return w, ids.astype(np.int32)
+
+
+def topk_softmax(x_f32, topk, renormalize=False, moe_softcapping=0.0, correction_bias=None):
+    """sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:75-215: optional tanh cap, optional bias added to the
+    logits, float32 softmax, picks best first (lower index on ties), weights = probabilities."""
+    v = x_f32.astype(np.float32)
+    if moe_softcapping != 0.0:
+        v = (np.tanh(v / np.float32(moe_softcapping)) * np.float32(moe_softcapping)).astype(np.float32)
+    if correction_bias is not None:
+        v = (v + correction_bias.astype(np.float32)[None, :]).astype(np.float32)
+    p = np.exp(v - v.max(-1, keepdims=True)).astype(np.float32)
+    p = (p * (np.float32(1.0) / p.sum(-1, keepdims=True, dtype=np.float32))).astype(np.float32)
+    ids = _topk_desc(p, topk)
+    w = np.take_along_axis(p, ids, axis=1)
+    if renormalize:
+        w = (w * (np.float32(1.0) / w.sum(-1, keepdims=True, dtype=np.float32))).astype(np.float32)
+    return w.astype(np.float32), ids.astype(np.int32)
+
+
+def topk_sigmoid(x_f32, topk, renormalize=False, correction_bias=None):
+    """sgl-kernel/csrc/moe/moe_topk_sigmoid_kernels.cu:75-170: c = sigmoid(x) + bias selects; the reported weight
+    is c - bias (float32, so not always the sigmoid bit for bit)."""
+    x = x_f32.astype(np.float32)
+    c = (np.float32(1.0) / (np.float32(1.0) + np.exp(-x))).astype(np.float32)
+    if correction_bias is not None:
+        c = (c + correction_bias.astype(np.float32)[None, :]).astype(np.float32)
+    ids = _topk_desc(c, topk)
+    w = np.take_along_axis(c, ids, axis=1)
+    if correction_bias is not None:
+        w = (w - correction_bias.astype(np.float32)[ids]).astype(np.float32)
+    if renormalize:
+        w = (w * (np.float32(1.0) / w.sum(-1, keepdims=True, dtype=np.float32))).astype(np.float32)
+    return w.astype(np.float32), ids.astype(np.int32)

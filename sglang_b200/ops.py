@@ -140,6 +140,60 @@ def moe_sum_reduce_out(x: torch.Tensor, out: torch.Tensor, routed_scaling_factor
     check(lib.sglb200_moe_sum_reduce(x.data_ptr(), out.data_ptr(), _dt(x), t, k, h, float(routed_scaling_factor), _stream(x)))
 
 
+_GATE_DT = (torch.bfloat16, torch.float16, torch.float32)
+
+
+def _gate_io(gating: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, what: str):
+    _cuda_contig(gating, "gating_output")
+    _cuda_contig(topk_weights, "topk_weights")
+    _cuda_contig(topk_ids, "topk_ids")
+    if gating.dim() != 2 or topk_weights.shape != topk_ids.shape or topk_weights.shape[0] != gating.shape[0]:
+        raise RuntimeError(f"{what}: gating [tokens, experts], outputs [tokens, topk]")
+    if topk_weights.dtype != torch.float32 or topk_ids.dtype != torch.int32:
+        raise RuntimeError(f"{what}: topk_weights must be float32 and topk_ids int32")
+    return gating.shape[0], gating.shape[1], topk_weights.shape[1]
+
+
+def _gate_bias(correction_bias: Optional[torch.Tensor], experts: int, what: str) -> int:
+    if correction_bias is None:
+        return 0
+    _cuda_contig(correction_bias, "correction_bias")
+    if correction_bias.dtype != torch.float32 or correction_bias.numel() != experts:
+        raise RuntimeError(f"{what}: correction_bias must be float32 [num_experts]")
+    return correction_bias.data_ptr()
+
+
+def topk_softmax_out(topk_weights, topk_ids, gating, renormalize=False, moe_softcapping=0.0, correction_bias=None) -> None:
+    rows, experts, k = _gate_io(gating, topk_weights, topk_ids, "topk_softmax")
+    check(lib.sglb200_topk_softmax(gating.data_ptr(), _dt(gating, _GATE_DT), rows, experts, k, int(bool(renormalize)),
+                                   float(moe_softcapping), _gate_bias(correction_bias, experts, "topk_softmax"),
+                                   topk_weights.data_ptr(), topk_ids.data_ptr(), _stream(gating)))
+
+
+def topk_sigmoid_out(topk_weights, topk_ids, gating, renormalize=False, correction_bias=None) -> None:
+    rows, experts, k = _gate_io(gating, topk_weights, topk_ids, "topk_sigmoid")
+    check(lib.sglb200_topk_sigmoid(gating.data_ptr(), _dt(gating, _GATE_DT), rows, experts, k, int(bool(renormalize)),
+                                   _gate_bias(correction_bias, experts, "topk_sigmoid"), topk_weights.data_ptr(),
+                                   topk_ids.data_ptr(), _stream(gating)))
+
+
+def moe_fused_gate(input: torch.Tensor, bias: torch.Tensor, num_expert_group: int, topk_group: int, topk: int,
+                   num_fused_shared_experts: int = 0, routed_scaling_factor: float = 0.0,
+                   apply_routed_scaling_factor_on_output: bool = False):
+    _cuda_contig(input, "input")
+    _cuda_contig(bias, "bias")
+    if input.dim() != 2 or bias.numel() != input.shape[1] or bias.dtype != input.dtype:
+        raise RuntimeError("moe_fused_gate: input [tokens, experts] and bias [experts] of the same dtype")
+    rows, experts = input.shape
+    w = torch.empty(rows, topk, dtype=torch.float32, device=input.device)
+    ids = torch.empty(rows, topk, dtype=torch.int32, device=input.device)
+    check(lib.sglb200_moe_fused_gate(input.data_ptr(), bias.data_ptr(), _dt(input, _GATE_DT), rows, experts, int(num_expert_group),
+                                     int(topk_group), int(topk), int(num_fused_shared_experts),
+                                     float(routed_scaling_factor), int(bool(apply_routed_scaling_factor_on_output)),
+                                     w.data_ptr(), ids.data_ptr(), _stream(input)))
+    return w, ids
+
+
 def gather_rows_fp8(
     src_q: torch.Tensor, src_s: torch.Tensor, sorted_token_ids: torch.Tensor, num_rows: torch.Tensor,
     numel: int, topk: int, max_rows: Optional[int] = None,

@@ -22,6 +22,9 @@ _SCHEMAS = {
     "silu_and_mul": "(Tensor(a!) out, Tensor input) -> ()",
     "moe_sum_reduce": "(Tensor input, Tensor(a!) output, float routed_scaling_factor) -> ()",
     "shuffle_rows": "(Tensor input, Tensor dst2src_map, Tensor(a!) output) -> ()",
+    "topk_softmax": "(Tensor(a!) topk_weights, Tensor(b!) topk_indices, Tensor gating_output, bool renormalize, float moe_softcapping, Tensor? correction_bias) -> ()",
+    "topk_sigmoid": "(Tensor(a!) topk_weights, Tensor(b!) topk_indices, Tensor gating_output, bool renormalize, Tensor? correction_bias) -> ()",
+    "moe_fused_gate": "(Tensor input, Tensor bias, int num_expert_group, int topk_group, int topk, int num_fused_shared_experts, float routed_scaling_factor, bool apply_routed_scaling_factor_on_output) -> Tensor[]",
 }
 
 
@@ -74,6 +77,21 @@ def _op_shuffle_rows(input, dst2src_map, output):
     torch.index_select(src, 0, dst2src_map.long(), out=dst)
 
 
+def _op_topk_softmax(topk_weights, topk_indices, gating_output, renormalize, moe_softcapping, correction_bias):
+    _ops.topk_softmax_out(topk_weights, topk_indices, gating_output, renormalize, moe_softcapping, correction_bias)
+
+
+def _op_topk_sigmoid(topk_weights, topk_indices, gating_output, renormalize, correction_bias):
+    _ops.topk_sigmoid_out(topk_weights, topk_indices, gating_output, renormalize, correction_bias)
+
+
+def _op_moe_fused_gate(input, bias, num_expert_group, topk_group, topk, num_fused_shared_experts,
+                       routed_scaling_factor, apply_routed_scaling_factor_on_output):
+    w, ids = _ops.moe_fused_gate(input, bias, num_expert_group, topk_group, topk, num_fused_shared_experts,
+                                 routed_scaling_factor, apply_routed_scaling_factor_on_output)
+    return [w, ids]
+
+
 _IMPLS = {
     "fp8_blockwise_scaled_mm": _op_fp8_blockwise_scaled_mm,
     "sgl_per_token_group_quant_8bit": _op_quant,
@@ -82,6 +100,9 @@ _IMPLS = {
     "silu_and_mul": _op_silu_and_mul,
     "moe_sum_reduce": _op_moe_sum_reduce,
     "shuffle_rows": _op_shuffle_rows,
+    "topk_softmax": _op_topk_softmax,
+    "topk_sigmoid": _op_topk_sigmoid,
+    "moe_fused_gate": _op_moe_fused_gate,
 }
 
 _LIBRARY = None
@@ -125,6 +146,22 @@ def moe_align_block_size(topk_ids, num_experts, block_size, sorted_token_ids, ex
     torch.ops.sgl_kernel.moe_align_block_size.default(
         topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, cumsum_buffer,
         pad_sorted_token_ids)
+
+
+def topk_softmax(topk_weights, topk_ids, gating_output, renormalize=False, moe_softcapping=0.0, correction_bias=None) -> None:
+    torch.ops.sgl_kernel.topk_softmax.default(topk_weights, topk_ids, gating_output, renormalize, moe_softcapping,
+                                              correction_bias)
+
+
+def topk_sigmoid(topk_weights, topk_ids, gating_output, renormalize=False, correction_bias=None) -> None:
+    torch.ops.sgl_kernel.topk_sigmoid.default(topk_weights, topk_ids, gating_output, renormalize, correction_bias)
+
+
+def moe_fused_gate(input_tensor, bias, num_expert_group, topk_group, topk, num_fused_shared_experts=0,
+                   routed_scaling_factor=0, apply_routed_scaling_factor_on_output=False):
+    return torch.ops.sgl_kernel.moe_fused_gate.default(input_tensor, bias, num_expert_group, topk_group, topk,
+                                                       num_fused_shared_experts, routed_scaling_factor,
+                                                       apply_routed_scaling_factor_on_output)
 
 
 def moe_sum_reduce(input_tensor, output_tensor, routed_scaling_factor=0):

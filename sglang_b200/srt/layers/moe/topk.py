@@ -1,7 +1,11 @@
-"""Routing used to drive the MoE path (torch ops on the device; not part of the timed kernels).
+"""Routing that feeds the MoE path.
 
-After python/sglang/srt/layers/moe/topk.py: `fused_topk_torch_native` (:427-456) and
-`biased_grouped_topk_impl` (:665-738)."""
+After python/sglang/srt/layers/moe/topk.py: `fused_topk` (:459-489, `topk_softmax` kernel),
+`fused_topk_torch_native` (:427-456) and `biased_grouped_topk_gpu` / `biased_grouped_topk_impl`
+(:741-850, :665-738; `moe_fused_gate` kernel).  CUDA tensors go through this library's routing kernels;
+the torch expressions below them are the reference's native forms, kept for CPU tensors (host-side tests of
+the expert-parallel logic run on CPU ranks).
+"""
 from __future__ import annotations
 
 from typing import Optional, Tuple
@@ -10,6 +14,14 @@ import torch
 
 
 def fused_topk(gating_output: torch.Tensor, topk: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    if gating_output.is_cuda:
+        from .... import ops
+
+        g = gating_output.contiguous()
+        w = torch.empty(g.shape[0], topk, dtype=torch.float32, device=g.device)
+        ids = torch.empty(g.shape[0], topk, dtype=torch.int32, device=g.device)
+        ops.topk_softmax_out(w, ids, g, renormalize)
+        return w, ids
     scores = torch.softmax(gating_output.float(), dim=-1)
     w, ids = torch.topk(scores, topk, dim=-1)
     if renormalize:
@@ -21,6 +33,16 @@ def biased_grouped_topk(
     gating_output: torch.Tensor, correction_bias: Optional[torch.Tensor], topk: int, renormalize: bool,
     num_expert_group: int, topk_group: int, routed_scaling_factor: Optional[float] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """`routed_scaling_factor` not None = scale the weights by it (apply_routed_scaling_factor_on_output)."""
+    if gating_output.is_cuda and renormalize:
+        from .... import ops
+
+        g = gating_output.contiguous()
+        bias = torch.zeros(g.shape[1], dtype=g.dtype, device=g.device) if correction_bias is None \
+            else correction_bias.to(g.dtype).contiguous()
+        return ops.moe_fused_gate(g, bias, num_expert_group, topk_group, topk, 0,
+                                  0.0 if routed_scaling_factor is None else routed_scaling_factor,
+                                  routed_scaling_factor is not None)
     scores = gating_output.float().sigmoid()
     T, E = scores.shape
     choice = scores if correction_bias is None else scores + correction_bias.float().unsqueeze(0)

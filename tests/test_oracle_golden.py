@@ -170,3 +170,61 @@ def test_moe_sum_reduce():
     x = O.bf16_round(rng.standard_normal((5, 8, 64)).astype(np.float32))
     out = O.moe_sum_reduce(x, 2.5)
     np.testing.assert_allclose(out, x.sum(1) * 2.5, rtol=1e-2, atol=1e-2)
+
+
+# ---- routing: oracle against the reference's torch-native functions (tests/golden/make_golden_topk.py) ----
+def _same_picks(ids_a, ids_b):
+    return np.array_equal(np.sort(ids_a, axis=1), np.sort(ids_b, axis=1))
+
+
+def _weights_by_id(w, ids):
+    order = np.argsort(ids, axis=1, kind="stable")
+    return np.take_along_axis(w, order, axis=1)
+
+
+def test_oracle_fused_gate_matches_reference_native(golden_dir):
+    from oracle import block_fp8_oracle as O
+
+    z = _load(golden_dir, "topk_native.npz")
+    for i in range(3):
+        for apply in (0, 1):
+            tag = f"g{i}a{apply}"
+            E, G, tg, k = (int(v) for v in z[tag + "_cfg"])
+            w, ids = O.moe_fused_gate(z[tag + "_x"], z[tag + "_bias"], G, tg, k, 0, 2.5, bool(apply), dtype="f32")
+            # the reference's topk is unsorted: compare the picked sets and the weight attached to each id
+            assert _same_picks(ids, z[tag + "_ids"]), tag
+            np.testing.assert_allclose(_weights_by_id(w, ids), _weights_by_id(z[tag + "_w"], z[tag + "_ids"]),
+                                       rtol=2e-6, atol=1e-7, err_msg=tag)
+
+
+def test_oracle_topk_softmax_matches_reference_native(golden_dir):
+    from oracle import block_fp8_oracle as O
+
+    z = _load(golden_dir, "topk_native.npz")
+    for i in range(4):
+        for renorm in (0, 1):
+            tag = f"s{i}r{renorm}"
+            w, ids = O.topk_softmax(z[tag + "_x"], int(z[tag + "_k"]), bool(renorm))
+            assert np.array_equal(ids, z[tag + "_ids"]), tag  # torch.topk sorted: same order, best first
+            np.testing.assert_allclose(w, z[tag + "_w"], rtol=3e-6, atol=1e-8, err_msg=tag)
+
+
+def test_oracle_gate_tie_rules():
+    from oracle import block_fp8_oracle as O
+
+    # equal scores everywhere: lower groups are kept, lower experts are picked, weights are equal
+    x = np.zeros((2, 16), dtype=np.float32)
+    w, ids = O.moe_fused_gate(x, np.zeros(16, np.float32), 4, 2, 3)
+    assert ids.tolist() == [[0, 1, 2], [0, 1, 2]]
+    np.testing.assert_allclose(w, 1.0 / 3.0, rtol=1e-6)
+    # fused shared expert: id E, weight 1/factor after normalisation (times the factor when applied)
+    w, ids = O.moe_fused_gate(x, np.zeros(16, np.float32), 4, 2, 4, 1, 2.5, False)
+    assert ids[0].tolist() == [0, 1, 2, 16]
+    np.testing.assert_allclose(w[0], [1 / 3, 1 / 3, 1 / 3, 0.4], rtol=1e-6)
+    w, _ = O.moe_fused_gate(x, np.zeros(16, np.float32), 4, 2, 4, 1, 2.5, True)
+    np.testing.assert_allclose(w[0], [2.5 / 3, 2.5 / 3, 2.5 / 3, 1.0], rtol=1e-6)
+    w, ids = O.topk_softmax(np.zeros((1, 8), np.float32), 2, True)
+    assert ids.tolist() == [[0, 1]] and np.allclose(w, 0.5)
+    b = np.linspace(0, 0.7, 8).astype(np.float32)
+    w, ids = O.topk_sigmoid(np.zeros((1, 8), np.float32), 2, False, b)
+    assert ids.tolist() == [[7, 6]] and np.allclose(w, 0.5, atol=1e-6)
