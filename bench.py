@@ -252,11 +252,30 @@ def run_main(args, dist_ctx):
                 gemm_ev.append((e0, e1, 2.0 * M * l["N"] * l["K"], l["name"]))
         return y
 
+    # End to end: host tensors in, host tensors out, through the public layer call.  Three streams, as a serving
+    # loop would run it: the input copy of layer i+1 and the output copy of layer i-1 travel (PCIe is full duplex)
+    # while layer i computes.  Device buffers are per layer; events order their reuse from one step to the next.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    for l in layers:
+        l["x_stage"] = torch.empty_like(l["x_dev"])
+        l["ev_in"], l["ev_done"], l["ev_out"] = (torch.cuda.Event() for _ in range(3))
+
     def step_e2e():
         for l in layers:
-            x = l["x_host"].to(dev, non_blocking=True)
-            y, _ = l["lin"](x)  # Fp8LinearMethod.apply: quantise + block GEMM
-            l["y_host"].copy_(y, non_blocking=True)
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(l["ev_done"])  # the previous step's GEMM has consumed the staging buffer
+                l["x_stage"].copy_(l["x_host"], non_blocking=True)
+                l["ev_in"].record(s_in)
+            stream.wait_event(l["ev_in"])
+            y, _ = l["lin"](l["x_stage"])  # Fp8LinearMethod.apply: quantise + block GEMM
+            l["ev_done"].record(stream)
+            y.record_stream(s_out)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(l["ev_done"])
+                l["y_host"].copy_(y, non_blocking=True)
+                l["ev_out"].record(s_out)
+        for l in layers:  # the step ends when its last output byte is on the host
+            stream.wait_event(l["ev_out"])
 
     def timed(fn, steps, warmup, **kw):
         for _ in range(warmup):
@@ -300,7 +319,7 @@ def run_main(args, dist_ctx):
         "config": _config(), "clocks": clocks,
         "e2e": {"value": e2e, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": t_e2e / args.steps * 1e3,
-                "api": "ColumnParallelLinear.forward -> Fp8LinearMethod.apply on pinned host tensors"},
+                "api": "ColumnParallelLinear.forward -> Fp8LinearMethod.apply on pinned host tensors; input / compute / output streams"},
         "gpu_launches": args.steps * 2 * len(layers),
         "roofline": {
             "kernel": "fp8_blockscale_gemm_kernel<false>", "bound": "tensor", "achieved": achieved, "peak": peak,
