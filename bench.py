@@ -125,7 +125,66 @@ def run_reference_arm(args):
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "sgl-kernel fp8_scaled_mm_cpu (AMX brgemm) on the host cores; the CPU path does not quantise activations",
     }
+    gpu_ref = reference_gpu_kernel(args)
+    if gpu_ref is not None:
+        line["reference_gpu_kernel"] = gpu_ref
     print(json.dumps(line), flush=True)
+
+
+def reference_gpu_kernel(args):
+    """Extra, rank 0 only: the reference's own CUDA block-FP8 GEMM (oracle/_ref/libsgl_gpu_ref.so, its
+    fp8_blockwise_gemm_kernel.cu compiled unmodified for sm_100a) timed on this box's GPU over the layers of the
+    workload it accepts (it wants N to be a multiple of 128, which leaves out N = 2112), M = 4096, inputs resident,
+    the layers run back to back so that the weights (583 MB) do not stay in L2.  Not part of `value`."""
+    lib = os.path.join(ROOT, "oracle", "_ref", "libsgl_gpu_ref.so")
+    try:
+        import torch
+        if not (os.path.exists(lib) and torch.cuda.is_available()):
+            return None
+        torch.ops.load_library(lib)
+        mm = torch.ops.sgl_gpu_ref.fp8_blockwise_scaled_mm
+        dev = torch.device("cuda", 0)
+        gen = torch.Generator(device=dev).manual_seed(1234)
+        M = M_TOKENS
+        layers = []
+        for name, N, K in DSV3_LAYERS:
+            if N % 128:
+                continue
+            wq, ws = make_block_fp8_weight(N, K, dev, gen)
+            x = torch.randn(M, K, device=dev, generator=gen)
+            g = x.view(M, K // 128, 128)
+            xs = (g.abs().amax(-1).clamp_min(1e-10) / 448.0)
+            xq = (g / xs.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(M, K)
+            layers.append((name, N, K, xq, xs.t().contiguous().t(), wq.t(), ws.t()))
+        per = {}
+        def step(record=None):
+            for name, N, K, xq, xs, wt, wst in layers:
+                if record is not None:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                mm(xq, wt, xs, wst, torch.bfloat16)
+                if record is not None:
+                    e1.record()
+                    record.append((name, 2.0 * M * N * K, e0, e1))
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        rec = []
+        for _ in range(args.steps):
+            step(rec)
+        torch.cuda.synchronize()
+        for name, fl, e0, e1 in rec:
+            d = per.setdefault(name, [0.0, 0.0])
+            d[0] += e0.elapsed_time(e1)
+            d[1] += fl
+        tot_ms = sum(d[0] for d in per.values())
+        tot_fl = sum(d[1] for d in per.values())
+        return {"kernel": "sgl-kernel fp8_blockwise_scaled_mm (CUTLASS sm100 blockwise, 128x128x128 tiles)",
+                "M": M, "unit": "TFLOP/s", "gemm_tflops": tot_fl / (tot_ms / 1e3) / 1e12,
+                "per_layer_tflops": {n: d[1] / (d[0] / 1e3) / 1e12 for n, d in per.items()},
+                "compare_with": "roofline.per_layer_tflops of the default arm (same shapes, same timing)"}
+    except Exception as e:  # the comparator is optional: never let it break the reference arm
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
 def _config():

@@ -49,25 +49,31 @@ constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 #ifndef SGLB_EPI_WARPS
 #define SGLB_EPI_WARPS 12
 #endif
+#ifndef SGLB_LOADS_IN_FLIGHT
+#define SGLB_LOADS_IN_FLIGHT 1
+#endif
 constexpr int kStages = SGLB_STAGES;
+constexpr int kLoadsInFlight = SGLB_LOADS_IN_FLIGHT;  // 32-column TMEM loads issued before each wait (32 registers each)
 constexpr int kTmemCols = 512;
-constexpr int kAccBufs = kTmemCols / BN;  // TMEM accumulator buffers in flight (3 of 160 columns)
+constexpr int kAccBufs = kTmemCols / BN;  // TMEM accumulator buffers in flight
 constexpr int kAccStride = BN;            // TMEM columns between buffers
 constexpr int kGemmThreads = 128 + SGLB_EPI_WARPS * 32;  // warp 0 TMA, warp 1 MMA + TMEM owner, warps 4.. promotion + epilogue
 constexpr int kEpiWarp0 = 4;
 constexpr int kEpiWarps = SGLB_EPI_WARPS;
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kEpiCols = 64;              // columns of a buffer owned by one warp (the last group may own fewer)
-static_assert(BN % 32 == 0 && BN <= (kEpiWarps / 4) * kEpiCols && BN > (kEpiWarps / 4 - 1) * kEpiCols &&
+constexpr int kColGroups = kEpiWarps / 4;  // promotion warps per TMEM lane quadrant
+constexpr int kEpiCols = BN / kColGroups;  // columns of a buffer owned by one warp
+static_assert(kEpiWarps % 4 == 0 && BN % kColGroups == 0 && kEpiCols % 32 == 0 && BN % 64 == 0 &&
                   kAccBufs * kAccStride <= kTmemCols && BN <= 256,
               "accumulator layout");
 constexpr int kScaleChunk = kEpiThreads / 32;                 // slabs of activation scales staged per shared-memory buffer
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 constexpr uint32_t kTileBytesB = BN * BK;
 constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
-// Output staging for the TMA store: per column group a [128 rows][64 columns] 2-byte tile in the 128-byte swizzle
-constexpr uint32_t kOutGroupBytes = BM * kEpiCols * 2;
-constexpr uint32_t kOutBytes = (kEpiWarps / 4) * kOutGroupBytes;
+// Output staging for the TMA store: per 64 columns a [128 rows][64 columns] 2-byte tile in the 128-byte swizzle
+constexpr int kOutGroups = BN / 64;
+constexpr uint32_t kOutGroupBytes = BM * 64 * 2;
+constexpr uint32_t kOutBytes = kOutGroups * kOutGroupBytes;
 
 __device__ int g_gemm_status = 0;  // 0 ok, 1 = a pipeline wait expired
 
@@ -286,13 +292,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // A thread that sees the abort flag keeps walking the same loops (without waiting or touching TMEM) so
     // that the named barrier below always collects all kEpiThreads arrivals.
     const int q = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int cgrp = (warp - kEpiWarp0) >> 2;   // column group: columns cgrp*64 .. of the tile (the last group is narrower)
+    const int cgrp = (warp - kEpiWarp0) >> 2;   // column group: columns cgrp*kEpiCols .. of the tile
     constexpr int kPiecesMax = kEpiCols / 32;
-    // when the tile width is a multiple of 64 a warp's 64 columns lie in one 128-wide weight block; otherwise
-    // (160-wide tiles) each 32-column piece looks up its own block
-    constexpr int kScalesPerWarp = (BN % kEpiCols == 0) ? 1 : kPiecesMax;
-    const int my_cols = min(kEpiCols, BN - cgrp * kEpiCols);
-    const int my_pieces = my_cols / 32;         // 32-column TMEM loads per slab for this warp
+    // one weight-block scale per warp when its columns can never straddle a 128-wide block (64 of a 192-wide
+    // tile, 128 of a 128-wide tile); otherwise (96 of 192) each 32-column piece looks up its own block
+    constexpr int kScalesPerWarp =
+        (kScaleBlockN % kEpiCols == 0 && BN % kEpiCols == 0 && (BN % kScaleBlockN) % kEpiCols == 0) ? 1 : kPiecesMax;
     const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
     const int row_in_tile = q * 32 + lane;
     const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
@@ -398,19 +403,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               // kernel, so fewer, wider loads beat 16-column loads double-buffered through two register sets
               // (tcgen05.wait::ld waits for every outstanding load of the thread, which defeats that overlap).
               // The buffer goes back to the MMA thread as soon as the last piece is in registers.
+              static_assert(kPiecesMax % kLoadsInFlight == 0, "pieces per wait");
 #pragma unroll
-              for (int i = 0; i < kPiecesMax; ++i) {
-                if (i < my_pieces) {  // warp-uniform
-                  uint32_t r[32];
-                  ptx::tmem_ld_32x32(taddr + 32 * i, r);
-                  ptx::tmem_ld_wait();
-                  if (i + 1 == my_pieces) {
-                    ptx::tc_fence_before();
-                    ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
-                  }
+              for (int i = 0; i < kPiecesMax; i += kLoadsInFlight) {
+                uint32_t r[kLoadsInFlight][32];
 #pragma unroll
-                  for (int j = 0; j < 32; ++j) acc[32 * i + j] = fmaf(__uint_as_float(r[j]), scale[kScalesPerWarp > 1 ? i : 0], acc[32 * i + j]);
+                for (int l = 0; l < kLoadsInFlight; ++l) ptx::tmem_ld_32x32(taddr + 32 * (i + l), r[l]);
+                ptx::tmem_ld_wait();
+                if (i + kLoadsInFlight == kPiecesMax) {
+                  ptx::tc_fence_before();
+                  ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
                 }
+#pragma unroll
+                for (int l = 0; l < kLoadsInFlight; ++l)
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    acc[32 * (i + l) + j] =
+                        fmaf(__uint_as_float(r[l][j]), scale[kScalesPerWarp > 1 ? i + l : 0], acc[32 * (i + l) + j]);
               }
             }
             if (++buf == (uint32_t)kAccBufs) {
@@ -429,13 +438,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // all banks) and let one thread of the column group hand the 128 x 64 block to the TMA engine, which
         // clips it to the tensor.  The store drains while the next tile is being promoted; its source is
         // reclaimed at the next epilogue.
-        const bool issuer = (q == 0 && lane == 0);
+        const bool issuer = (ep_tid == 0);
         if (issuer) ptx::tma_store_wait_read();
-        // (a warp whose wait expired still joins both barriers of its column group; only the data movement is skipped)
-        asm volatile("bar.sync %0, 128;" ::"r"(2 + cgrp) : "memory");
+        // (a warp whose wait expired still joins both barriers; only the data movement is skipped)
+        asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
         if (alive && n0 < n_end) {
-          const uint32_t grp = ptx::smem_u32(out_stage) + cgrp * kOutGroupBytes;
-          const uint32_t row_addr = grp + row_in_tile * 128;
+          const uint32_t stage0 = ptx::smem_u32(out_stage) + row_in_tile * 128;
 #pragma unroll
           for (int j = 0; j < kEpiCols / 8; ++j) {
             float x[8];
@@ -464,13 +472,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
               for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(x[i]);
             }
-            ptx::sts_128(row_addr + ((j ^ (row_in_tile & 7)) << 4), raw);
+            const int col = cgrp * kEpiCols + j * 8;  // within the tile: 64-column group col / 64, 16-byte chunk (col % 64) / 8
+            ptx::sts_128(stage0 + (col >> 6) * kOutGroupBytes + ((((col & 63) >> 3) ^ (row_in_tile & 7)) << 4), raw);
           }
           ptx::fence_async_smem();
         }
-        asm volatile("bar.sync %0, 128;" ::"r"(2 + cgrp) : "memory");
-        if (issuer && alive && n0 < n_end) {
-          ptx::tma_store_2d(&map_c, ptx::smem_u32(out_stage) + cgrp * kOutGroupBytes, n0, m_tile * BM);
+        asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+        if (issuer && alive) {
+#pragma unroll
+          for (int g = 0; g < kOutGroups; ++g) {
+            if (n_tile * BN + g * 64 < n_end)
+              ptx::tma_store_2d(&map_c, ptx::smem_u32(out_stage) + g * kOutGroupBytes, n_tile * BN + g * 64, m_tile * BM);
+          }
           ptx::tma_store_commit();
         }
         continue;
@@ -514,7 +527,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 
   // ------------------------------ teardown ------------------------------
-  if (warp >= kEpiWarp0 && (warp & 3) == 0 && lane == 0) ptx::tma_store_wait_read();  // sources stay valid until read
+  if (threadIdx.x == kEpiWarp0 * 32) ptx::tma_store_wait_read();  // sources stay valid until read
   ptx::tc_fence_before();
   __syncthreads();
   if (ctl->abort_flag != 0 && threadIdx.x == 0) {

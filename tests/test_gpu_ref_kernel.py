@@ -1,0 +1,72 @@
+"""This library's block GEMM against the reference's own CUDA kernel on the same device buffers.
+
+`oracle/_ref/libsgl_gpu_ref.so` is sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu compiled unmodified for
+sm_100a (oracle/Makefile, target `ref_gpu`).  Both kernels form the same float32 partial sums per 128-wide K slab
+and add them in the same order, so wherever this library does not split K the outputs must agree bit for bit;
+with split-K (few output tiles, long K) the float32 summation order differs and the bf16 results may differ by
+one rounding.  The reference kernel wants N to be a multiple of 128 and M-major activation scales.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libsgl_gpu_ref.so")
+
+
+@pytest.fixture(scope="module")
+def ref_mm():
+    if not os.path.exists(LIB):
+        pytest.skip("oracle/_ref/libsgl_gpu_ref.so not built (make -C oracle ref_gpu)")
+    torch.ops.load_library(LIB)
+    return torch.ops.sgl_gpu_ref.fp8_blockwise_scaled_mm
+
+
+def _inputs(M, N, K, seed):
+    from sglang_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    x[torch.rand(M, K, device="cuda", generator=g) < 0.001] *= 10
+    xq, xs = ops.per_token_group_quant_fp8(x, 128)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    blk = w.view(N // 128, 128, K // 128, 128)
+    ws = blk.abs().amax(dim=(1, 3)) / 448.0
+    wq = (blk / ws[:, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(N, K).contiguous()
+    return xq, xs, wq, ws.contiguous()
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 7168, 2048), (2048, 4608, 7168), (513, 1536, 1536), (130, 24576, 1536),
+                                   (1024, 7168, 18432), (4, 512, 512), (128, 256, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_bitwise_equal_to_reference_kernel(ref_mm, M, N, K, out_dtype):
+    from sglang_b200 import ops
+    xq, xs, wq, ws = _inputs(M, N, K, M + N + K)
+    mine = ops.w8a8_block_fp8_matmul(xq, wq, xs, ws, [128, 128], out_dtype)
+    ref = ref_mm(xq, wq.t(), xs.t().contiguous().t(), ws.t(), out_dtype)
+    torch.cuda.synchronize()
+    assert torch.equal(mine.view(torch.int16), ref.view(torch.int16))
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (16, 7168, 16384), (1, 7168, 18432)])
+def test_split_k_regime_against_reference_kernel(ref_mm, M, N, K):
+    from sglang_b200 import ops
+    xq, xs, wq, ws = _inputs(M, N, K, M + N + K)
+    mine = ops.w8a8_block_fp8_matmul(xq, wq, xs, ws, [128, 128], torch.bfloat16).float()
+    ref = ref_mm(xq, wq.t(), xs.t().contiguous().t(), ws.t(), torch.bfloat16).float()
+    torch.cuda.synchronize()
+    # one bf16 rounding apart at most: 2^-8 relative, plus a little absolute slack near zero
+    assert torch.allclose(mine, ref, rtol=2 ** -7, atol=2e-3)
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0).item() > 0.99999
+
+
+def test_op_surface_matches_reference_call(ref_mm):
+    """The same positional call through torch.ops.sgl_kernel (this library) and the reference's op."""
+    import sglang_b200.sgl_kernel  # noqa: F401  (registers torch.ops.sgl_kernel.*)
+    xq, xs, wq, ws = _inputs(256, 1024, 1024, 5)
+    a_s = xs.t().contiguous().t()
+    mine = torch.ops.sgl_kernel.fp8_blockwise_scaled_mm.default(xq, wq.t(), a_s, ws.t(), torch.bfloat16)
+    ref = ref_mm(xq, wq.t(), a_s, ws.t(), torch.bfloat16)
+    assert torch.equal(mine.view(torch.int16), ref.view(torch.int16))
