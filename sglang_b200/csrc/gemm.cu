@@ -47,10 +47,10 @@ constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 #define SGLB_STAGES 4
 #endif
 #ifndef SGLB_EPI_WARPS
-#define SGLB_EPI_WARPS 12
+#define SGLB_EPI_WARPS 8
 #endif
 #ifndef SGLB_LOADS_IN_FLIGHT
-#define SGLB_LOADS_IN_FLIGHT 1
+#define SGLB_LOADS_IN_FLIGHT 3
 #endif
 constexpr int kStages = SGLB_STAGES;
 constexpr int kLoadsInFlight = SGLB_LOADS_IN_FLIGHT;  // 32-column TMEM loads issued before each wait (32 registers each)
@@ -673,7 +673,7 @@ static int get_out_map(const void* ptr, uint64_t N, uint64_t rows, int out_fp16,
   if (enc == nullptr) return fail(SGLB200_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {N, rows};
   cuuint64_t strides[1] = {N * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kEpiCols, (cuuint32_t)BM};
+  cuuint32_t box[2] = {64u, (cuuint32_t)BM};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, out_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
