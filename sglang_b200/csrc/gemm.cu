@@ -10,21 +10,23 @@
 //   * warp 1 (one elected lane) issues four tcgen05.mma kind::f8f6f4 (128x192x32) that write the
 //     slab's partial sums into one of two TMEM buffers, then commits the slab to the
 //     `empty` barrier of the ring slot and to the `tmem_full` barrier of the buffer;
-//   * warps 4-15 (three groups of four, 64 columns each) pull the partial sums out of TMEM with two
-//     32-column tcgen05.ld, release the buffer, and promote them into float32 register accumulators
-//     with the slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be
-//     folded into the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores,
-//     overlapped with the next slab's MMAs through the two TMEM buffers).  The scales of the tile
-//     reach the promotion warps through shared memory: 12 slabs' worth (128 rows x 12, plus the
-//     weight-block scales) are fetched while the previous 12 slabs are being promoted.
-// What bounds the kernel is the instruction issue of the two single-thread roles: every instruction
-// a promotion warp executes (or a waiting warp spends polling) delays the TMA and MMA threads that
-// share its scheduler, so the per-slab loops are kept short and every wait suspends in hardware
-// (mbarrier.try_wait with a time hint) instead of spinning.
+//   * warps 4-11 (two per TMEM lane quadrant, 96 columns each) pull the partial sums out of TMEM with
+//     three 32-column tcgen05.ld issued back to back, release the buffer, and promote them into float32
+//     register accumulators with the slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float
+//     scales cannot be folded into the hardware's power-of-two MX scaling, so promotion runs on the CUDA
+//     cores, overlapped with the next slab's MMAs through the two TMEM buffers).  A thread's activation
+//     scales are prefetched into registers four slabs at a time; the weight-block scales of the tile are
+//     staged by each warp for itself in its own strip of shared memory, so the slab loop has no barrier
+//     between warps.
+// The kernel runs power- and issue-limited rather than tensor-limited (the tensor pipe is busy about half
+// of the cycles): every instruction a promotion warp executes or a waiting warp spends polling costs time,
+// so the per-slab loops are kept short, waits suspend in hardware (mbarrier.try_wait with a time hint) and
+// each promotion warp owns as many columns as the register file allows (fewer warps = less per-slab overhead).
 // The epilogue rounds to bf16/fp16, parks the tile in swizzled shared memory and writes it with TMA
 // stores that drain during the next tile; in grouped "scatter" mode it multiplies by the routing
-// weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids, and the
-// split-K form writes float32 partial sums.
+// weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids.  Split tiles
+// (every tile when there are few of them and K is long; the tiles of a short last wave otherwise) write
+// float32 partial sums that a second kernel adds in a fixed order.
 //
 // Every mbarrier wait is bounded; on expiry the CTA raises a status word, unwinds, frees its TMEM
 // and returns (sglb200_gemm_status() reports it).
