@@ -395,8 +395,8 @@ def run_main(args, dist_ctx):
 # `bench.py --steps 1 --warmup 1 --sections main --cpu-baseline 0` (dram__bytes_read.sum + dram__bytes_write.sum
 # of the first six fp8_blockscale_gemm_kernel launches; profiles/gemm_dram_traffic_M4096.md).  Algorithmic bytes
 # of the same six launches: 1 706 MB (weights 583, activations 210, outputs 906, scales 7).
-_GEMM_DRAM_BYTES_PER_STEP_M4096 = {"fused_qkv_a": 48.9e6, "q_b": 188.7e6, "kv_b": 227.4e6, "o_proj": 501.2e6,
-                                   "gate_up": 582.9e6, "down": 717.0e6}
+_GEMM_DRAM_BYTES_PER_STEP_M4096 = {"fused_qkv_a": 49.2e6, "q_b": 187.5e6, "kv_b": 226.1e6, "o_proj": 503.1e6,
+                                   "gate_up": 577.2e6, "down": 689.9e6}
 
 
 def _gemm_traffic(M, layers):
