@@ -161,6 +161,16 @@ int sglb200_moe_sum_reduce(const void* x, void* out, int dtype, int64_t tokens, 
                            float scale, void* stream);
 
 /*
+ * Combine step of the expert-parallel layer: out[t, :] = T( scale * sum_j src[slot[t, j], :] ), float32 accumulation in
+ * ascending j; entries of `slot` [tokens, per_token] (int64) outside [0, src_rows) contribute nothing.  Replaces the
+ * per-rank gather-and-add that follows `buffer.combine` in the reference's DeepEP dispatcher
+ * (python/sglang/srt/layers/moe/token_dispatcher/deepep.py:502-509) for the NCCL all-to-all form used here.
+ * src [src_rows, hidden], out [tokens, hidden], dtype 0 bf16 / 1 fp16, hidden % 8 == 0.
+ */
+int sglb200_gather_sum_rows(const void* src, const int64_t* slot, void* out, int dtype, int64_t tokens, int per_token,
+                            int64_t src_rows, int64_t hidden, float scale, void* stream);
+
+/*
  * Row gather into expert-sorted order: for r < *num_rows_dev,
  *   src = sorted_token_ids[r]; if src < numel: dst_q[r,:] = src_q[src / topk, :], dst_s[r,:] = src_s[src / topk, :]
  *   else (padding) the row and its scales are zero-filled.

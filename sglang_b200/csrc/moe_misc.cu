@@ -75,6 +75,30 @@ __global__ void __launch_bounds__(256)
   reinterpret_cast<uint4*>(out)[c] = pack8<T>(acc);
 }
 
+// out[t, 8c..] = T(scale * sum_j src[slot[t, j], 8c..]) over the j with 0 <= slot[t, j] < src_rows, ascending j,
+// float32 accumulation; one thread per 8 outputs.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    gather_sum_rows_kernel(const T* __restrict__ src, const int64_t* __restrict__ slot, T* __restrict__ out,
+                           int64_t total_chunks, int chunks_per_row, int per_token, int64_t src_rows, float scale) {
+  const int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (c >= total_chunks) return;
+  const int64_t t = c / chunks_per_row;
+  const int64_t cc = c - t * chunks_per_row;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < per_token; ++j) {
+    const int64_t r = slot[t * per_token + j];
+    if (r < 0 || r >= src_rows) continue;
+    float v[8];
+    unpack8<T>(ld_nc_16(src + (r * chunks_per_row + cc) * 8), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += v[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] *= scale;
+  reinterpret_cast<uint4*>(out)[c] = pack8<T>(acc);
+}
+
 // One CTA per destination row r: copies hidden bytes (16 B per thread per step) and `groups` scales.
 __global__ void __launch_bounds__(256)
     gather_rows_kernel(const uint4* __restrict__ src_q, const float* __restrict__ src_s, uint4* __restrict__ dst_q,
@@ -146,6 +170,32 @@ extern "C" int sglb200_moe_sum_reduce(const void* x, void* out, int dtype, int64
                                                                     (int)(hidden / 8), (int)topk, scale);
   else
     return fail(SGLB200_E_UNSUPPORTED, "moe_sum_reduce: dtype code %d (0 bf16, 1 fp16)", dtype);
+  SGLB_CUDA(cudaGetLastError());
+  return SGLB200_OK;
+}
+
+extern "C" int sglb200_gather_sum_rows(const void* src, const int64_t* slot, void* out, int dtype, int64_t tokens,
+                                       int per_token, int64_t src_rows, int64_t hidden, float scale, void* stream) {
+  SGLB_REQUIRE(tokens >= 0 && per_token >= 1 && src_rows >= 0 && hidden > 0 && hidden % 8 == 0,
+               "gather_sum_rows: tokens=%lld per_token=%d hidden=%lld (hidden must be a multiple of 8)",
+               (long long)tokens, per_token, (long long)hidden);
+  if (tokens == 0) return SGLB200_OK;
+  SGLB_REQUIRE(slot && out && (src || src_rows == 0) && aligned16(src) && aligned16(out),
+               "gather_sum_rows: null or misaligned pointer");
+  const int64_t total = tokens * (hidden / 8);
+  const int64_t blocks = (total + 255) / 256;
+  SGLB_REQUIRE(blocks < (1ll << 31), "gather_sum_rows: input too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    gather_sum_rows_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(src), slot, static_cast<__nv_bfloat16*>(out), total, (int)(hidden / 8),
+        per_token, src_rows, scale);
+  else if (dtype == 1)
+    gather_sum_rows_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __half*>(src), slot,
+                                                                     static_cast<__half*>(out), total, (int)(hidden / 8),
+                                                                     per_token, src_rows, scale);
+  else
+    return fail(SGLB200_E_UNSUPPORTED, "gather_sum_rows: dtype code %d (0 bf16, 1 fp16)", dtype);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }

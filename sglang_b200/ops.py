@@ -140,6 +140,18 @@ def moe_sum_reduce_out(x: torch.Tensor, out: torch.Tensor, routed_scaling_factor
     check(lib.sglb200_moe_sum_reduce(x.data_ptr(), out.data_ptr(), _dt(x), t, k, h, float(routed_scaling_factor), _stream(x)))
 
 
+def gather_sum_rows(src: torch.Tensor, slot: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = scale * sum_j src[slot[t, j]] (float32 accumulation); slots outside [0, len(src)) are skipped."""
+    _cuda_contig(src, "src")
+    _cuda_contig(slot, "slot")
+    if src.dim() != 2 or slot.dim() != 2 or slot.dtype != torch.int64:
+        raise RuntimeError("gather_sum_rows: src [rows, hidden], slot [tokens, per_token] int64")
+    out = torch.empty((slot.shape[0], src.shape[1]), dtype=src.dtype, device=src.device)
+    check(lib.sglb200_gather_sum_rows(src.data_ptr(), slot.data_ptr(), out.data_ptr(), _dt(src), slot.shape[0],
+                                      slot.shape[1], src.shape[0], src.shape[1], float(scale), _stream(src)))
+    return out
+
+
 _GATE_DT = (torch.bfloat16, torch.float16, torch.float32)
 
 

@@ -86,6 +86,12 @@ def combine(out_rows: torch.Tensor, plan: EPDispatchPlan, group: GroupCoordinato
     """Returns rows to their sources and sums them per token (float32, ascending rank) -> [T,H]."""
     H = out_rows.shape[1]
     S = int(plan.send_token.numel())
+    if out_rows.is_cuda and H % 8 == 0 and out_rows.dtype in (torch.bfloat16, torch.float16):
+        from ..... import ops as _ops
+
+        back = torch.empty((S, H), dtype=out_rows.dtype, device=out_rows.device)
+        group.all_to_all_single(back, out_rows.contiguous(), plan.send_splits, plan.recv_splits)
+        return _ops.gather_sum_rows(back, plan.slot, routed_scaling_factor)  # slot S = "no row": skipped
     back = torch.zeros((S + 1, H), dtype=out_rows.dtype, device=out_rows.device)  # last row stays zero
     group.all_to_all_single(back[:S], out_rows.contiguous(), plan.send_splits, plan.recv_splits)
     acc = torch.zeros((num_tokens, H), dtype=torch.float32, device=out_rows.device)

@@ -123,6 +123,19 @@ def test_moe_sum_reduce_bit_exact(ops, tokens, topk, hidden):
     assert np.array_equal(bf16_bits(out), ref)
 
 
+@pytest.mark.parametrize("tokens,per_token,hidden,src_rows", [(1, 2, 7168, 2), (97, 8, 1024, 300), (512, 4, 2048, 1000)])
+def test_gather_sum_rows_bit_exact(ops, tokens, per_token, hidden, src_rows):
+    """The expert-parallel combine: gathering the rows and summing them with the plain sum-reduce oracle."""
+    g = torch.Generator().manual_seed(tokens + per_token)
+    src = make_act(src_rows, hidden, 7 + tokens, outliers=False).cuda()
+    slot = torch.randint(0, src_rows + 1, (tokens, per_token), generator=g)  # src_rows = "no row"
+    slot[0, 0] = src_rows
+    out = ops.gather_sum_rows(src, slot.cuda(), 2.5)
+    padded = torch.cat([src.cpu(), torch.zeros(1, hidden, dtype=src.dtype)])
+    ref = CO.moe_sum_reduce(bf16_bits(padded[slot].contiguous()), 2.5)  # adding a zero row changes nothing
+    assert np.array_equal(bf16_bits(out), ref)
+
+
 def test_gather_rows(ops):
     T, topk, H, E = 50, 4, 512, 16
     g = torch.Generator().manual_seed(3)
