@@ -105,6 +105,22 @@ _IMPLS = {
     "moe_fused_gate": _op_moe_fused_gate,
 }
 
+def _fake_none(*args, **kwargs):
+    return None
+
+
+def _fake_fp8_blockwise_scaled_mm(mat_a, mat_b, scales_a, scales_b, out_dtype):
+    return mat_a.new_empty((mat_a.shape[0], mat_b.shape[1]), dtype=out_dtype)
+
+
+def _fake_moe_fused_gate(input, bias, num_expert_group, topk_group, topk, num_fused_shared_experts,
+                         routed_scaling_factor, apply_routed_scaling_factor_on_output):
+    return [input.new_empty((input.shape[0], topk), dtype=torch.float32),
+            input.new_empty((input.shape[0], topk), dtype=torch.int32)]
+
+
+_FAKES = {"fp8_blockwise_scaled_mm": _fake_fp8_blockwise_scaled_mm, "moe_fused_gate": _fake_moe_fused_gate}
+
 _LIBRARY = None
 
 
@@ -116,6 +132,9 @@ def _register():
     for name, schema in _SCHEMAS.items():
         lib.define(name + schema)
         lib.impl(name, _IMPLS[name], "CUDA")
+        # shape-only implementations for tracing (torch.compile, FakeTensor, meta tensors), as the reference
+        # registers for its ops (fp8_kernel.py:48-50, 1840-1859; fp8_utils.py:58-63)
+        torch.library.register_fake(f"sgl_kernel::{name}", _FAKES.get(name, _fake_none), lib=lib)
     _LIBRARY = lib
 
 

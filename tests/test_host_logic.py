@@ -145,3 +145,26 @@ def test_tp_sharding_two_gloo_ranks():
         assert np.array_equal(d["row_w"], d["full_w2"][:, 256 * r : 256 * r + 256])
         assert np.array_equal(d["row_s"], d["full_s2"][:, 2 * r : 2 * r + 2])
         assert np.all(d["ar"] == 3.0)
+
+
+def test_sgl_kernel_ops_have_shape_only_implementations():
+    """torch.ops.sgl_kernel.* can be traced without a GPU (meta tensors), as torch.compile needs."""
+    import torch
+    import sglang_b200.sgl_kernel  # noqa: F401
+
+    a = torch.empty(33, 256, dtype=torch.float8_e4m3fn, device="meta")
+    b = torch.empty(256, 384, dtype=torch.float8_e4m3fn, device="meta")
+    sa = torch.empty(33, 2, device="meta")
+    sb = torch.empty(2, 3, device="meta")
+    out = torch.ops.sgl_kernel.fp8_blockwise_scaled_mm.default(a, b, sa, sb, torch.bfloat16)
+    assert out.shape == (33, 384) and out.dtype == torch.bfloat16 and out.device.type == "meta"
+    x = torch.empty(33, 256, dtype=torch.bfloat16, device="meta")
+    q = torch.empty(33, 256, dtype=torch.float8_e4m3fn, device="meta")
+    s = torch.empty(33, 2, device="meta")
+    assert torch.ops.sgl_kernel.sgl_per_token_group_quant_8bit.default(x, q, s, 128, 1e-10, -448.0, 448.0, False) is None
+    w, ids = torch.ops.sgl_kernel.moe_fused_gate.default(torch.empty(7, 256, device="meta"), torch.empty(256, device="meta"),
+                                                         8, 4, 8, 0, 2.5, True)
+    assert w.shape == (7, 8) and w.dtype == torch.float32 and ids.dtype == torch.int32
+    tw = torch.empty(7, 4, device="meta")
+    ti = torch.empty(7, 4, dtype=torch.int32, device="meta")
+    assert torch.ops.sgl_kernel.topk_softmax.default(tw, ti, torch.empty(7, 64, device="meta"), True, 0.0, None) is None
