@@ -171,6 +171,16 @@ int sglb200_gather_sum_rows(const void* src, const int64_t* slot, void* out, int
                             int64_t src_rows, int64_t hidden, float scale, void* stream);
 
 /*
+ * output[t, :] = T( sum_j factors[t * topk + j] * input[permutation[t * topk + j], :] ), float32 accumulation in
+ * ascending j; `factors` (same dtype as the data) may be NULL (= 1).  Replaces torch.ops.sgl_kernel.apply_shuffle_mul_sum
+ * (sgl-kernel/csrc/moe/prepare_moe_input.cu:258-392, schema common_extension.cc:267-268), the combine of the
+ * reference's CUTLASS MoE path (python/sglang/srt/layers/moe/cutlass_moe.py).  input [tokens * topk, hidden],
+ * output [tokens, hidden], dtype 0 bf16 / 1 fp16, hidden % 8 == 0.
+ */
+int sglb200_shuffle_mul_sum(const void* input, void* output, const int32_t* permutation, const void* factors, int dtype,
+                            int64_t tokens, int topk, int64_t hidden, void* stream);
+
+/*
  * Row gather into expert-sorted order: for r < *num_rows_dev,
  *   src = sorted_token_ids[r]; if src < numel: dst_q[r,:] = src_q[src / topk, :], dst_s[r,:] = src_s[src / topk, :]
  *   else (padding) the row and its scales are zero-filled.

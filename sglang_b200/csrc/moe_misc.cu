@@ -99,6 +99,28 @@ __global__ void __launch_bounds__(256)
   reinterpret_cast<uint4*>(out)[c] = pack8<T>(acc);
 }
 
+// out[t, 8c..] = T( sum_j f[t, j] * in[perm[t * topk + j], 8c..] ), float32 accumulation in ascending j; factors in
+// the output type (or absent = 1).  One thread per 8 outputs.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    shuffle_mul_sum_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __restrict__ perm,
+                           const T* __restrict__ factors, int64_t total_chunks, int chunks_per_row, int topk) {
+  const int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (c >= total_chunks) return;
+  const int64_t t = c / chunks_per_row;
+  const int64_t cc = c - t * chunks_per_row;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < topk; ++j) {
+    const int64_t r = perm[t * topk + j];
+    const float f = factors != nullptr ? ElemTraits<T>::to_f32(factors[t * topk + j]) : 1.0f;
+    float v[8];
+    unpack8<T>(ld_nc_16(in + (r * chunks_per_row + cc) * 8), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += f * v[i];
+  }
+  reinterpret_cast<uint4*>(out)[c] = pack8<T>(acc);
+}
+
 // One CTA per destination row r: copies hidden bytes (16 B per thread per step) and `groups` scales.
 __global__ void __launch_bounds__(256)
     gather_rows_kernel(const uint4* __restrict__ src_q, const float* __restrict__ src_s, uint4* __restrict__ dst_q,
@@ -196,6 +218,33 @@ extern "C" int sglb200_gather_sum_rows(const void* src, const int64_t* slot, voi
                                                                      per_token, src_rows, scale);
   else
     return fail(SGLB200_E_UNSUPPORTED, "gather_sum_rows: dtype code %d (0 bf16, 1 fp16)", dtype);
+  SGLB_CUDA(cudaGetLastError());
+  return SGLB200_OK;
+}
+
+extern "C" int sglb200_shuffle_mul_sum(const void* input, void* output, const int32_t* permutation, const void* factors,
+                                       int dtype, int64_t tokens, int topk, int64_t hidden, void* stream) {
+  SGLB_REQUIRE(tokens >= 0 && topk >= 1 && hidden > 0 && hidden % 8 == 0,
+               "shuffle_mul_sum: tokens=%lld topk=%d hidden=%lld (hidden must be a multiple of 8)", (long long)tokens,
+               topk, (long long)hidden);
+  if (tokens == 0) return SGLB200_OK;
+  SGLB_REQUIRE(input && output && permutation && aligned16(input) && aligned16(output),
+               "shuffle_mul_sum: null or misaligned pointer");
+  const int64_t total = tokens * (hidden / 8);
+  const int64_t blocks = (total + 255) / 256;
+  SGLB_REQUIRE(blocks < (1ll << 31), "shuffle_mul_sum: input too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    shuffle_mul_sum_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(output), permutation,
+        static_cast<const __nv_bfloat16*>(factors), total, (int)(hidden / 8), topk);
+  else if (dtype == 1)
+    shuffle_mul_sum_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __half*>(input),
+                                                                     static_cast<__half*>(output), permutation,
+                                                                     static_cast<const __half*>(factors), total,
+                                                                     (int)(hidden / 8), topk);
+  else
+    return fail(SGLB200_E_UNSUPPORTED, "shuffle_mul_sum: dtype code %d (0 bf16, 1 fp16)", dtype);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }

@@ -152,6 +152,28 @@ def gather_sum_rows(src: torch.Tensor, slot: torch.Tensor, scale: float = 1.0) -
     return out
 
 
+def shuffle_mul_sum_out(input: torch.Tensor, output: torch.Tensor, permutation: torch.Tensor,
+                        factors: Optional[torch.Tensor] = None) -> None:
+    """output[t] = sum_j factors[t, j] * input[permutation[t * topk + j]] (float32 accumulation)."""
+    _cuda_contig(input, "input")
+    _cuda_contig(output, "output")
+    _cuda_contig(permutation, "permutation")
+    tokens, hidden = output.shape
+    if permutation.dtype != torch.int32 or tokens == 0 or permutation.numel() % max(tokens, 1):
+        raise RuntimeError("apply_shuffle_mul_sum: permutation must be int32 with tokens * topk entries")
+    topk = permutation.numel() // tokens
+    if input.dtype != output.dtype or input.shape[1] != hidden:
+        raise RuntimeError("apply_shuffle_mul_sum: input [tokens * topk, hidden] and output [tokens, hidden] of one dtype")
+    f = 0
+    if factors is not None:
+        _cuda_contig(factors, "factors")
+        if factors.dtype != output.dtype or factors.numel() != permutation.numel():
+            raise RuntimeError("apply_shuffle_mul_sum: factors must match the output dtype and have tokens * topk entries")
+        f = factors.data_ptr()
+    check(lib.sglb200_shuffle_mul_sum(input.data_ptr(), output.data_ptr(), permutation.data_ptr(), f, _dt(output), tokens,
+                                      topk, hidden, _stream(output)))
+
+
 _GATE_DT = (torch.bfloat16, torch.float16, torch.float32)
 
 

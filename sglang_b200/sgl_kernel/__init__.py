@@ -22,6 +22,9 @@ _SCHEMAS = {
     "silu_and_mul": "(Tensor(a!) out, Tensor input) -> ()",
     "moe_sum_reduce": "(Tensor input, Tensor(a!) output, float routed_scaling_factor) -> ()",
     "shuffle_rows": "(Tensor input, Tensor dst2src_map, Tensor(a!) output) -> ()",
+    "apply_shuffle_mul_sum": "(Tensor input, Tensor(a!) output, Tensor permutation, Tensor? factors) -> ()",
+    "prepare_moe_input": "(Tensor topk_ids, Tensor(a!) expert_offsets, Tensor(b!)? blockscale_offsets, Tensor(c!) problem_sizes1, Tensor(d!) problem_sizes2, Tensor(e!) input_permutation, Tensor(f!) output_permutation, int num_experts, int n, int k) -> ()",
+    "fp8_blockwise_scaled_grouped_mm": "(Tensor(a!) output, Tensor a_ptrs, Tensor b_ptrs, Tensor out_ptrs, Tensor a_scales_ptrs, Tensor b_scales_ptrs, Tensor a, Tensor b, Tensor scales_a, Tensor scales_b, Tensor stride_a, Tensor stride_b, Tensor stride_c, Tensor layout_sfa, Tensor layout_sfb, Tensor problem_sizes, Tensor expert_offsets, Tensor workspace) -> ()",
     "topk_softmax": "(Tensor(a!) topk_weights, Tensor(b!) topk_indices, Tensor gating_output, bool renormalize, float moe_softcapping, Tensor? correction_bias) -> ()",
     "topk_sigmoid": "(Tensor(a!) topk_weights, Tensor(b!) topk_indices, Tensor gating_output, bool renormalize, Tensor? correction_bias) -> ()",
     "moe_fused_gate": "(Tensor input, Tensor bias, int num_expert_group, int topk_group, int topk, int num_fused_shared_experts, float routed_scaling_factor, bool apply_routed_scaling_factor_on_output) -> Tensor[]",
@@ -77,6 +80,60 @@ def _op_shuffle_rows(input, dst2src_map, output):
     torch.index_select(src, 0, dst2src_map.long(), out=dst)
 
 
+def _op_apply_shuffle_mul_sum(input, output, permutation, factors):
+    _ops.shuffle_mul_sum_out(input, output, permutation.reshape(-1), None if factors is None else factors.reshape(-1))
+
+
+def _op_prepare_moe_input(topk_ids, expert_offsets, blockscale_offsets, problem_sizes1, problem_sizes2,
+                          input_permutation, output_permutation, num_experts, n, k):
+    # prepare_moe_input.cu:10-168: rows per expert, their prefix sums, and the two permutations between the
+    # token-major and the expert-major order.  The reference fills the permutations with atomics (any order inside
+    # an expert); here the order is the stable one of this library's sort (block size 1 = no padding).
+    if topk_ids.dtype != torch.int32:
+        raise RuntimeError("prepare_moe_input: topk_ids must be int32")
+    numel, topk = topk_ids.numel(), topk_ids.shape[1]
+    order, _, _ = _ops.moe_align_block_size(topk_ids, 1, num_experts)
+    order = order[:numel]
+    counts = torch.bincount(topk_ids.reshape(-1), minlength=num_experts)[:num_experts].to(torch.int32)
+    expert_offsets[0] = 0
+    expert_offsets[1 : num_experts + 1] = torch.cumsum(counts, 0)
+    if blockscale_offsets is not None:
+        blockscale_offsets[0] = 0
+        blockscale_offsets[1 : num_experts + 1] = torch.cumsum((counts + 127) // 128 * 128, 0)
+    problem_sizes1[:, 0], problem_sizes1[:, 1], problem_sizes1[:, 2] = counts, 2 * n, k
+    problem_sizes2[:, 0], problem_sizes2[:, 1], problem_sizes2[:, 2] = counts, k, n
+    input_permutation.copy_(order // topk)
+    output_permutation[order.long()] = torch.arange(numel, dtype=torch.int32, device=topk_ids.device)
+
+
+def _op_fp8_blockwise_scaled_grouped_mm(output, a_ptrs, b_ptrs, out_ptrs, a_scales_ptrs, b_scales_ptrs, a, b, scales_a,
+                                        scales_b, stride_a, stride_b, stride_c, layout_sfa, layout_sfb, problem_sizes,
+                                        expert_offsets, workspace):
+    # fp8_blockwise_moe_kernel.cu:650-810: per expert e, output[off_e : off_e + M_e] = blockscaled(a[off_e : ...], b[e]).
+    # The pointer / stride / layout / workspace tensors are scratch of the reference's CUTLASS launch and are not
+    # needed here.  The rows of every expert are padded to this library's 128-row blocks (stable sort of the rows'
+    # expert numbers), gathered, multiplied, and written back to their unpadded places by the scatter epilogue.
+    R, K = a.shape
+    E = b.shape[0]
+    w = b.transpose(1, 2)  # the reference passes [E, K, N] views of [E, N, K] weights
+    if not w.is_contiguous():
+        raise RuntimeError("fp8_blockwise_scaled_grouped_mm: b must be the transposed view of a contiguous [E, N, K] tensor")
+    N = w.shape[1]
+    nb, kb = (N + 127) // 128, (K + 127) // 128
+    if scales_b.transpose(1, 2).is_contiguous() and tuple(scales_b.shape[1:]) == (kb, nb):
+        ws = scales_b.transpose(1, 2)  # as fp8.py passes them: the transposed view of [E, N/128, K/128]
+    elif scales_b.is_contiguous() and tuple(scales_b.shape[1:]) == (nb, kb):
+        ws = scales_b
+    else:
+        raise RuntimeError("fp8_blockwise_scaled_grouped_mm: scales_b must be [E, N/128, K/128] or its transposed view")
+    rows_per_expert = problem_sizes[:, 0].to(torch.int64)
+    row_expert = torch.repeat_interleave(torch.arange(E, device=a.device, dtype=torch.int32), rows_per_expert,
+                                         output_size=R)
+    sorted_ids, expert_ids, post = _ops.moe_align_block_size(row_expert.view(R, 1), 128, E)
+    aq, a_s = _ops.gather_rows_fp8(a, scales_a.contiguous(), sorted_ids, post, R, 1)
+    _ops.grouped_block_fp8_matmul(aq, a_s, w, ws, sorted_ids, expert_ids, post, numel=R, scatter=True, out=output)
+
+
 def _op_topk_softmax(topk_weights, topk_indices, gating_output, renormalize, moe_softcapping, correction_bias):
     _ops.topk_softmax_out(topk_weights, topk_indices, gating_output, renormalize, moe_softcapping, correction_bias)
 
@@ -100,6 +157,9 @@ _IMPLS = {
     "silu_and_mul": _op_silu_and_mul,
     "moe_sum_reduce": _op_moe_sum_reduce,
     "shuffle_rows": _op_shuffle_rows,
+    "apply_shuffle_mul_sum": _op_apply_shuffle_mul_sum,
+    "prepare_moe_input": _op_prepare_moe_input,
+    "fp8_blockwise_scaled_grouped_mm": _op_fp8_blockwise_scaled_grouped_mm,
     "topk_softmax": _op_topk_softmax,
     "topk_sigmoid": _op_topk_sigmoid,
     "moe_fused_gate": _op_moe_fused_gate,
@@ -165,6 +225,25 @@ def moe_align_block_size(topk_ids, num_experts, block_size, sorted_token_ids, ex
     torch.ops.sgl_kernel.moe_align_block_size.default(
         topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, cumsum_buffer,
         pad_sorted_token_ids)
+
+
+def prepare_moe_input(topk_ids, expert_offsets, problem_sizes1, problem_sizes2, input_permutation, output_permutation,
+                      num_experts, n, k, blockscale_offsets=None):
+    torch.ops.sgl_kernel.prepare_moe_input.default(topk_ids, expert_offsets, blockscale_offsets, problem_sizes1,
+                                                   problem_sizes2, input_permutation, output_permutation, num_experts,
+                                                   n, k)
+
+
+def apply_shuffle_mul_sum(input, output, permutation, factors=None):
+    torch.ops.sgl_kernel.apply_shuffle_mul_sum.default(input, output, permutation, factors)
+
+
+def fp8_blockwise_scaled_grouped_mm(output, a_ptrs, b_ptrs, out_ptrs, a_scales_ptrs, b_scales_ptrs, a, b, scales_a, scales_b,
+                                    stride_a, stride_b, stride_c, layout_sfa, layout_sfb, problem_sizes, expert_offsets,
+                                    workspace):
+    torch.ops.sgl_kernel.fp8_blockwise_scaled_grouped_mm.default(
+        output, a_ptrs, b_ptrs, out_ptrs, a_scales_ptrs, b_scales_ptrs, a, b, scales_a, scales_b, stride_a, stride_b,
+        stride_c, layout_sfa, layout_sfb, problem_sizes, expert_offsets, workspace)
 
 
 def topk_softmax(topk_weights, topk_ids, gating_output, renormalize=False, moe_softcapping=0.0, correction_bias=None) -> None:

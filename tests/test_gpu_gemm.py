@@ -173,3 +173,53 @@ def test_sgl_kernel_gemm_op_surface(ops):
     w = codes_to_fp8(wq)
     c = sk.fp8_blockwise_scaled_mm(xq, w.t(), xs, torch.from_numpy(ws).cuda().t(), torch.bfloat16)
     assert_close_fp(to_f32_np(c), O.block_fp8_linear(to_f32_np(x), wq, ws))
+
+
+def test_cutlass_moe_path_ops(ops):
+    """The op sequence of the reference's CUTLASS MoE runner (python/sglang/srt/layers/moe/cutlass_moe.py:125-260:
+    prepare_moe_input -> quantise -> shuffle_rows -> grouped GEMM -> silu_and_mul -> quantise -> grouped GEMM ->
+    apply_shuffle_mul_sum), with the tensor layouts fp8.py:1071-1104 passes, against the fused-experts oracle."""
+    import sglang_b200.sgl_kernel as sk
+    T, E, H, I, topk = 70, 8, 512, 256, 4
+    x, w13q, w13s, w2q, w2s, w, ids = _moe_inputs(T, E, H, I, topk, seed=31, filtered=False)
+    dev = "cuda"
+    a = x.cuda()
+    w1 = codes_to_fp8(w13q).transpose(1, 2)            # [E, k, 2n] view
+    w2 = codes_to_fp8(w2q).transpose(1, 2)             # [E, n, k] view
+    w1_s = torch.from_numpy(w13s).cuda().transpose(1, 2)
+    w2_s = torch.from_numpy(w2s).cuda().transpose(1, 2)
+    topk_ids, topk_w = ids.cuda(), w.cuda()
+    m, k, n = T, H, I
+    i32 = dict(dtype=torch.int32, device=dev)
+    expert_offsets = torch.empty(E + 1, **i32)
+    ps1, ps2 = torch.empty(E, 3, **i32), torch.empty(E, 3, **i32)
+    a_map, c_map = torch.empty(m * topk, **i32), torch.empty(m * topk, **i32)
+    sk.prepare_moe_input(topk_ids, expert_offsets, ps1, ps2, a_map, c_map, E, n, k)
+    counts = np.bincount(ids.numpy().reshape(-1), minlength=E)
+    assert expert_offsets.cpu().tolist() == [0] + np.cumsum(counts).tolist()
+    assert ps1.cpu().tolist() == [[int(c), 2 * n, k] for c in counts] and ps2.cpu().tolist() == [[int(c), k, n] for c in counts]
+    flat = ids.numpy().reshape(-1)
+    assert np.array_equal(flat[c_map.cpu().numpy().argsort()], np.sort(flat))          # expert-major order
+    assert np.array_equal(a_map.cpu().numpy()[c_map.cpu().numpy()], np.arange(m * topk) // topk)
+    a_q, a1_scale = ops.per_token_group_quant_fp8(a, 128)
+    rep_a_q = sk.shuffle_rows(a_q, a_map, (m * topk, k))
+    rep_a1_s = sk.shuffle_rows(a1_scale, a_map, (m * topk, k // 128))
+    c1 = torch.empty(m * topk, 2 * n, device=dev, dtype=torch.bfloat16)
+    c2 = torch.empty(m * topk, k, device=dev, dtype=torch.bfloat16)
+    scratch = torch.empty(E, dtype=torch.int64, device=dev)
+    lay = torch.empty(E, 5, **i32)
+    sk.fp8_blockwise_scaled_grouped_mm(c1, scratch, scratch, scratch, scratch, scratch, rep_a_q, w1, rep_a1_s, w1_s,
+                                       scratch, scratch, scratch, lay, lay, ps1, expert_offsets[:-1], scratch)
+    inter = torch.empty(m * topk, n, device=dev, dtype=torch.bfloat16)
+    sk.silu_and_mul(c1, inter)
+    inter_q, a2_scale = ops.per_token_group_quant_fp8(inter, 128)
+    sk.fp8_blockwise_scaled_grouped_mm(c2, scratch, scratch, scratch, scratch, scratch, inter_q, w2, a2_scale, w2_s,
+                                       scratch, scratch, scratch, lay, lay, ps2, expert_offsets[:-1], scratch)
+    out = torch.empty(m, k, device=dev, dtype=torch.bfloat16)
+    sk.apply_shuffle_mul_sum(c2, out, c_map, topk_w.to(torch.bfloat16))
+    torch.cuda.synchronize()
+    assert ops.gemm_status() == 0
+    # the CUTLASS path rounds the routing weights to bf16 and applies them after the bf16 rounding of GEMM 2
+    ref = O.fused_experts_block_fp8(to_f32_np(x), w13q, w13s, w2q, w2s,
+                                    w.to(torch.bfloat16).float().numpy(), ids.numpy(), 1.0)
+    assert_close_fp(to_f32_np(out), ref, rtol=3e-2, atol=3e-2)
