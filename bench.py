@@ -272,6 +272,7 @@ def make_block_fp8_weight(N, K, device, gen, std=0.02, experts=None):
 def run_main(args, dist_ctx):
     import torch
     from sglang_b200 import ops
+    from sglang_b200._lib import lib as _lib
     from sglang_b200.srt.layers.linear import ColumnParallelLinear
     from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
 
@@ -379,7 +380,9 @@ def run_main(args, dist_ctx):
         "e2e": {"value": e2e, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": t_e2e / args.steps * 1e3,
                 "api": "ColumnParallelLinear.forward -> Fp8LinearMethod.apply on pinned host tensors; input / compute / output streams"},
-        "gpu_launches": args.steps * 2 * len(layers),
+        # per layer: the quantizer, the GEMM, and the partial-sum reduction where the GEMM splits tiles along K
+        "gpu_launches": args.steps * sum(2 + (1 if _lib.sglb200_gemm_workspace_bytes(M, l["N"], l["K"]) > 0 else 0)
+                                         for l in layers),
         "roofline": {
             "kernel": "fp8_blockscale_gemm_kernel<false>", "bound": "tensor", "achieved": achieved, "peak": peak,
             "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": _gemm_traffic(M, layers),
