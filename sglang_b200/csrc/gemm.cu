@@ -445,37 +445,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // (a warp whose wait expired still joins both barriers; only the data movement is skipped)
         asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
         if (alive && n0 < n_end) {
+          if (p.bias != nullptr) {
+            // (tile columns past N are clipped by the store; their bias reads are clamped to stay in bounds)
+            const uint16_t* bsrc = static_cast<const uint16_t*>(p.bias);
+#pragma unroll
+            for (int j = 0; j < kEpiCols; ++j) {
+              const uint16_t raw16 = __ldg(bsrc + min(n0 + j, (int)p.N - 1));
+              acc[j] += p.out_fp16 ? __half2float(__ushort_as_half(raw16)) : __bfloat162float(__ushort_as_bfloat16(raw16));
+            }
+          }
+          // round pairs of adjacent columns with one packed conversion each, then 16-byte shared-memory stores
+          uint32_t packed[kEpiCols / 2];
+          if (p.out_fp16) {
+#pragma unroll
+            for (int j = 0; j < kEpiCols / 2; ++j) {
+              const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+              packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kEpiCols / 2; ++j) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+              packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          }
           const uint32_t stage0 = ptx::smem_u32(out_stage) + row_in_tile * 128;
+          const uint32_t swz = (uint32_t)(row_in_tile & 7);
 #pragma unroll
           for (int j = 0; j < kEpiCols / 8; ++j) {
-            float x[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = acc[j * 8 + i];
-            const int n = n0 + j * 8;
-            if (p.bias != nullptr && n + 8 <= n_end) {
-              const uint4 braw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + n));
-              if (p.out_fp16) {
-                const __half* bb = reinterpret_cast<const __half*>(&braw);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) x[i] += __half2float(bb[i]);
-              } else {
-                const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&braw);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) x[i] += __bfloat162float(bb[i]);
-              }
-            }
-            uint4 raw;
-            if (p.out_fp16) {
-              __half* o = reinterpret_cast<__half*>(&raw);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = __float2half_rn(x[i]);
-            } else {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&raw);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(x[i]);
-            }
             const int col = cgrp * kEpiCols + j * 8;  // within the tile: 64-column group col / 64, 16-byte chunk (col % 64) / 8
-            ptx::sts_128(stage0 + (col >> 6) * kOutGroupBytes + ((((col & 63) >> 3) ^ (row_in_tile & 7)) << 4), raw);
+            ptx::sts_128(stage0 + (col >> 6) * kOutGroupBytes + ((((col & 63) >> 3) ^ swz) << 4),
+                         make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]));
           }
           ptx::fence_async_smem();
         }
