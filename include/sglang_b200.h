@@ -240,6 +240,15 @@ int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s, const void
  */
 int sglb200_gemm_status(void);
 
+/*
+ * Health of the streaming kernels (the quantizer and the fused silu_and_mul + quantizer stage their input
+ * through shared memory with bulk copies that complete on mbarriers): 0, or 1 if a bounded wait for a staged
+ * tile expired since the library was loaded (the CTA then returns and leaves its output incomplete).
+ * Synchronises the device.  Stands in for the CUDA error a failed run of the reference's quantizer launcher
+ * (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-217) would surface at the next synchronisation.
+ */
+int sglb200_stream_status(void);
+
 #ifdef __cplusplus
 }
 #endif

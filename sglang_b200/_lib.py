@@ -42,6 +42,7 @@ SIGNATURES = {
     "sglb200_fp8_blockwise_scaled_mm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "sglb200_fp8_blockwise_grouped_mm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _i32, _vp]),
     "sglb200_gemm_status": (_i32, []),
+    "sglb200_stream_status": (_i32, []),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

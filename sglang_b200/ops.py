@@ -375,3 +375,9 @@ def grouped_block_fp8_matmul(
 def gemm_status() -> int:
     """0, or 1 if a pipeline wait inside a GEMM kernel expired since the library was loaded (synchronises)."""
     return lib.sglb200_gemm_status()
+
+
+def stream_status() -> int:
+    """0, or 1 if a wait for a staged tile inside a streaming kernel (quantizer, fused silu_and_mul + quantizer)
+    expired since the library was loaded (synchronises)."""
+    return lib.sglb200_stream_status()

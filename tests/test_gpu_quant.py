@@ -41,6 +41,38 @@ def test_quant_groups_and_dtypes(ops, group, dtype, code):
     assert np.array_equal(fp8_codes(q), rq)
 
 
+@pytest.mark.parametrize("dtype,code", [(torch.bfloat16, 0), (torch.float16, 1), (torch.float32, 2)])
+def test_quant_special_values(ops, dtype, code):
+    # NaN, infinities and signed zeros: a group holding a NaN or an infinity leaves the fast path of the kernel and
+    # must still follow the reference arithmetic (NaN-ignoring maximum, clamp that maps a NaN quotient to -448)
+    x = make_act(64, 1024, 77, dtype=dtype)
+    x[1, 3] = float("nan")
+    x[2, 130] = float("inf")
+    x[3, 260] = float("-inf")
+    x[4, 5] = float("nan")
+    x[4, 6] = float("inf")
+    x[5, :8] = -0.0
+    x[6, 128:256] = -0.0  # an all-zero group of negative zeros
+    x[7, 511] = float("nan")
+    q, s = ops.per_token_group_quant_fp8(x.cuda(), 128)
+    raw = x.numpy() if code == 2 else x.view(torch.int16).numpy().view(np.uint16)
+    rq, rs = CO.quant(raw, code, 128)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), rs.view(np.uint32))
+    assert np.array_equal(fp8_codes(q), rq)
+    assert ops.stream_status() == 0
+
+
+def test_quant_ragged_tile_edges(ops):
+    # sizes around the kernel's 8192-element tiles and its ring of staged tiles
+    for tokens, hidden in [(1, 8192), (1, 8192 + 128), (3, 8192 - 128), (5 * 148 * 3 + 1, 8192), (33, 24576 + 384)]:
+        x = make_act(tokens, hidden, tokens + hidden)
+        q, s = ops.per_token_group_quant_fp8(x.cuda(), 128)
+        rq, rs = CO.quant(bf16_bits(x), 0, 128)
+        assert np.array_equal(s.cpu().numpy().view(np.uint32), rs.view(np.uint32))
+        assert np.array_equal(fp8_codes(q), rq)
+    assert ops.stream_status() == 0
+
+
 def test_quant_column_major_scales(ops):
     x = make_act(83, 2048, 5)
     q, s = ops.per_token_group_quant_fp8(x.cuda(), 128, column_major_scales=True, scale_tma_aligned=True)
@@ -97,7 +129,7 @@ def test_silu_and_mul(ops, rows, d):
     assert (got != ref).mean() < 5e-3
 
 
-@pytest.mark.parametrize("rows,d", [(1, 128), (19, 768), (300, 2048)])
+@pytest.mark.parametrize("rows,d", [(1, 128), (19, 768), (300, 2048), (2777, 768), (37, 14336), (4500, 2048), (3, 8192)])
 def test_silu_mul_quant_equals_unfused_pipeline(ops, rows, d):
     x = (make_act(rows, 2 * d, 77 + rows, outliers=False) * 3).cuda()
     h = torch.empty(rows, d, device="cuda", dtype=torch.bfloat16)
@@ -112,6 +144,7 @@ def test_silu_mul_quant_equals_unfused_pipeline(ops, rows, d):
     lim = torch.tensor([rows // 2], device="cuda", dtype=torch.int32)
     q2, s2 = ops.silu_and_mul_quant_fp8(x, 128, num_rows=lim)
     assert torch.equal(q2.view(torch.uint8)[: rows // 2], q.view(torch.uint8)[: rows // 2])
+    assert ops.stream_status() == 0
 
 
 @pytest.mark.parametrize("tokens,topk,hidden", [(1, 8, 7168), (33, 8, 2048), (512, 6, 1024), (5, 1, 128)])
