@@ -82,18 +82,19 @@ __device__ __forceinline__ void scan_over_warps(int B, int* wc, int* tot) {
   }
 }
 
-// prefix[0..B] = exclusive scan of ceil(tot[b]/block)*block.  `scratch` holds 33 ints.
+// prefix[0..B] = exclusive scan of ceil(tot[b]/block)*block.  `scratch` holds 33 ints.  NT = threads of the CTA.
+template <int NT = kAlignThreads>
 __device__ __forceinline__ void padded_prefix(int B, int block_size, const int* tot, int* prefix, int* scratch) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int carry = 0;
-  for (int base = 0; base < B; base += kAlignThreads) {
+  for (int base = 0; base < B; base += NT) {
     const int b = base + threadIdx.x;
     const int v = b < B ? (tot[b] + block_size - 1) / block_size * block_size : 0;
     const int incl = warp_incl_scan(v);
     if (lane == 31) scratch[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      const int w = scratch[lane];
+      const int w = lane < NT / 32 ? scratch[lane] : 0;
       const int wi = warp_incl_scan(w);
       scratch[lane] = wi - w;
       if (lane == 31) scratch[32] = wi;
@@ -143,11 +144,12 @@ __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ ids, i
 }
 
 // expert_ids for blocks [first, first+stride, ...) and the padding tails of buckets b = first_b, first_b+stride_b, ...
+template <int NT = kAlignThreads>
 __device__ __forceinline__ void fill_meta(int B, int block_size, int64_t numel, const int* prefix, const int* tot_all,
                                           int32_t* __restrict__ expert_ids, int32_t* __restrict__ sorted,
                                           bool pad_sorted, int part, int parts) {
   const int num_blocks = prefix[B] / block_size;
-  for (int i = part * kAlignThreads + threadIdx.x; i < num_blocks; i += parts * kAlignThreads) {
+  for (int i = part * NT + threadIdx.x; i < num_blocks; i += parts * NT) {
     const int pos = i * block_size;
     int lo = 0, hi = B;  // first bucket whose end is > pos
     while (lo < hi) {
@@ -158,7 +160,7 @@ __device__ __forceinline__ void fill_meta(int B, int block_size, int64_t numel, 
   }
   if (pad_sorted) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int b = part * kAlignWarps + warp; b < B; b += parts * kAlignWarps) {
+    for (int b = part * (NT / 32) + warp; b < B; b += parts * (NT / 32)) {
       const int begin = prefix[b] + tot_all[b], end = prefix[b + 1];
       for (int p = begin + lane; p < end; p += 32) sorted[p] = (int32_t)numel;
     }
@@ -256,6 +258,119 @@ __global__ void __launch_bounds__(kAlignThreads)
   scatter_chunk(ids, begin, end, span, B, wc, base, sorted);
 }
 
+// ---- numel > kLargeMin: tile-sorted scatter ---------------------------------------------------
+// With the per-warp scatter above every (CTA, warp, bucket) is an output stream of its own that grows four
+// bytes at a time; at tens of millions of ids those streams (millions of half-written 32-byte sectors) no
+// longer fit the L2 and the sort is bound by partial-sector traffic.  Here a CTA sorts a tile of kTsTile ids
+// in shared memory first (ranks from the same ballots, then a scan over the warps and over the buckets of the
+// tile) and writes each bucket's run of the tile with consecutive threads, so a CTA has one stream per bucket
+// and writes it in runs.
+constexpr int kTsThreads = 512;
+constexpr int kTsWarps = kTsThreads / 32;
+constexpr int kTsItems = 8;
+constexpr int kTsTile = kTsThreads * kTsItems;  // 4096 ids
+constexpr int64_t kLargeMin = 1 << 20;          // inputs above this take the tile-sorted path
+
+__global__ void __launch_bounds__(kTsThreads, 2)
+    moe_align_tile_scatter_kernel(const int32_t* __restrict__ ids, int64_t numel, int64_t chunk_len, int B,
+                                  int block_size, const int* __restrict__ chunk_hist, const int* __restrict__ totals,
+                                  int32_t* __restrict__ sorted, int32_t* __restrict__ expert_ids,
+                                  int32_t* __restrict__ post_pad, int32_t* __restrict__ cumsum, bool pad_sorted) {
+  extern __shared__ int smem[];
+  int* wc = smem;                        // [16][B]  per-warp counts of the tile, then exclusive over warps
+  int* tot_all = wc + kTsWarps * B;      // [B]      totals over all chunks
+  int* prefix = tot_all + B;             // [B+1]    padded starts of the buckets in the output
+  int* base = prefix + B + 1;            // [B]      where this CTA's next entry of a bucket goes
+  int* ttot = base + B;                  // [B]      totals of the tile
+  int* tstart = ttot + B;                // [B+1]    starts of the buckets inside the sorted tile
+  int* scratch = tstart + B + 1;         // [40]
+  int* val = scratch + 40;               // [kTsTile] flat indices of the tile in sorted order
+  uint16_t* bkt = reinterpret_cast<uint16_t*>(val + kTsTile);  // [kTsTile] their buckets
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  for (int b = tid; b < B; b += kTsThreads) tot_all[b] = totals[b];
+  __syncthreads();
+  padded_prefix<kTsThreads>(B, block_size, tot_all, prefix, scratch);
+  for (int b = tid; b < B; b += kTsThreads) base[b] = prefix[b] + chunk_hist[(int64_t)blockIdx.x * B + b];
+  if (blockIdx.x == 0) {
+    for (int b = tid; b <= B; b += kTsThreads) cumsum[b] = prefix[b];
+    if (tid == 0) *post_pad = prefix[B];
+  }
+  fill_meta<kTsThreads>(B, block_size, numel, prefix, tot_all, expert_ids, sorted, pad_sorted, blockIdx.x, gridDim.x);
+
+  const int64_t begin = (int64_t)blockIdx.x * chunk_len;
+  const int64_t end = begin + chunk_len < numel ? begin + chunk_len : numel;
+  const int nbits = 32 - __clz(B + 31);  // keys run up to B + 31
+  const unsigned below = (1u << lane) - 1u;
+  for (int64_t t0 = begin; t0 < end; t0 += kTsTile) {
+    for (int b = lane; b < B; b += 32) wc[warp * B + b] = 0;
+    const int64_t w0 = t0 + warp * (32 * kTsItems);
+    int key[kTsItems], loc[kTsItems];
+#pragma unroll
+    for (int j = 0; j < kTsItems; ++j) {
+      const int64_t i = w0 + j * 32 + lane;
+      int b = i < end ? ids[i] + 1 : -1;
+      if (b >= B) b = -1;
+      key[j] = b;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < kTsItems; ++j) {
+      const int b = key[j];
+      const unsigned peers = peers_of(b >= 0 ? b : B + lane, nbits);  // invalid lanes match nobody
+      int start = 0;
+      if (b >= 0) start = wc[warp * B + b];
+      __syncwarp();
+      if (b >= 0 && lane == 31 - __clz(peers)) wc[warp * B + b] = start + __popc(peers);
+      __syncwarp();
+      loc[j] = start + __popc(peers & below);
+    }
+    __syncthreads();
+    for (int b = tid; b < B; b += kTsThreads) {
+      int run = 0;
+#pragma unroll
+      for (int w = 0; w < kTsWarps; ++w) {
+        const int c = wc[w * B + b];
+        wc[w * B + b] = run;
+        run += c;
+      }
+      ttot[b] = run;
+    }
+    __syncthreads();
+    padded_prefix<kTsThreads>(B, 1, ttot, tstart, scratch);
+#pragma unroll
+    for (int j = 0; j < kTsItems; ++j) {
+      const int b = key[j];
+      if (b >= 0) {
+        const int pos = tstart[b] + wc[warp * B + b] + loc[j];
+        val[pos] = (int)(w0 + j * 32 + lane);
+        bkt[pos] = (uint16_t)b;
+      }
+    }
+    __syncthreads();
+    const int n = tstart[B];
+    for (int p = tid; p < n; p += kTsThreads) {
+      const int b = bkt[p];
+      sorted[(int64_t)base[b] + (p - tstart[b])] = val[p];
+    }
+    __syncthreads();
+    for (int b = tid; b < B; b += kTsThreads) base[b] += ttot[b];
+  }
+}
+
+static size_t tile_scatter_smem_bytes(int B) {
+  return sizeof(int) * ((size_t)kTsWarps * B + 5 * (size_t)B + 2 + 40 + kTsTile + kTsTile / 2);
+}
+
+// Chunks of the tile-sorted path: two CTAs per SM, chunk lengths a multiple of the tile (and of the histogram
+// kernel's 32 warps x 32 ids).
+static void align_plan_large(int64_t numel, int64_t* chunks, int64_t* chunk_len) {
+  int64_t len = (numel + kMaxChunks - 1) / kMaxChunks;
+  len = (len + kTsTile - 1) / kTsTile * kTsTile;
+  *chunk_len = len;
+  *chunks = (numel + len - 1) / len;
+}
+
 // How the ids are cut: number of chunks (CTAs) and ids per warp (a multiple of 32).
 static void align_plan(int64_t numel, int64_t* chunks, int* span) {
   if (numel <= kSingleMax) {
@@ -282,8 +397,13 @@ using namespace sglb200;
 extern "C" int64_t sglb200_moe_align_workspace_bytes(int64_t numel, int num_experts) {
   if (numel <= kSingleMax) return 0;
   int64_t chunks = 0;
-  int span = 0;
-  align_plan(numel, &chunks, &span);
+  if (numel > kLargeMin) {
+    int64_t chunk_len = 0;
+    align_plan_large(numel, &chunks, &chunk_len);
+  } else {
+    int span = 0;
+    align_plan(numel, &chunks, &span);
+  }
   return (chunks + 1) * (int64_t)num_experts * (int64_t)sizeof(int);
 }
 
@@ -306,6 +426,32 @@ extern "C" int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t num
     SGLB_CUDA(cudaFuncSetAttribute(moe_align_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     SGLB_CUDA(cudaFuncSetAttribute(moe_align_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     SGLB_CUDA(cudaFuncSetAttribute(moe_align_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  }
+  if (numel > kLargeMin) {
+    SGLB_REQUIRE(B < 65536, "moe_align: %d buckets exceed the 16-bit bucket field of the large-input path", B);
+    const size_t ts_smem = tile_scatter_smem_bytes(B);
+    SGLB_REQUIRE(ts_smem <= 200 * 1024, "moe_align: %d buckets need %zu bytes of shared memory (limit 200 KiB)", B,
+                 ts_smem);
+    if (ts_smem > 48 * 1024)
+      SGLB_CUDA(cudaFuncSetAttribute(moe_align_tile_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     200 * 1024));
+    int64_t lchunks = 0, chunk_len = 0;
+    align_plan_large(numel, &lchunks, &chunk_len);
+    const int64_t lneed = (lchunks + 1) * (int64_t)B * (int64_t)sizeof(int);
+    if (workspace == nullptr || workspace_bytes < lneed)
+      return fail(SGLB200_E_WORKSPACE, "moe_align: workspace of %lld bytes required, got %lld", (long long)lneed,
+                  (long long)workspace_bytes);
+    int* hist = static_cast<int*>(workspace);
+    int* tot = hist + lchunks * B;
+    moe_align_hist_kernel<<<(unsigned)lchunks, kAlignThreads, smem, st>>>(topk_ids, numel, (int)(chunk_len / kAlignWarps),
+                                                                          B, hist);
+    moe_align_scan_kernel<<<(unsigned)((B + kAlignWarps - 1) / kAlignWarps), kAlignThreads, 0, st>>>(hist, tot,
+                                                                                                     (int)lchunks, B);
+    moe_align_tile_scatter_kernel<<<(unsigned)lchunks, kTsThreads, ts_smem, st>>>(
+        topk_ids, numel, chunk_len, B, block_size, hist, tot, sorted_token_ids, expert_ids, num_tokens_post_pad,
+        cumsum_buffer, pad_sorted_token_ids != 0);
+    SGLB_CUDA(cudaGetLastError());
+    return SGLB200_OK;
   }
   int64_t chunks = 0;
   int span = 0;

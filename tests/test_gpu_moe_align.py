@@ -67,6 +67,13 @@ def test_large_input_properties(ops):
     # 3.2M ids with filtered entries: chunks longer than 8192 ids (more than two CTAs per SM otherwise)
     ids = rng.integers(-1, E, size=(400000, 8)).astype(np.int32)
     _check(ops, ids, block, E)
+    # ragged length, every id in one bucket: a tile of the large-input path is a single run
+    _check(ops, np.full((1300001, 1), 7, dtype=np.int32), 64, 16)
+    # many buckets under Zipf skew, ragged length
+    E = 1000
+    p = 1.0 / np.arange(1, E + 2) ** 1.2
+    ids = rng.choice(E + 1, size=(1500003, 1), p=p / p.sum()).astype(np.int32) - 1
+    _check(ops, ids, 128, E)
 
 
 def test_sgl_kernel_op_surface(ops):
