@@ -201,6 +201,57 @@ def moe_layer(args, ctx, peaks):
 
 
 # ------------------------------------------------------------------------------------------------
+# config 4: Qwen3-30B-A3B-shaped MoE layer under Zipf-skewed expert popularity
+# ------------------------------------------------------------------------------------------------
+
+
+def moe_layer_skewed(args, ctx, peaks):
+    """128 experts, hidden 2048, moe_intermediate 768, top-8 softmax routing; the logits carry log(p_e) with
+    p_e ~ rank^-1.2 over a seeded permutation of the experts.  Reports the layer time (max over ranks), this
+    rank's own time and the spread of tokens per local expert, i.e. the load-imbalance tail."""
+    from sglang_b200.srt.distributed import initialize_model_parallel
+    from sglang_b200.srt.layers.moe.fused_moe_triton.layer import FusedMoE
+    from sglang_b200.srt.layers.moe.token_dispatcher import StandardTopKOutput
+    from sglang_b200.srt.layers.moe.topk import fused_topk
+    from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+    rank, world, dev = ctx
+    initialize_model_parallel(1, world)
+    E, H, I, topk = 128, 2048, 768, 8
+    gen = torch.Generator(device=dev).manual_seed(41 + rank)
+    moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="nccl", device=dev)
+    _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
+    _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
+    perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))  # the same popularity order on every rank
+    logp = torch.empty(E)
+    logp[perm] = -1.2 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
+    logp = logp.to(dev)
+    res = {}
+    for T in (32, 1024, 16384):
+        x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
+        logits = torch.randn(T, E, device=dev, generator=gen) + logp
+        w, ids = fused_topk(logits, topk, True)
+        top = StandardTopKOutput(w, ids, None)
+        counts = torch.bincount(ids.flatten().long(), minlength=E).float()
+        ms = _time(lambda: moe(x, top), 10, 3, world, dev)
+        # this rank alone, without the barrier-and-max: the gap to `ms` at EP > 1 is the wait for the busiest rank
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(10):
+            moe(x, top)
+        e1.record()
+        torch.cuda.synchronize()
+        res[str(T)] = {"ms": ms, "ms_this_rank": e0.elapsed_time(e1) / 10, "tokens_per_s": world * T / ms * 1e3,
+                       "tflops_per_gpu": 6.0 * T * topk * H * I / ms / 1e9,
+                       "routed_per_expert_max_over_mean": float(counts.max() / counts.mean()),
+                       "experts_hit": int((counts > 0).sum())}
+    return {"moe_layer_skewed": {"config": "BASELINE config 4: Qwen3-30B-A3B MoE, 128 experts, hidden 2048, "
+                                           "moe_intermediate 768, top-8 softmax routing, Zipf(1.2) expert popularity, "
+                                           "tokens per GPU as keyed",
+                                 "ep": world, "scaling": "weak", "results": res}}
+
+
+# ------------------------------------------------------------------------------------------------
 # the memory-bound kernels of the path: GB/s of algorithmic bytes against the measured HBM copy rate
 # ------------------------------------------------------------------------------------------------
 
@@ -275,5 +326,7 @@ def run(sections, args, ctx, peaks):
         torch.cuda.empty_cache()
     if "moe" in sections:
         out.update(moe_layer(args, ctx, peaks))
+        torch.cuda.empty_cache()
+        out.update(moe_layer_skewed(args, ctx, peaks))
         torch.cuda.empty_cache()
     return out

@@ -47,6 +47,19 @@ __device__ __forceinline__ unsigned peers_of(int key, int nbits) {
   return peers;
 }
 
+// The same with the bit count known at compile time (fully unrolled, no loop bookkeeping).
+template <int NBITS>
+__device__ __forceinline__ unsigned peers_of_fixed(int key) {
+  unsigned peers = 0xffffffffu;
+#pragma unroll
+  for (int k = 0; k < NBITS; ++k) {
+    const bool bit = (key >> k) & 1;
+    const unsigned set = __ballot_sync(0xffffffffu, bit);
+    peers &= set ^ (bit ? 0u : 0xffffffffu);
+  }
+  return peers;
+}
+
 constexpr int kBatch = 8;  // steps whose id loads are issued together: hides the load latency of a long span
 
 // Per-warp bucket counts of the chunk [chunk_begin, chunk_end) into wc[warp][B] (smem, zeroed by caller).
@@ -271,6 +284,7 @@ constexpr int kTsItems = 8;
 constexpr int kTsTile = kTsThreads * kTsItems;  // 4096 ids
 constexpr int64_t kLargeMin = 1 << 20;          // inputs above this take the tile-sorted path
 
+template <int NBITS>
 __global__ void __launch_bounds__(kTsThreads, 2)
     moe_align_tile_scatter_kernel(const int32_t* __restrict__ ids, int64_t numel, int64_t chunk_len, int B,
                                   int block_size, const int* __restrict__ chunk_hist, const int* __restrict__ totals,
@@ -284,8 +298,7 @@ __global__ void __launch_bounds__(kTsThreads, 2)
   int* ttot = base + B;                  // [B]      totals of the tile
   int* tstart = ttot + B;                // [B+1]    starts of the buckets inside the sorted tile
   int* scratch = tstart + B + 1;         // [40]
-  int* val = scratch + 40;               // [kTsTile] flat indices of the tile in sorted order
-  uint16_t* bkt = reinterpret_cast<uint16_t*>(val + kTsTile);  // [kTsTile] their buckets
+  int* val = scratch + 40;               // [kTsTile] the tile in sorted order: bucket << 12 | index inside the tile
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   for (int b = tid; b < B; b += kTsThreads) tot_all[b] = totals[b];
@@ -300,7 +313,6 @@ __global__ void __launch_bounds__(kTsThreads, 2)
 
   const int64_t begin = (int64_t)blockIdx.x * chunk_len;
   const int64_t end = begin + chunk_len < numel ? begin + chunk_len : numel;
-  const int nbits = 32 - __clz(B + 31);  // keys run up to B + 31
   const unsigned below = (1u << lane) - 1u;
   for (int64_t t0 = begin; t0 < end; t0 += kTsTile) {
     for (int b = lane; b < B; b += 32) wc[warp * B + b] = 0;
@@ -317,7 +329,7 @@ __global__ void __launch_bounds__(kTsThreads, 2)
 #pragma unroll
     for (int j = 0; j < kTsItems; ++j) {
       const int b = key[j];
-      const unsigned peers = peers_of(b >= 0 ? b : B + lane, nbits);  // invalid lanes match nobody
+      const unsigned peers = peers_of_fixed<NBITS>(b >= 0 ? b : B + lane);  // invalid lanes match nobody
       int start = 0;
       if (b >= 0) start = wc[warp * B + b];
       __syncwarp();
@@ -343,23 +355,28 @@ __global__ void __launch_bounds__(kTsThreads, 2)
       const int b = key[j];
       if (b >= 0) {
         const int pos = tstart[b] + wc[warp * B + b] + loc[j];
-        val[pos] = (int)(w0 + j * 32 + lane);
-        bkt[pos] = (uint16_t)b;
+        val[pos] = (b << 12) | (warp * (32 * kTsItems) + j * 32 + lane);
       }
+    }
+    // ttot[b] becomes the offset from a position in the sorted tile to its place in the output
+    for (int b = tid; b < B; b += kTsThreads) {
+      const int c = ttot[b];
+      ttot[b] = base[b] - tstart[b];
+      base[b] += c;
     }
     __syncthreads();
     const int n = tstart[B];
+    const int t_lo = (int)t0;  // numel < 2^31
     for (int p = tid; p < n; p += kTsThreads) {
-      const int b = bkt[p];
-      sorted[(int64_t)base[b] + (p - tstart[b])] = val[p];
+      const int e = val[p];
+      sorted[ttot[e >> 12] + p] = t_lo + (e & (kTsTile - 1));
     }
     __syncthreads();
-    for (int b = tid; b < B; b += kTsThreads) base[b] += ttot[b];
   }
 }
 
 static size_t tile_scatter_smem_bytes(int B) {
-  return sizeof(int) * ((size_t)kTsWarps * B + 5 * (size_t)B + 2 + 40 + kTsTile + kTsTile / 2);
+  return sizeof(int) * ((size_t)kTsWarps * B + 5 * (size_t)B + 2 + 40 + kTsTile);
 }
 
 // Chunks of the tile-sorted path: two CTAs per SM, chunk lengths a multiple of the tile (and of the histogram
@@ -428,13 +445,11 @@ extern "C" int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t num
     SGLB_CUDA(cudaFuncSetAttribute(moe_align_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   }
   if (numel > kLargeMin) {
-    SGLB_REQUIRE(B < 65536, "moe_align: %d buckets exceed the 16-bit bucket field of the large-input path", B);
+    SGLB_REQUIRE(B <= 8160, "moe_align: %d buckets exceed the bucket field of the large-input path", B);
     const size_t ts_smem = tile_scatter_smem_bytes(B);
     SGLB_REQUIRE(ts_smem <= 200 * 1024, "moe_align: %d buckets need %zu bytes of shared memory (limit 200 KiB)", B,
                  ts_smem);
-    if (ts_smem > 48 * 1024)
-      SGLB_CUDA(cudaFuncSetAttribute(moe_align_tile_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     200 * 1024));
+    const int nbits = 32 - __builtin_clz((unsigned)(B + 31));  // keys run up to B + 31
     int64_t lchunks = 0, chunk_len = 0;
     align_plan_large(numel, &lchunks, &chunk_len);
     const int64_t lneed = (lchunks + 1) * (int64_t)B * (int64_t)sizeof(int);
@@ -447,9 +462,26 @@ extern "C" int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t num
                                                                           B, hist);
     moe_align_scan_kernel<<<(unsigned)((B + kAlignWarps - 1) / kAlignWarps), kAlignThreads, 0, st>>>(hist, tot,
                                                                                                      (int)lchunks, B);
-    moe_align_tile_scatter_kernel<<<(unsigned)lchunks, kTsThreads, ts_smem, st>>>(
-        topk_ids, numel, chunk_len, B, block_size, hist, tot, sorted_token_ids, expert_ids, num_tokens_post_pad,
-        cumsum_buffer, pad_sorted_token_ids != 0);
+#define SGLB_TILE_SCATTER(NB)                                                                                       \
+  case NB:                                                                                                          \
+    if (ts_smem > 48 * 1024)                                                                                        \
+      SGLB_CUDA(cudaFuncSetAttribute(moe_align_tile_scatter_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                     200 * 1024));                                                                  \
+    moe_align_tile_scatter_kernel<NB><<<(unsigned)lchunks, kTsThreads, ts_smem, st>>>(                              \
+        topk_ids, numel, chunk_len, B, block_size, hist, tot, sorted_token_ids, expert_ids, num_tokens_post_pad,    \
+        cumsum_buffer, pad_sorted_token_ids != 0);                                                                  \
+    break
+    switch (nbits) {
+      SGLB_TILE_SCATTER(6);
+      SGLB_TILE_SCATTER(7);
+      SGLB_TILE_SCATTER(8);
+      SGLB_TILE_SCATTER(9);
+      SGLB_TILE_SCATTER(10);
+      SGLB_TILE_SCATTER(11);
+      SGLB_TILE_SCATTER(12);
+      default: SGLB_TILE_SCATTER(13);
+    }
+#undef SGLB_TILE_SCATTER
     SGLB_CUDA(cudaGetLastError());
     return SGLB200_OK;
   }
