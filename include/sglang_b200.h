@@ -249,6 +249,45 @@ int sglb200_gemm_status(void);
  */
 int sglb200_stream_status(void);
 
+/*
+ * Fused row-parallel all-reduce (tensor-parallel o_proj / down): the sum over ranks of a row-parallel layer as a
+ * two-shot all-reduce whose reduce-scatter is folded into the GEMM epilogue.
+ * Replaces, for RowParallelLinear.forward (python/sglang/srt/layers/linear.py:1365-1393): the block GEMM followed
+ * by tensor_model_parallel_all_reduce (python/sglang/srt/distributed/parallel_state.py:544-623), i.e. the
+ * reference's NCCL / custom all-reduce (sgl-kernel/csrc/allreduce/custom_all_reduce.cuh) after the matmul.
+ *
+ * Peer buffers are plain device allocations shared with CUDA IPC handles (one process per GPU, one node):
+ *   sglb200_comm_alloc       zero-filled device memory for a buffer peers will touch (set-up time; synchronises)
+ *   sglb200_comm_ipc_export  64-byte handle of such a buffer, to be sent to the other ranks by any host channel
+ *   sglb200_comm_ipc_open    maps a peer's buffer into this process; sglb200_comm_ipc_close unmaps it
+ *   sglb200_comm_flag_bytes  size of the flag buffer each rank must provide (zero-filled once)
+ *
+ * sglb200_fp8_blockwise_scaled_mm_push: the dense block GEMM of this rank's K slice, M % (world * 128) == 0;
+ *   output tile rows [m0, m0+128) go to rank m0 / (M / world)'s staging buffer, block `rank`, instead of to a
+ *   local C.  stage_ptrs: HOST array of `world` device pointers, entry d = rank d's staging buffer
+ *   [world][M / world][N] of out_dtype as mapped in THIS process.  The first call for a given set of buffers and
+ *   shape allocates and fills a small device table (do it before any stream capture).
+ * sglb200_reduce_gather: after the push GEMM on the same stream.  Waits (bounded) until every rank's GEMM has
+ *   finished, sums the `world` blocks of this rank's staging buffer in rank order in float32 into
+ *   reduced_ptrs[rank] and `out`, waits for the other ranks, then copies their reduced rows from
+ *   reduced_ptrs[peer] into `out` [M][N] (private memory of this rank).  flag_ptrs[d] = rank d's flag buffer.
+ *   `epoch` must be non-zero, the same on every rank for one call and different from the previous call's
+ *   (a counter).  Every rank must make the same sequence of calls.  sglb200_comm_status() is 1 after a wait
+ *   for a peer expired (the kernel then returns without touching peer data; the output is incomplete).
+ */
+int sglb200_comm_alloc(int64_t bytes, void** out);
+int sglb200_comm_free(void* p);
+int sglb200_comm_ipc_export(void* p, void* handle64);
+int sglb200_comm_ipc_open(const void* handle64, void** out);
+int sglb200_comm_ipc_close(void* p);
+int64_t sglb200_comm_flag_bytes(void);
+int sglb200_comm_status(void);
+int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B, const float* a_s, const float* b_s,
+                                         void* const* stage_ptrs, int world, int rank, int64_t M, int64_t N, int64_t K,
+                                         int64_t as_stride_m, int64_t as_stride_k, int out_dtype, void* stream);
+int sglb200_reduce_gather(const void* stage, void* const* reduced_ptrs, void* const* flag_ptrs, void* out, int world,
+                          int rank, int64_t rows_own, int64_t N, int dtype, uint32_t epoch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,15 @@ SIGNATURES = {
     "sglb200_fp8_blockwise_grouped_mm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _i32, _vp]),
     "sglb200_gemm_status": (_i32, []),
     "sglb200_stream_status": (_i32, []),
+    "sglb200_comm_alloc": (_i32, [_i64, C.POINTER(_vp)]),
+    "sglb200_comm_free": (_i32, [_vp]),
+    "sglb200_comm_ipc_export": (_i32, [_vp, _vp]),
+    "sglb200_comm_ipc_open": (_i32, [_vp, C.POINTER(_vp)]),
+    "sglb200_comm_ipc_close": (_i32, [_vp]),
+    "sglb200_comm_flag_bytes": (_i64, []),
+    "sglb200_comm_status": (_i32, []),
+    "sglb200_fp8_blockwise_scaled_mm_push": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(_vp), _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "sglb200_reduce_gather": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp), _vp, _i32, _i32, _i64, _i64, _i32, C.c_uint32, _vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

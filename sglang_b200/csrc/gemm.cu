@@ -98,6 +98,11 @@ struct GemmParams {
   int out_fp16;
   int tma_out;                 // rows of C are written with TMA tile stores (map_c is valid)
   int group_m;                 // m-tiles per rasterization group
+  // push mode (row-parallel layers): the output rows are owned in equal blocks by `world` GPUs and each tile
+  // is stored into its owner's staging buffer [source rank][rows per owner][N] through that buffer's tensor map
+  const CUtensorMap* push_maps;  // [world] in global memory, nullptr = ordinary output through map_c
+  int push_rows_per_owner;       // a multiple of BM
+  int push_rank;                 // this GPU's slot in the owners' staging buffers
 };
 
 constexpr int kBChunk = 256;  // slabs of weight-block scales a promotion warp stages at a time
@@ -481,10 +486,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
         if (issuer && alive) {
+          const CUtensorMap* cmap = &map_c;
+          int out_row0 = m_tile * BM;
+          if (p.push_maps != nullptr) {
+            const int owner = out_row0 / p.push_rows_per_owner;
+            cmap = p.push_maps + owner;
+            out_row0 += (p.push_rank - owner) * p.push_rows_per_owner;
+          }
 #pragma unroll
           for (int g = 0; g < kOutGroups; ++g) {
             if (n_tile * BN + g * 64 < n_end)
-              ptx::tma_store_2d(&map_c, ptx::smem_u32(out_stage) + g * kOutGroupBytes, n_tile * BN + g * 64, m_tile * BM);
+              ptx::tma_store_2d(cmap, ptx::smem_u32(out_stage) + g * kOutGroupBytes, n_tile * BN + g * 64, out_row0);
           }
           ptx::tma_store_commit();
         }
@@ -514,7 +526,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 
   // ------------------------------ teardown ------------------------------
-  if (threadIdx.x == kEpiWarp0 * 32) ptx::tma_store_wait_read();  // sources stay valid until read
+  if (threadIdx.x == kEpiWarp0 * 32) {
+    if (p.push_maps != nullptr)
+      ptx::tma_store_wait_all();  // tiles pushed to other GPUs have landed before the kernel counts as finished
+    else
+      ptx::tma_store_wait_read();  // sources stay valid until read
+  }
   ptx::tc_fence_before();
   __syncthreads();
   if (ctl->abort_flag != 0 && threadIdx.x == 0) {
@@ -849,4 +866,96 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   }
   const int64_t tiles = ((max_rows + BM - 1) / BM) * p.tiles_n;
   return launch_gemm<true>(ma, mb, mc, p, tiles, static_cast<cudaStream_t>(stream));
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Push mode: the GEMM of a row-parallel layer with the reduce-scatter folded into its epilogue.
+// ---------------------------------------------------------------------------------------------
+namespace sglb200 {
+
+// Device copy of the per-owner output tensor maps, built once per (staging buffers, shape) and kept.
+struct PushKey {
+  const void* ptrs[8];
+  uint64_t N, rows;
+  int world, out_fp16;
+  bool operator==(const PushKey& o) const {
+    for (int i = 0; i < 8; ++i)
+      if (ptrs[i] != o.ptrs[i]) return false;
+    return N == o.N && rows == o.rows && world == o.world && out_fp16 == o.out_fp16;
+  }
+};
+struct PushKeyHash {
+  size_t operator()(const PushKey& k) const {
+    size_t h = k.N * 1000003u ^ k.rows;
+    for (int i = 0; i < 8; ++i) h = h * 1000003u ^ reinterpret_cast<size_t>(k.ptrs[i]);
+    return h * 31u + (size_t)k.world * 2 + (size_t)k.out_fp16;
+  }
+};
+
+static int get_push_maps(void* const* stage_ptrs, int world, uint64_t N, uint64_t rows, int out_fp16,
+                         const CUtensorMap** out) {
+  static thread_local std::unordered_map<PushKey, CUtensorMap*, PushKeyHash> cache;
+  PushKey key{};
+  for (int i = 0; i < world; ++i) key.ptrs[i] = stage_ptrs[i];
+  key.N = N, key.rows = rows, key.world = world, key.out_fp16 = out_fp16;
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return SGLB200_OK;
+  }
+  CUtensorMap host[8];
+  for (int i = 0; i < world; ++i) {
+    const int rc = get_out_map(stage_ptrs[i], N, rows, out_fp16, &host[i]);
+    if (rc) return rc;
+  }
+  CUtensorMap* dev = nullptr;
+  SGLB_CUDA(cudaMalloc(&dev, sizeof(CUtensorMap) * 8));
+  SGLB_CUDA(cudaMemcpy(dev, host, sizeof(CUtensorMap) * world, cudaMemcpyHostToDevice));
+  cache.emplace(key, dev);
+  *out = dev;
+  return SGLB200_OK;
+}
+
+}  // namespace sglb200
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B, const float* a_s, const float* b_s,
+                                                    void* const* stage_ptrs, int world, int rank, int64_t M, int64_t N,
+                                                    int64_t K, int64_t as_stride_m, int64_t as_stride_k, int out_dtype,
+                                                    void* stream) {
+  SGLB_REQUIRE(world >= 2 && world <= 8 && rank >= 0 && rank < world, "mm_push: world %d, rank %d", world, rank);
+  SGLB_REQUIRE(M > 0 && N > 0 && K > 0 && M % ((int64_t)world * BM) == 0,
+               "mm_push: M=%lld must be a positive multiple of world * %d", (long long)M, BM);
+  SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, "mm_push: K=%lld must be a multiple of 16 and N=%lld of 8", (long long)K,
+               (long long)N);
+  SGLB_REQUIRE(out_dtype == 0 || out_dtype == 1, "mm_push: out_dtype %d (0 bf16, 1 fp16)", out_dtype);
+  SGLB_REQUIRE(A && B && a_s && b_s && stage_ptrs, "mm_push: null pointer");
+  for (int i = 0; i < world; ++i)
+    SGLB_REQUIRE(stage_ptrs[i] != nullptr && aligned16(stage_ptrs[i]), "mm_push: staging buffer %d missing or unaligned", i);
+  SGLB_REQUIRE(aligned16(A) && aligned16(B), "mm_push: A and B must be 16-byte aligned");
+  SGLB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "mm_push: dimension too large");
+  CUtensorMap ma, mb;
+  int rc = get_tensor_map(A, (uint64_t)K, (uint64_t)M, 1, BM, 2, &ma);
+  if (rc) return rc;
+  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, BN, 3, &mb);
+  if (rc) return rc;
+  GemmParams p{};
+  p.a_s = a_s, p.b_s = b_s, p.C = nullptr, p.bias = nullptr;
+  p.M = M, p.N = N, p.K = K;
+  p.as_stride_m = as_stride_m, p.as_stride_k = as_stride_k;
+  p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
+  p.tiles_n = (int)((N + BN - 1) / BN);
+  p.group_m = choose_group_m(M, K);
+  p.out_fp16 = out_dtype;
+  const int64_t tiles = (M / BM) * p.tiles_n;
+  p.full_units = (int)tiles, p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;  // one unit per tile
+  p.tma_out = 1;
+  // every owner's staging buffer is [world][M / world][N]: M rows in all
+  rc = get_push_maps(stage_ptrs, world, (uint64_t)N, (uint64_t)M, out_dtype, &p.push_maps);
+  if (rc) return rc;
+  p.push_rows_per_owner = (int)(M / world), p.push_rank = rank;
+  CUtensorMap mc = {};
+  rc = get_out_map(stage_ptrs[rank], (uint64_t)N, (uint64_t)M, out_dtype, &mc);  // unused by the stores; keeps map_c valid
+  if (rc) return rc;
+  return launch_gemm<false>(ma, mb, mc, p, tiles, static_cast<cudaStream_t>(stream));
 }

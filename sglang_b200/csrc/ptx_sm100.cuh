@@ -111,6 +111,9 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 // Returns once every committed store of this thread has finished READING shared memory (the source may be
 // overwritten; the global writes complete on their own).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Returns once every committed store of this thread has been performed (used before the kernel ends when the
+// destination is another GPU's memory and a later kernel tells that GPU that the data is there).
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Orders this thread's ordinary shared-memory writes before later reads by the TMA engine.
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void sts_128(uint32_t addr, uint4 v) {

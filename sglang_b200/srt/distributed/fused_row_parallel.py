@@ -1,0 +1,108 @@
+"""GEMM-fused all-reduce for row-parallel block-FP8 linears on one NVSwitch node.
+
+Stands where the reference runs the block GEMM and then `tensor_model_parallel_all_reduce`
+(python/sglang/srt/layers/linear.py:1365-1393, python/sglang/srt/distributed/parallel_state.py:544-623; its
+custom all-reduce with IPC-registered buffers is sgl-kernel/csrc/allreduce/custom_all_reduce.cuh).  Here the
+all-reduce is two-shot and its first shot happens inside the GEMM: each output tile is stored by the GEMM's
+epilogue into the staging buffer of the rank that owns those rows, while later tiles are still being computed;
+one more kernel sums the staged blocks in rank order and fetches the other ranks' reduced rows with peer loads.
+Every rank ends with bit-identical rows (the NCCL ring does not promise that).
+
+Buffers that peers touch come from the library's own `cudaMalloc` and travel as CUDA IPC handles through the
+group's `all_gather_object`; one process drives one GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..._lib import check, lib
+
+_BM = 128  # rows of a GEMM output tile: ownership of output rows changes on these boundaries
+
+
+def _alloc(nbytes: int) -> int:
+    p = C.c_void_p()
+    check(lib.sglb200_comm_alloc(nbytes, C.byref(p)))
+    return p.value
+
+
+def _exchange(group, world: int, rank: int, ptr: int) -> List[int]:
+    """Device pointers of every rank's buffer as mapped in this process (own pointer for `rank`)."""
+    handle = (C.c_char * 64)()
+    check(lib.sglb200_comm_ipc_export(ptr, handle))
+    handles: List[Optional[bytes]] = [None] * world
+    dist.all_gather_object(handles, bytes(handle.raw), group=group)
+    out = []
+    for r, h in enumerate(handles):
+        if r == rank:
+            out.append(ptr)
+            continue
+        q = C.c_void_p()
+        buf = (C.c_char * 64).from_buffer_copy(h)
+        check(lib.sglb200_comm_ipc_open(buf, C.byref(q)))
+        out.append(q.value)
+    return out
+
+
+class FusedRowParallelComm:
+    """Staging, reduced-row and flag buffers of one tensor-parallel group, sized for `max_elems` output elements."""
+
+    def __init__(self, group, world: int, rank: int, max_elems: int, device: torch.device):
+        assert 2 <= world <= 8
+        self.group, self.world, self.rank, self.device = group, world, rank, device
+        self.max_elems = int(max_elems)
+        with torch.cuda.device(device):
+            self._stage = _alloc(self.max_elems * 2)
+            self._reduced = _alloc((self.max_elems + world - 1) // world * 2)
+            self._flags = _alloc(lib.sglb200_comm_flag_bytes())
+            self.stage_ptrs = _exchange(group, world, rank, self._stage)
+            self.reduced_ptrs = _exchange(group, world, rank, self._reduced)
+            self.flag_ptrs = _exchange(group, world, rank, self._flags)
+        arr = C.c_void_p * world
+        self._stage_arr = arr(*self.stage_ptrs)
+        self._reduced_arr = arr(*self.reduced_ptrs)
+        self._flag_arr = arr(*self.flag_ptrs)
+        self.epoch = 0
+        dist.barrier(group=group)  # nobody launches before every rank has mapped every buffer
+
+    def supports(self, M: int, N: int) -> bool:
+        return M > 0 and M % (self.world * _BM) == 0 and N % 8 == 0 and M * N <= self.max_elems
+
+    def linear(self, xq: torch.Tensor, xs: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor,
+               out_dtype: torch.dtype) -> torch.Tensor:
+        """sum over ranks of blockscaled(xq, weight): xq [M, K_local] e4m3, xs [M, K_local/128] float32."""
+        M, K = xq.shape
+        N = weight.shape[0]
+        if not self.supports(M, N):
+            raise RuntimeError(f"fused row-parallel all-reduce does not take M={M}, N={N} at world {self.world}")
+        stream = torch.cuda.current_stream(xq.device).cuda_stream
+        dt = 0 if out_dtype == torch.bfloat16 else 1
+        check(lib.sglb200_fp8_blockwise_scaled_mm_push(
+            xq.data_ptr(), weight.data_ptr(), xs.data_ptr(), weight_scale.data_ptr(), self._stage_arr, self.world,
+            self.rank, M, N, K, xs.stride(0), xs.stride(1), dt, stream))
+        out = torch.empty(M, N, device=xq.device, dtype=out_dtype)
+        self.epoch = self.epoch % 0x7FFFFFFF + 1  # never 0, never equal to the previous call's
+        check(lib.sglb200_reduce_gather(
+            self._stage, self._reduced_arr, self._flag_arr, out.data_ptr(), self.world, self.rank, M // self.world, N,
+            dt, self.epoch, stream))
+        return out
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for ptrs in (self.stage_ptrs, self.reduced_ptrs, self.flag_ptrs):
+            for r, p in enumerate(ptrs):
+                if r != self.rank:
+                    check(lib.sglb200_comm_ipc_close(p))
+        dist.barrier(group=self.group)
+        for p in (self._stage, self._reduced, self._flags):
+            check(lib.sglb200_comm_free(p))
+
+
+def comm_status() -> int:
+    """0, or 1 if a wait for a peer's flag inside the reduce kernel expired since the library was loaded."""
+    return lib.sglb200_comm_status()

@@ -70,9 +70,36 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, expert_model_
 
 
 def destroy_model_parallel() -> None:
-    global _TP, _MOE_EP
+    global _TP, _MOE_EP, _FUSED_ROW
+    if _FUSED_ROW is not None:
+        _FUSED_ROW.close()
+        _FUSED_ROW = None
     _TP = None
     _MOE_EP = None
+
+
+_FUSED_ROW = None
+
+
+def enable_fused_row_parallel(max_elems: int, device=None):
+    """Row-parallel linears of the tensor-parallel group sum their partial outputs with the GEMM-fused all-reduce
+    (`fused_row_parallel.FusedRowParallelComm`) whenever the output has at most `max_elems` elements and its row
+    count is a multiple of 128 x world; other shapes keep the NCCL all-reduce.  Collective: every rank of the
+    group calls it, after `initialize_model_parallel`.  Returns the communicator (None for a single rank)."""
+    global _FUSED_ROW
+    tp = get_tp_group()
+    if tp.world_size == 1:
+        return None
+    from .fused_row_parallel import FusedRowParallelComm
+
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    _FUSED_ROW = FusedRowParallelComm(tp.device_group, tp.world_size, tp.rank_in_group, max_elems, device)
+    return _FUSED_ROW
+
+
+def get_fused_row_parallel():
+    return _FUSED_ROW
 
 
 def get_tp_group() -> GroupCoordinator:

@@ -15,10 +15,12 @@ import torch
 from torch import nn
 
 from ..distributed import (
+    get_fused_row_parallel,
     get_tensor_model_parallel_rank,
     get_tensor_model_parallel_world_size,
     tensor_model_parallel_all_reduce,
 )
+from .quantization.fp8_kernel import per_token_group_quant_fp8
 
 
 def divide(a: int, b: int) -> int:
@@ -115,6 +117,23 @@ class RowParallelLinear(LinearBase):
             x = x[..., self.tp_rank * k : (self.tp_rank + 1) * k].contiguous()
         # bias is added by rank 0 only so that the all-reduce counts it once (linear.py:1376-1378)
         bias = self.bias if (self.tp_rank == 0 or self.tp_size == 1) else None
+        fused = get_fused_row_parallel() if (self.reduce_results and self.tp_size > 1 and self.bias is None) else None
+        if fused is not None and getattr(self.quant_method, "block_quant", False):
+            # GEMM with the reduce-scatter in its epilogue, then one reduce-and-gather kernel over peer memory
+            xq, xs = x if isinstance(x, tuple) else (None, None)
+            lead = (xq if xq is not None else x).shape[:-1]
+            rows = 1
+            for d in lead:
+                rows *= d
+            if fused.supports(rows, self.output_size):
+                if xq is None:
+                    x2 = x.reshape(rows, x.shape[-1])
+                    xq, xs = per_token_group_quant_fp8(x2, self.quant_method.quant_config.weight_block_size[1])
+                    out_dtype = x.dtype
+                else:
+                    xq, xs, out_dtype = xq.reshape(rows, -1), xs.reshape(rows, -1), torch.bfloat16
+                out = fused.linear(xq, xs, self.weight, self.weight_scale_inv, out_dtype)
+                return out.view(*lead, self.output_size), None
         out = self.quant_method.apply(self, x, bias)
         if self.reduce_results and self.tp_size > 1:
             out = tensor_model_parallel_all_reduce(out)

@@ -107,3 +107,57 @@ def test_tp_and_ep_on_two_gpus():
     ref0 = O.fused_experts_block_fp8(ret[0]["x"], w13q, w13s, wdq, wds, ret[0]["tw"], ret[0]["ti"], 1.0)
     for r in range(world):
         assert_close_fp(ret[r]["moe_std"], ref0, rtol=2e-2, atol=2e-2)
+
+
+def _fused_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from sglang_b200 import ops
+        from sglang_b200.srt.distributed import (destroy_model_parallel, enable_fused_row_parallel,
+                                                 initialize_model_parallel)
+        from sglang_b200.srt.distributed.fused_row_parallel import comm_status
+        from sglang_b200.srt.layers.linear import RowParallelLinear
+        from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+        initialize_model_parallel(world, 1)
+        K, N = 1024, 712  # N is not a multiple of the 192-column tile nor of its 64-column store groups
+        wq, ws = make_weight(N, K, 21)
+        down = RowParallelLinear(K, N, quant_config=Fp8Config(), device=dev)
+        down.load_full_weight(codes_to_fp8(wq, dev), torch.from_numpy(ws).to(dev))
+        k = K // world
+        xs = [make_act(M, K, 30 + i, outliers=False)[:, rank * k : (rank + 1) * k].contiguous().to(dev)
+              for i, M in enumerate((512, 256, 70, 1024))]
+        nccl = [down(x)[0].clone() for x in xs]            # plain path: GEMM, then NCCL all-reduce
+        comm = enable_fused_row_parallel(1024 * N)
+        assert comm.supports(512, N) and comm.supports(1024, N) and not comm.supports(70, N)
+        fused = [down(x)[0].clone() for x in xs]           # 70 rows fall back to the plain path
+        fused2 = [down(x)[0].clone() for x in xs]          # flags and staging are reused by later calls
+        torch.cuda.synchronize()
+        ret[rank] = dict(nccl=[t.float().cpu().numpy() for t in nccl], fused=[t.float().cpu().numpy() for t in fused],
+                         again=all(torch.equal(a, b) for a, b in zip(fused, fused2)),
+                         status=(ops.gemm_status(), comm_status()))
+        destroy_model_parallel()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_row_parallel_all_reduce_on_two_gpus():
+    """The GEMM whose epilogue pushes tiles to their owner + the reduce-and-gather kernel against GEMM + NCCL."""
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_fused_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    K, N = 1024, 712
+    wq, ws = make_weight(N, K, 21)
+    for r in range(world):
+        assert ret[r]["status"] == (0, 0) and ret[r]["again"]
+    for i, M in enumerate((512, 256, 70, 1024)):
+        # with two ranks, adding two bf16 partial sums in float32 and rounding once is what NCCL's bf16 sum does too
+        for r in range(world):
+            assert np.array_equal(ret[r]["fused"][i], ret[r]["nccl"][i])
+        assert np.array_equal(ret[0]["fused"][i], ret[1]["fused"][i])
+        x = to_f32_np(make_act(M, K, 30 + i, outliers=False))
+        assert_close_fp(ret[0]["fused"][i], O.block_fp8_linear(x, wq, ws), rtol=2e-2, atol=2e-2, min_cos=0.9995)
