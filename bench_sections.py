@@ -131,23 +131,48 @@ def tp_layer(args, ctx, peaks):
         _fill_weight(lin.weight.data, lin.weight_scale_inv.data, gen)
     flops_per_token = 2.0 * (H * (heads + 2 * kv_heads) * hd + heads * hd * H + H * 2 * I + I * H)
     res = {}
-    for M in (8, 128, 2048, 8192):
-        x = torch.randn(M, H, device=dev, generator=gen).bfloat16()
-        attn = torch.randn(M, heads * hd // world, device=dev, generator=gen).bfloat16()
+    sizes = (8, 128, 2048, 8192)
+    inputs = {M: (torch.randn(M, H, device=dev, generator=gen).bfloat16(),
+                  torch.randn(M, heads * hd // world, device=dev, generator=gen).bfloat16()) for M in sizes}
 
-        def layer():
-            qkv(x)
-            h, _ = o_proj(attn)
-            gu, _ = gate_up(h)
-            act = torch.empty(M, gu.shape[1] // 2, device=dev, dtype=gu.dtype)
-            ops.silu_and_mul_out(act, gu)
-            down(act)
+    def run_all(key):
+        for M in sizes:
+            x, attn = inputs[M]
 
-        ms = _time(layer, 10 if M >= 2048 else 20, 3, world, dev)
-        res[str(M)] = {"ms": ms, "tflops": flops_per_token * M / ms / 1e9, "allreduce_bytes": 2 * M * H * 2}
+            def layer():
+                qkv(x)
+                h, _ = o_proj(attn)
+                gu, _ = gate_up(h)
+                act = torch.empty(M, gu.shape[1] // 2, device=dev, dtype=gu.dtype)
+                ops.silu_and_mul_out(act, gu)
+                down(act)
+
+            ms = _time(layer, 10 if M >= 2048 else 20, 3, world, dev)
+            res.setdefault(str(M), {"allreduce_bytes": 2 * M * H * 2})[key] = ms
+
+    run_all("ms_nccl" if world > 1 else "ms")
+    if world > 1:
+        # the same layer with the all-reduce of o_proj and down fused into their GEMMs where the shape allows
+        # (rows a multiple of 128 x world); other sizes keep the NCCL all-reduce and repeat the number above
+        from sglang_b200.srt.distributed import destroy_model_parallel, enable_fused_row_parallel
+        from sglang_b200.srt.distributed.fused_row_parallel import comm_status
+        comm = enable_fused_row_parallel(max(sizes) * H)
+        run_all("ms_fused")
+        for M in sizes:
+            r = res[str(M)]
+            r["fused_all_reduce"] = bool(comm.supports(M, H))
+            r["ms"] = r["ms_fused"] if r["fused_all_reduce"] else r["ms_nccl"]
+        status = comm_status()
+        destroy_model_parallel()
+    else:
+        status = 0
+    for M in sizes:
+        res[str(M)]["tflops"] = flops_per_token * M / res[str(M)]["ms"] / 1e9
     return {"tp_layer": {"config": "BASELINE config 2: Llama-3-70B layer (hidden 8192, inter 28672, 64q/8kv x 128), "
-                                   "QKV + gate_up column-parallel, o_proj + down row-parallel with NCCL all-reduce",
-                         "tp": world, "scaling": "strong", "results": res}}
+                                   "QKV + gate_up column-parallel, o_proj + down row-parallel; the sum over ranks is "
+                                   "an NCCL all-reduce (ms_nccl) or the GEMM-fused all-reduce over peer memory "
+                                   "(ms_fused); ms is the fused form where the shape allows it",
+                         "tp": world, "scaling": "strong", "comm_status": status, "results": res}}
 
 
 # ------------------------------------------------------------------------------------------------

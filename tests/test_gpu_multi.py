@@ -109,6 +109,10 @@ def test_tp_and_ep_on_two_gpus():
         assert_close_fp(ret[r]["moe_std"], ref0, rtol=2e-2, atol=2e-2)
 
 
+def _fused_sizes(world):
+    return (4 * 128 * world // 2, 128 * world, 70, 4 * 128 * world)
+
+
 def _fused_worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -127,11 +131,12 @@ def _fused_worker(rank, world, port, ret):
         down = RowParallelLinear(K, N, quant_config=Fp8Config(), device=dev)
         down.load_full_weight(codes_to_fp8(wq, dev), torch.from_numpy(ws).to(dev))
         k = K // world
+        sizes = _fused_sizes(world)
         xs = [make_act(M, K, 30 + i, outliers=False)[:, rank * k : (rank + 1) * k].contiguous().to(dev)
-              for i, M in enumerate((512, 256, 70, 1024))]
+              for i, M in enumerate(sizes)]
         nccl = [down(x)[0].clone() for x in xs]            # plain path: GEMM, then NCCL all-reduce
-        comm = enable_fused_row_parallel(1024 * N)
-        assert comm.supports(512, N) and comm.supports(1024, N) and not comm.supports(70, N)
+        comm = enable_fused_row_parallel(max(sizes) * N)
+        assert comm.supports(sizes[0], N) and comm.supports(sizes[3], N) and not comm.supports(70, N)
         fused = [down(x)[0].clone() for x in xs]           # 70 rows fall back to the plain path
         fused2 = [down(x)[0].clone() for x in xs]          # flags and staging are reused by later calls
         torch.cuda.synchronize()
@@ -143,10 +148,7 @@ def _fused_worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fused_row_parallel_all_reduce_on_two_gpus():
-    """The GEMM whose epilogue pushes tiles to their owner + the reduce-and-gather kernel against GEMM + NCCL."""
-    world = 2
+def _check_fused(world):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_fused_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
@@ -154,10 +156,23 @@ def test_fused_row_parallel_all_reduce_on_two_gpus():
     wq, ws = make_weight(N, K, 21)
     for r in range(world):
         assert ret[r]["status"] == (0, 0) and ret[r]["again"]
-    for i, M in enumerate((512, 256, 70, 1024)):
-        # with two ranks, adding two bf16 partial sums in float32 and rounding once is what NCCL's bf16 sum does too
+    for i, M in enumerate(_fused_sizes(world)):
         for r in range(world):
-            assert np.array_equal(ret[r]["fused"][i], ret[r]["nccl"][i])
-        assert np.array_equal(ret[0]["fused"][i], ret[1]["fused"][i])
+            if world == 2 or M == 70:
+                # with two ranks, adding two bf16 partial sums in float32 and rounding once is what NCCL's bf16 sum does
+                assert np.array_equal(ret[r]["fused"][i], ret[r]["nccl"][i])
+            if M != 70:  # (the ring all-reduce of the plain path does not promise identical rows on every rank)
+                assert np.array_equal(ret[r]["fused"][i], ret[0]["fused"][i])
         x = to_f32_np(make_act(M, K, 30 + i, outliers=False))
         assert_close_fp(ret[0]["fused"][i], O.block_fp8_linear(x, wq, ws), rtol=2e-2, atol=2e-2, min_cos=0.9995)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_row_parallel_all_reduce_on_two_gpus():
+    """The GEMM whose epilogue pushes tiles to their owner + the reduce-and-gather kernel against GEMM + NCCL."""
+    _check_fused(2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs or more")
+def test_fused_row_parallel_all_reduce_on_all_gpus():
+    _check_fused(8 if torch.cuda.device_count() >= 8 else 4)
