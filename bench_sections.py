@@ -39,6 +39,20 @@ def _time(fn, iters, warmup, world, dev):
     return _max_ms(e0.elapsed_time(e1) / iters, world, dev)
 
 
+def _time_graph(fn, iters, warmup, dev):
+    """One call of `fn` captured into a CUDA graph and replayed: the launch-bound small-batch sizes are served from
+    graphs (as the reference serves its decode batches), so their eager time measures Python, not the GPU."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    ms = _time(g.replay, iters, 2, 1, dev)
+    del g
+    return ms
+
+
 def _fill_weight(dst_q, dst_s, gen, std=0.02, chunk=8):
     """Random N(0,std) weights quantised per 128x128 block, written expert-chunk by expert-chunk."""
     from bench import make_block_fp8_weight
@@ -149,6 +163,10 @@ def tp_layer(args, ctx, peaks):
 
             ms = _time(layer, 10 if M >= 2048 else 20, 3, world, dev)
             res.setdefault(str(M), {"allreduce_bytes": 2 * M * H * 2})[key] = ms
+            if world == 1 and M <= 128:
+                res[str(M)]["ms_eager"] = ms
+                res[str(M)][key] = _time_graph(layer, 20, 3, dev)
+                res[str(M)]["launch"] = "cuda graph"
 
     run_all("ms_nccl" if world > 1 else "ms")
     if world > 1:
@@ -217,8 +235,12 @@ def moe_layer(args, ctx, peaks):
             return routed + shared
 
         ms = _time(layer, 10, 3, world, dev)
+        extra = {}
+        if world == 1 and T <= 512:
+            extra = {"ms_eager": ms, "launch": "cuda graph"}
+            ms = _time_graph(layer, 10, 3, dev)
         flops = 6.0 * T * topk * H * I + 6.0 * T * H * I
-        res[str(T)] = {"ms": ms, "tokens_per_s": world * T / ms * 1e3, "tflops_per_gpu": flops / ms / 1e9}
+        res[str(T)] = {"ms": ms, "tokens_per_s": world * T / ms * 1e3, "tflops_per_gpu": flops / ms / 1e9, **extra}
     return {"moe_layer": {"config": "BASELINE config 3: DeepSeek-V3 MoE, 256 routed experts + 1 shared, hidden 7168, "
                                     "moe_intermediate 2048, top-8 grouped sigmoid routing (8 groups, top-4), "
                                     "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine",
@@ -258,6 +280,10 @@ def moe_layer_skewed(args, ctx, peaks):
         top = StandardTopKOutput(w, ids, None)
         counts = torch.bincount(ids.flatten().long(), minlength=E).float()
         ms = _time(lambda: moe(x, top), 10, 3, world, dev)
+        extra = {}
+        if world == 1 and T <= 1024:
+            extra = {"ms_eager": ms, "launch": "cuda graph"}
+            ms = _time_graph(lambda: moe(x, top), 10, 3, dev)
         # this rank alone, without the barrier-and-max: the gap to `ms` at EP > 1 is the wait for the busiest rank
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -269,7 +295,7 @@ def moe_layer_skewed(args, ctx, peaks):
         res[str(T)] = {"ms": ms, "ms_this_rank": e0.elapsed_time(e1) / 10, "tokens_per_s": world * T / ms * 1e3,
                        "tflops_per_gpu": 6.0 * T * topk * H * I / ms / 1e9,
                        "routed_per_expert_max_over_mean": float(counts.max() / counts.mean()),
-                       "experts_hit": int((counts > 0).sum())}
+                       "experts_hit": int((counts > 0).sum()), **extra}
     return {"moe_layer_skewed": {"config": "BASELINE config 4: Qwen3-30B-A3B MoE, 128 experts, hidden 2048, "
                                            "moe_intermediate 768, top-8 softmax routing, Zipf(1.2) expert popularity, "
                                            "tokens per GPU as keyed",
