@@ -272,7 +272,10 @@ int sglb200_stream_status(void);
  *   reduced_ptrs[rank] and `out`, waits for the other ranks, then copies their reduced rows from
  *   reduced_ptrs[peer] into `out` [M][N] (private memory of this rank).  flag_ptrs[d] = rank d's flag buffer.
  *   `epoch` must be non-zero, the same on every rank for one call and different from the previous call's
- *   (a counter).  Every rank must make the same sequence of calls.  sglb200_comm_status() is 1 after a wait
+ *   (a counter).  Every rank must make the same sequence of calls.
+ *   Pipelining over row chunks: `sm_margin` SMs are left free by the push GEMM and `max_blocks` (> 0; the same on
+ *   every rank) caps the CTAs of sglb200_reduce_gather, so that the reduce-and-gather of chunk c (issued on a second
+ *   stream, on its own slices of the buffers) runs beside the GEMM of chunk c + 1.  0 / 0 = no pipelining.  sglb200_comm_status() is 1 after a wait
  *   for a peer expired (the kernel then returns without touching peer data; the output is incomplete).
  */
 int sglb200_comm_alloc(int64_t bytes, void** out);
@@ -284,9 +287,11 @@ int64_t sglb200_comm_flag_bytes(void);
 int sglb200_comm_status(void);
 int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B, const float* a_s, const float* b_s,
                                          void* const* stage_ptrs, int world, int rank, int64_t M, int64_t N, int64_t K,
-                                         int64_t as_stride_m, int64_t as_stride_k, int out_dtype, void* stream);
+                                         int64_t as_stride_m, int64_t as_stride_k, int out_dtype, int sm_margin,
+                                         void* stream);
 int sglb200_reduce_gather(const void* stage, void* const* reduced_ptrs, void* const* flag_ptrs, void* out, int world,
-                          int rank, int64_t rows_own, int64_t N, int dtype, uint32_t epoch, void* stream);
+                          int rank, int64_t rows_own, int64_t N, int dtype, uint32_t epoch, int max_blocks,
+                          void* stream);
 
 #ifdef __cplusplus
 }

@@ -133,9 +133,13 @@ __global__ void __launch_bounds__(kCommThreads)
     const uint4* src = reinterpret_cast<const uint4*>(c.reduced[peer]);
     uint4* dst = out4 + (int64_t)peer * chunks;
     int64_t i = (int64_t)blockIdx.x * kCommThreads + threadIdx.x;
-    for (; i + 3 * stride < chunks; i += 4 * stride) {  // four loads in flight per thread
-      const uint4 a = src[i], b = src[i + stride], e = src[i + 2 * stride], f = src[i + 3 * stride];
-      dst[i] = a, dst[i + stride] = b, dst[i + 2 * stride] = e, dst[i + 3 * stride] = f;
+    constexpr int kFlight = 8;  // peer loads in flight per thread: a small grid must still cover the NVLink latency
+    for (; i + (kFlight - 1) * stride < chunks; i += kFlight * stride) {
+      uint4 v[kFlight];
+#pragma unroll
+      for (int k = 0; k < kFlight; ++k) v[k] = src[i + k * stride];
+#pragma unroll
+      for (int k = 0; k < kFlight; ++k) dst[i + k * stride] = v[k];
     }
     for (; i < chunks; i += stride) dst[i] = src[i];
   }
@@ -194,7 +198,7 @@ extern "C" int sglb200_comm_status(void) {
 
 extern "C" int sglb200_reduce_gather(const void* stage, void* const* reduced_ptrs, void* const* flag_ptrs, void* out,
                                      int world, int rank, int64_t rows_own, int64_t N, int dtype, uint32_t epoch,
-                                     void* stream) {
+                                     int max_blocks, void* stream) {
   SGLB_REQUIRE(world >= 2 && world <= kCommMaxWorld && rank >= 0 && rank < world, "reduce_gather: world %d, rank %d",
                world, rank);
   SGLB_REQUIRE(rows_own > 0 && N > 0 && N % 8 == 0, "reduce_gather: rows %lld, N %lld (N must be a multiple of 8)",
@@ -215,6 +219,7 @@ extern "C" int sglb200_reduce_gather(const void* stage, void* const* reduced_ptr
   const int sms = sm_count();
   if (blocks > sms) blocks = sms;
   if (blocks > kCommMaxBlocks) blocks = kCommMaxBlocks;
+  if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;  // (the same on every rank: block b pairs with block b)
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
     reduce_gather_kernel<false><<<(unsigned)blocks, kCommThreads, 0, st>>>(c, static_cast<uint16_t*>(out), chunks, world,

@@ -738,7 +738,7 @@ static size_t gemm_smem_bytes() { return (size_t)kStages * kStageBytes + kOutByt
 
 template <bool kGrouped>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const GemmParams& p,
-                       int64_t max_tiles, cudaStream_t st) {
+                       int64_t max_tiles, cudaStream_t st, int sm_margin = 0) {
   const size_t smem = gemm_smem_bytes();
   static thread_local bool attr_set[64] = {false};  // the opt-in is per function and per device
   int dev = 0;
@@ -748,7 +748,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
                                    (int)smem));
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
-  const int sms = sm_count();
+  int sms = sm_count() - sm_margin;  // SMs left free run a concurrent kernel (the reduce-and-gather of an earlier chunk)
+  if (sms < 1) sms = 1;
   const unsigned grid = (unsigned)(max_tiles < sms ? max_tiles : sms);
   fp8_blockscale_gemm_kernel<kGrouped><<<grid, kGemmThreads, smem, st>>>(ma, mb, mc, p);
   SGLB_CUDA(cudaGetLastError());
@@ -922,8 +923,9 @@ static int get_push_maps(void* const* stage_ptrs, int world, uint64_t N, uint64_
 extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B, const float* a_s, const float* b_s,
                                                     void* const* stage_ptrs, int world, int rank, int64_t M, int64_t N,
                                                     int64_t K, int64_t as_stride_m, int64_t as_stride_k, int out_dtype,
-                                                    void* stream) {
+                                                    int sm_margin, void* stream) {
   SGLB_REQUIRE(world >= 2 && world <= 8 && rank >= 0 && rank < world, "mm_push: world %d, rank %d", world, rank);
+  SGLB_REQUIRE(sm_margin >= 0 && sm_margin < sm_count(), "mm_push: sm_margin %d", sm_margin);
   SGLB_REQUIRE(M > 0 && N > 0 && K > 0 && M % ((int64_t)world * BM) == 0,
                "mm_push: M=%lld must be a positive multiple of world * %d", (long long)M, BM);
   SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, "mm_push: K=%lld must be a multiple of 16 and N=%lld of 8", (long long)K,
@@ -957,5 +959,5 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B
   CUtensorMap mc = {};
   rc = get_out_map(stage_ptrs[rank], (uint64_t)N, (uint64_t)M, out_dtype, &mc);  // unused by the stores; keeps map_c valid
   if (rc) return rc;
-  return launch_gemm<false>(ma, mb, mc, p, tiles, static_cast<cudaStream_t>(stream));
+  return launch_gemm<false>(ma, mb, mc, p, tiles, static_cast<cudaStream_t>(stream), sm_margin);
 }

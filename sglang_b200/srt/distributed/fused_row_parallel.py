@@ -67,10 +67,26 @@ class FusedRowParallelComm:
         self._reduced_arr = arr(*self.reduced_ptrs)
         self._flag_arr = arr(*self.flag_ptrs)
         self.epoch = 0
+        self.pipeline = True     # large outputs are cut into row chunks (see `_chunks`)
+        self.min_waves = 3       # a chunk keeps at least this many waves of GEMM tiles
+        self.sm_margin = 16      # SMs the GEMM of a later chunk leaves to the reduce-and-gather of an earlier one
+        self.sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self._side = torch.cuda.Stream(device=device, priority=-1)
         dist.barrier(group=group)  # nobody launches before every rank has mapped every buffer
 
     def supports(self, M: int, N: int) -> bool:
         return M > 0 and M % (self.world * _BM) == 0 and N % 8 == 0 and M * N <= self.max_elems
+
+    def _chunks(self, M: int, N: int) -> int:
+        """Row chunks to pipeline over: the reduce-and-gather of chunk c runs beside the GEMM of chunk c + 1 on the
+        SMs that GEMM leaves free.  Chunks keep at least `min_waves` waves of GEMM tiles each."""
+        if not self.pipeline:
+            return 1
+        tiles_n = (N + 191) // 192
+        for c in (4, 2):
+            if M % (c * self.world * _BM) == 0 and (M // c // _BM) * tiles_n >= self.min_waves * (self.sms - self.sm_margin):
+                return c
+        return 1
 
     def linear(self, xq: torch.Tensor, xs: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor,
                out_dtype: torch.dtype) -> torch.Tensor:
@@ -79,16 +95,38 @@ class FusedRowParallelComm:
         N = weight.shape[0]
         if not self.supports(M, N):
             raise RuntimeError(f"fused row-parallel all-reduce does not take M={M}, N={N} at world {self.world}")
-        stream = torch.cuda.current_stream(xq.device).cuda_stream
+        if not (xq.is_contiguous() and xs.is_contiguous()):
+            xq, xs = xq.contiguous(), xs.contiguous()
+        main = torch.cuda.current_stream(xq.device)
         dt = 0 if out_dtype == torch.bfloat16 else 1
-        check(lib.sglb200_fp8_blockwise_scaled_mm_push(
-            xq.data_ptr(), weight.data_ptr(), xs.data_ptr(), weight_scale.data_ptr(), self._stage_arr, self.world,
-            self.rank, M, N, K, xs.stride(0), xs.stride(1), dt, stream))
         out = torch.empty(M, N, device=xq.device, dtype=out_dtype)
-        self.epoch = self.epoch % 0x7FFFFFFF + 1  # never 0, never equal to the previous call's
-        check(lib.sglb200_reduce_gather(
-            self._stage, self._reduced_arr, self._flag_arr, out.data_ptr(), self.world, self.rank, M // self.world, N,
-            dt, self.epoch, stream))
+        C_ = self._chunks(M, N)
+        Mc = M // C_
+        arr = C.c_void_p * self.world
+        side = self._side if C_ > 1 else main
+        if C_ > 1:
+            out.record_stream(side)
+        for c in range(C_):
+            stage_off, red_off = c * Mc * N * 2, c * (Mc // self.world) * N * 2
+            stage = self._stage_arr if C_ == 1 else arr(*[p + stage_off for p in self.stage_ptrs])
+            reduced = self._reduced_arr if C_ == 1 else arr(*[p + red_off for p in self.reduced_ptrs])
+            check(lib.sglb200_fp8_blockwise_scaled_mm_push(
+                xq.data_ptr() + c * Mc * K, weight.data_ptr(), xs.data_ptr() + c * Mc * xs.stride(0) * 4,
+                weight_scale.data_ptr(), stage, self.world, self.rank, Mc, N, K, xs.stride(0), xs.stride(1), dt,
+                self.sm_margin if c > 0 else 0, main.cuda_stream))
+            if C_ > 1:
+                ev = torch.cuda.Event()
+                ev.record(main)
+                side.wait_event(ev)
+            self.epoch = self.epoch % 0x7FFFFFFF + 1  # never 0, never equal to the previous call's
+            check(lib.sglb200_reduce_gather(
+                self._stage + stage_off, reduced, self._flag_arr, out.data_ptr() + c * Mc * N * 2, self.world,
+                self.rank, Mc // self.world, N, dt, self.epoch, self.sm_margin if c < C_ - 1 else 0,
+                side.cuda_stream))
+        if C_ > 1:
+            done = torch.cuda.Event()
+            done.record(side)
+            main.wait_event(done)
         return out
 
     def close(self) -> None:
