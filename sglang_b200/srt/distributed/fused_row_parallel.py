@@ -68,6 +68,7 @@ class FusedRowParallelComm:
         self._flag_arr = arr(*self.flag_ptrs)
         self.epoch = 0
         self.pipeline = True     # large outputs are cut into row chunks (see `_chunks`)
+        self.min_comm_ratio = 0.4  # pipeline only where gather time / GEMM time exceeds this (see `_chunks`)
         self.min_waves = 3       # a chunk keeps at least this many waves of GEMM tiles
         self.sm_margin = 16      # SMs the GEMM of a later chunk leaves to the reduce-and-gather of an earlier one
         self.sms = torch.cuda.get_device_properties(device).multi_processor_count
@@ -77,10 +78,12 @@ class FusedRowParallelComm:
     def supports(self, M: int, N: int) -> bool:
         return M > 0 and M % (self.world * _BM) == 0 and N % 8 == 0 and M * N <= self.max_elems
 
-    def _chunks(self, M: int, N: int) -> int:
+    def _chunks(self, M: int, N: int, K: int) -> int:
         """Row chunks to pipeline over: the reduce-and-gather of chunk c runs beside the GEMM of chunk c + 1 on the
-        SMs that GEMM leaves free.  Chunks keep at least `min_waves` waves of GEMM tiles each."""
-        if not self.pipeline:
+        SMs that GEMM leaves free.  Chunks keep at least `min_waves` waves of GEMM tiles each.  Pipelining costs
+        the later chunks' GEMMs `sm_margin` SMs, so it is used only where the exposed gather is a sizeable part of
+        the GEMM time: gather / GEMM = ((p-1)/p * 2MN B / ~700 GB/s) / (2MNK FLOP / ~1.8 PFLOP/s) ~ (p-1)/p * 2570 / K."""
+        if not self.pipeline or (self.world - 1) / self.world * 2570.0 / K < self.min_comm_ratio:
             return 1
         tiles_n = (N + 191) // 192
         for c in (4, 2):
@@ -100,7 +103,7 @@ class FusedRowParallelComm:
         main = torch.cuda.current_stream(xq.device)
         dt = 0 if out_dtype == torch.bfloat16 else 1
         out = torch.empty(M, N, device=xq.device, dtype=out_dtype)
-        C_ = self._chunks(M, N)
+        C_ = self._chunks(M, N, K)
         Mc = M // C_
         arr = C.c_void_p * self.world
         side = self._side if C_ > 1 else main

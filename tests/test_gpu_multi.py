@@ -139,9 +139,9 @@ def _fused_worker(rank, world, port, ret):
         assert comm.supports(sizes[0], N) and comm.supports(sizes[3], N) and not comm.supports(70, N)
         fused = [down(x)[0].clone() for x in xs]           # 70 rows fall back to the plain path
         fused2 = [down(x)[0].clone() for x in xs]          # flags and staging are reused by later calls
-        comm.min_waves = 0                                 # cut into row chunks wherever the row count allows:
+        comm.min_waves, comm.min_comm_ratio = 0, 0.0       # cut into row chunks wherever the row count allows:
         piped = [down(x)[0].clone() for x in xs]           # reduce-and-gather of a chunk beside the next chunk's GEMM
-        assert comm._chunks(sizes[3], N) == 4 and comm._chunks(sizes[0], N) == 2 and comm._chunks(sizes[1], N) == 1
+        assert comm._chunks(sizes[3], N, k) == 4 and comm._chunks(sizes[0], N, k) == 2 and comm._chunks(sizes[1], N, k) == 1
         torch.cuda.synchronize()
         ret[rank] = dict(nccl=[t.float().cpu().numpy() for t in nccl], fused=[t.float().cpu().numpy() for t in fused],
                          again=all(torch.equal(a, b) for a, b in zip(fused, fused2)) and
