@@ -211,7 +211,8 @@ def moe_layer(args, ctx, peaks):
     cfg = Fp8Config()
     E, H, I, topk = 256, 7168, 2048, 8
     gen = torch.Generator(device=dev).manual_seed(23 + rank)
-    moe = FusedMoE(E, H, I, topk, quant_config=cfg, a2a_backend="nccl", device=dev)
+    # (every rank holds the same number of tokens here, so decode-sized batches may take the gather form)
+    moe = FusedMoE(E, H, I, topk, quant_config=cfg, a2a_backend="nccl", device=dev, equal_tokens_gather_below=2048)
     _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
     _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
     # the shared expert is a dense block-FP8 MLP replicated on every rank (models/deepseek_v2.py:826-882)
@@ -243,7 +244,8 @@ def moe_layer(args, ctx, peaks):
         res[str(T)] = {"ms": ms, "tokens_per_s": world * T / ms * 1e3, "tflops_per_gpu": flops / ms / 1e9, **extra}
     return {"moe_layer": {"config": "BASELINE config 3: DeepSeek-V3 MoE, 256 routed experts + 1 shared, hidden 7168, "
                                     "moe_intermediate 2048, top-8 grouped sigmoid routing (8 groups, top-4), "
-                                    "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine",
+                                    "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine (batches of at "
+                                    "most 2048 tokens over all ranks: all-gather, local experts, reduce-scatter)",
                           "ep": world, "scaling": "weak", "results": res}}
 
 
@@ -265,7 +267,8 @@ def moe_layer_skewed(args, ctx, peaks):
     initialize_model_parallel(1, world)
     E, H, I, topk = 128, 2048, 768, 8
     gen = torch.Generator(device=dev).manual_seed(41 + rank)
-    moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="nccl", device=dev)
+    moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="nccl", device=dev,
+                   equal_tokens_gather_below=2048)
     _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
     _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
     perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))  # the same popularity order on every rank

@@ -103,6 +103,11 @@ struct GemmParams {
   const CUtensorMap* push_maps;  // [world] in global memory, nullptr = ordinary output through map_c
   int push_rows_per_owner;       // a multiple of BM
   int push_rank;                 // this GPU's slot in the owners' staging buffers
+  // stream-K mode (weight streaming, few tiles): the tiles x slabs space is cut into `sk_ctas` equal runs of
+  // `sk_share` slabs, one per CTA; a run covers the end of one tile and the start of the next (two pieces)
+  int sk_share;                  // 0 = off; otherwise <= kb_total
+  int sk_ctas;
+  int sk_total;                  // tiles * kb_total
 };
 
 constexpr int kBChunk = 256;  // slabs of weight-block scales a promotion warp stages at a time
@@ -137,11 +142,29 @@ __device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int 
 // [0, full_units) whole, then `splits` consecutive units per remaining tile.
 struct Unit {
   int tile, sp, kb_begin, kb_stop;
+  int slot;  // split units: which [BM][BN] float32 block of the partial-sum scratch
   bool split;
 };
 template <bool kGrouped>
 __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
   Unit x;
+  x.slot = 0;
+  if (!kGrouped && p.sk_share > 0) {
+    // unit u = piece u / sk_ctas (0 or 1) of the run of CTA u % sk_ctas
+    const int piece = u / p.sk_ctas, c = u - piece * p.sk_ctas;
+    const int lo = c * p.sk_share, hi = min(lo + p.sk_share, p.sk_total);
+    const int t0 = lo / p.kb_total, kb0 = lo - t0 * p.kb_total;
+    const int end0 = min(hi, (t0 + 1) * p.kb_total);
+    x.sp = piece, x.slot = u, x.split = true;
+    if (piece == 0) {
+      x.tile = t0, x.kb_begin = kb0, x.kb_stop = kb0 + (end0 - lo);
+    } else if (hi > end0) {
+      x.tile = t0 + 1, x.kb_begin = 0, x.kb_stop = hi - end0;
+    } else {
+      x.tile = t0, x.kb_begin = 0, x.kb_stop = 0;  // no second piece: every role skips an empty K range
+    }
+    return x;
+  }
   if (kGrouped || u < p.full_units) {
     x.tile = u, x.sp = 0, x.kb_begin = 0, x.kb_stop = p.kb_total, x.split = false;
   } else {
@@ -150,6 +173,7 @@ __device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
     x.sp = v - (x.tile - p.full_units) * p.splits;
     x.kb_begin = x.sp * p.kb_per_split;
     x.kb_stop = min(p.kb_total, x.kb_begin + p.kb_per_split);
+    x.slot = v;
     x.split = true;
   }
   return x;
@@ -207,7 +231,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int tiles_n = p.tiles_n;
   const int num_tiles = tiles_m * tiles_n;
   const int kb_total = p.kb_total;
-  const int num_units = kGrouped ? num_tiles : p.full_units + (num_tiles - p.full_units) * p.splits;
+  const int num_units = kGrouped         ? num_tiles
+                        : p.sk_share > 0 ? 2 * p.sk_ctas
+                                         : p.full_units + (num_tiles - p.full_units) * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -330,6 +356,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
       const Unit un = decode_unit<kGrouped>(p, u);
       const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
+      if (kb_begin >= kb_stop) continue;  // (an empty second piece of a stream-K run; uniform over the CTA)
       int m_tile, n_tile;
       tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
       const int64_t row = (int64_t)m_tile * BM + row_in_tile;
@@ -430,9 +457,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (un.split) {
         // this unit's float32 partial sums, tile-local layout; a second kernel adds the units of a tile in a
         // fixed order, adds the bias and rounds once
-        if (alive) {
-          float* dst = p.partial + ((int64_t)(t - p.full_units) * p.splits + un.sp) * (BM * BN) + row_in_tile * BN +
-                       cgrp * kEpiCols;
+        if (alive && row < rows) {  // (rows past M are never read back)
+          float* dst = p.partial + (int64_t)un.slot * (BM * BN) + row_in_tile * BN + cgrp * kEpiCols;
 #pragma unroll
           for (int j = 0; j < kEpiCols / 4; ++j)
             *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
@@ -581,6 +607,42 @@ __global__ void __launch_bounds__(256)
   *reinterpret_cast<uint4*>(C + row * N + col) = raw;
 }
 
+// The same for stream-K runs: output tile `blockIdx.x` is the sum, in ascending K order, of the pieces of the runs
+// that cover its slabs; run c covers slabs [c * share, (c + 1) * share) of the tiles x slabs space and its piece
+// for this tile sits in slot c (first piece of the run) or c + ctas (second piece).
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+    streamk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
+                          int64_t M, int64_t N, int tiles_m, int tiles_n, int group_m, int kb_total, int share,
+                          int ctas) {
+  const int tile = blockIdx.x;
+  int m_tile, n_tile;
+  tile_coord(tile, tiles_m, tiles_n, group_m, m_tile, n_tile);
+  const int i = blockIdx.y * 256 + threadIdx.x;  // 8-column group within the tile
+  const int r = i / (BN / 8), c8 = (i - r * (BN / 8)) * 8;
+  const int64_t row = (int64_t)m_tile * BM + r;
+  const int64_t col = (int64_t)n_tile * BN + c8;
+  if (row >= M || col >= N) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int c_first = tile * kb_total / share, c_last = ((tile + 1) * kb_total - 1) / share;
+  for (int c = c_first; c <= c_last; ++c) {
+    const int slot = (c * share / kb_total == tile) ? c : c + ctas;
+    const float* src = partial + (int64_t)slot * (BM * BN) + r * BN + c8;
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+    acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
+    acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+  }
+  if (bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += ElemTraits<OutT>::to_f32(bias[col + j]);
+  }
+  uint4 raw;
+  OutT* o = reinterpret_cast<OutT*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = ElemTraits<OutT>::from_f32(acc[j]);
+  *reinterpret_cast<uint4*>(C + row * N + col) = raw;
+}
+
 // How a dense problem is cut into units.
 //  * Few tiles, long K (weight streaming, M <= 64 or so): every tile is split so that all SMs stream weights.
 //    The partial sums cost extra traffic, kept below a quarter of the weight bytes.
@@ -590,16 +652,36 @@ __global__ void __launch_bounds__(256)
 #define SGLB_TAIL_SPLIT 1
 #endif
 constexpr bool kTailSplit = SGLB_TAIL_SPLIT != 0;
+#ifndef SGLB_STREAM_K
+#define SGLB_STREAM_K 1
+#endif
+constexpr bool kStreamK = SGLB_STREAM_K != 0;
 struct UnitPlan {
   int full_units, splits, kb_per_split;
   int64_t split_tiles;
+  int sk_share, sk_ctas;  // stream-K (sk_share > 0): supersedes the three fields above
+  int64_t scratch_blocks() const { return sk_share > 0 ? 2 * (int64_t)sk_ctas : split_tiles * splits; }
 };
 static UnitPlan plan_units(int64_t M, int64_t N, int64_t K) {
   const int kb_total = (int)((K + BK - 1) / BK);
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int sms = sm_count();
-  UnitPlan pl{(int)tiles, 1, kb_total, 0};
+  UnitPlan pl{(int)tiles, 1, kb_total, 0, 0, 0};
   int64_t s = 1, split_tiles = 0;
+  if (kStreamK && tiles * 2 <= sms && kb_total >= 8 && kb_total % 4 == 0) {
+    // Few tiles, long K: equal runs of slabs over ALL SMs (splitting every tile the same number of ways leaves
+    // sms mod tiles of them idle).  Taken when the partial sums (two pieces per CTA, M rows each, written and read
+    // back) stay below a quarter of the weight bytes.
+    const int64_t total = tiles * kb_total;
+    int64_t share = (total + sms - 1) / sms;
+    share = (share + 3) / 4 * 4;  // runs start on multiples of four slabs: aligned 128-bit loads of the activation scales
+    const int64_t ctas = (total + share - 1) / share;
+    const int64_t rows = M < BM ? M : BM;
+    if (share <= kb_total && 2 * ctas * rows * BN * 4 * 2 * 4 <= N * K) {
+      pl.sk_share = (int)share, pl.sk_ctas = (int)ctas;
+      return pl;
+    }
+  }
   if (tiles * 2 <= sms && kb_total >= 8) {
     // (measured: splitting further, to several units per SM, costs more in partial-sum traffic and per-unit
     // start-up than it gains in balance)
@@ -769,7 +851,7 @@ extern "C" int sglb200_gemm_status(void) {
 extern "C" int64_t sglb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const UnitPlan pl = plan_units(M, N, K);
-  return pl.split_tiles * pl.splits * (int64_t)(BM * BN * sizeof(float));
+  return pl.scratch_blocks() * (int64_t)(BM * BN * sizeof(float));
 }
 
 extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, const float* a_s, const float* b_s,
@@ -802,22 +884,36 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   p.out_fp16 = out_dtype;
   UnitPlan pl = plan_units(M, N, K);
   const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
-  if (pl.split_tiles > 0 && (workspace == nullptr || !aligned16(workspace) ||
-                             workspace_bytes < pl.split_tiles * pl.splits * (int64_t)(BM * BN * sizeof(float))))
-    pl = UnitPlan{(int)tiles, 1, p.kb_total, 0};  // no scratch offered: one unit per tile
+  if (pl.scratch_blocks() > 0 && (workspace == nullptr || !aligned16(workspace) ||
+                                  workspace_bytes < pl.scratch_blocks() * (int64_t)(BM * BN * sizeof(float))))
+    pl = UnitPlan{(int)tiles, 1, p.kb_total, 0, 0, 0};  // no scratch offered: one unit per tile
   p.full_units = pl.full_units, p.splits = pl.splits, p.kb_per_split = pl.kb_per_split;
+  p.sk_share = pl.sk_share, p.sk_ctas = pl.sk_ctas, p.sk_total = (int)(tiles * p.kb_total);
   p.partial = static_cast<float*>(workspace);
   CUtensorMap mc{};
-  p.tma_out = pl.full_units > 0;
+  p.tma_out = pl.sk_share == 0 && pl.full_units > 0;
   if (p.tma_out) {
     rc = get_out_map(C, (uint64_t)N, (uint64_t)M, out_dtype, &mc);
     if (rc) return rc;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  rc = launch_gemm<false>(ma, mb, mc, p, pl.full_units + pl.split_tiles * pl.splits, st);
-  if (rc != SGLB200_OK || pl.split_tiles == 0) return rc;
-  const dim3 grid((unsigned)pl.split_tiles, BM * BN / 8 / 256);
+  rc = launch_gemm<false>(ma, mb, mc, p, pl.sk_share > 0 ? pl.sk_ctas : pl.full_units + pl.split_tiles * pl.splits, st);
+  if (rc != SGLB200_OK || pl.scratch_blocks() == 0) return rc;
   const int tiles_m = (int)((M + BM - 1) / BM);
+  if (pl.sk_share > 0) {
+    const dim3 sgrid((unsigned)tiles, BM * BN / 8 / 256);
+    if (out_dtype == 0)
+      streamk_reduce_kernel<__nv_bfloat16><<<sgrid, 256, 0, st>>>(
+          p.partial, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, tiles_m, p.tiles_n,
+          p.group_m, p.kb_total, pl.sk_share, pl.sk_ctas);
+    else
+      streamk_reduce_kernel<__half><<<sgrid, 256, 0, st>>>(p.partial, static_cast<__half*>(C),
+                                                           static_cast<const __half*>(bias), M, N, tiles_m, p.tiles_n,
+                                                           p.group_m, p.kb_total, pl.sk_share, pl.sk_ctas);
+    SGLB_CUDA(cudaGetLastError());
+    return SGLB200_OK;
+  }
+  const dim3 grid((unsigned)pl.split_tiles, BM * BN / 8 / 256);
   if (out_dtype == 0)
     split_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p.partial, static_cast<__nv_bfloat16*>(C),
                                                              static_cast<const __nv_bfloat16*>(bias), M, N, tiles_m,

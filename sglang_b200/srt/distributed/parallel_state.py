@@ -41,6 +41,19 @@ class GroupCoordinator:
         dist.all_gather(parts, x.contiguous(), group=self.device_group)
         return torch.cat(parts, dim=dim)
 
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over the group of `x` [world * n, ...]; this rank keeps rows [rank * n, (rank + 1) * n)."""
+        if self.world_size == 1:
+            return x
+        n = x.shape[0] // self.world_size
+        if x.is_cuda:
+            out = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            dist.reduce_scatter_tensor(out, x.contiguous(), group=self.device_group)
+            return out
+        x = x.clone()  # (gloo has no reduce-scatter)
+        dist.all_reduce(x, group=self.device_group)
+        return x[self.rank_in_group * n : (self.rank_in_group + 1) * n].contiguous()
+
     def all_to_all_single(self, out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits) -> torch.Tensor:
         """Variable-size row exchange: rank r sends inp rows [sum(in_splits[:i]) ...) to peer i."""
         if self.world_size == 1:

@@ -9,6 +9,12 @@ rank r of an EP group of size p owns experts [r*E/p, (r+1)*E/p) (:182-185).
   their experts in one all-to-all, the results return in a second one and are summed at the source.
   This replaces the DeepEP dispatch/combine of the reference
   (python/sglang/srt/layers/moe/token_dispatcher/deepep.py:449-509) with NCCL over NVLink.
+  With `equal_tokens_gather_below = n` a batch of at most n tokens over all ranks (decode-sized; every rank must
+  hold the SAME number of tokens, as under the reference's padded data-parallel attention) takes the
+  gather form instead: all-gather tokens and routing, local experts on all of them with remote ids masked
+  to -1, reduce-scatter of the partial outputs (the reference's dp_gather / dp_scatter around its standard
+  dispatcher, python/sglang/srt/layers/dp_attention.py).  It needs no host synchronisation and three small
+  collectives, which is what a batch of a few tokens is bound by.
 """
 from __future__ import annotations
 
@@ -27,7 +33,7 @@ class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, hidden_size: int, intermediate_size: int, top_k: int,
                  params_dtype: torch.dtype = torch.bfloat16, quant_config=None, prefix: str = "",
                  routed_scaling_factor: Optional[float] = None, a2a_backend: str = "none", inplace: bool = False,
-                 device=None):
+                 device=None, equal_tokens_gather_below: Optional[int] = None):
         super().__init__()
         ep = get_moe_ep_group()
         self.moe_ep_size = ep.world_size
@@ -39,6 +45,7 @@ class FusedMoE(nn.Module):
         self.intermediate_size_per_partition = intermediate_size
         self.top_k = top_k
         self.a2a_backend = a2a_backend
+        self.equal_tokens_gather_below = equal_tokens_gather_below
         self.quant_config = quant_config
         self.quant_method = quant_config.get_quant_method(self, prefix=prefix)
         self.quant_method.create_weights(self, self.num_local_experts, hidden_size, intermediate_size, params_dtype,
@@ -60,6 +67,9 @@ class FusedMoE(nn.Module):
 
     def forward(self, hidden_states: torch.Tensor, topk_output: StandardTopKOutput) -> torch.Tensor:
         if self.a2a_backend == "nccl" and self.moe_ep_size > 1:
+            n = self.equal_tokens_gather_below
+            if n is not None and hidden_states.shape[0] * self.moe_ep_size <= n:
+                return self._forward_gathered(hidden_states, topk_output)
             return ep_all_to_all_forward(self, hidden_states, topk_output)
         dispatch_output = self.dispatcher.dispatch(hidden_states, topk_output)
         combine_input = self.quant_method.apply(self, dispatch_output)
@@ -67,3 +77,12 @@ class FusedMoE(nn.Module):
         if self.moe_ep_size > 1:
             out = get_moe_ep_group().all_reduce(out)
         return out
+
+    def _forward_gathered(self, hidden_states: torch.Tensor, topk_output: StandardTopKOutput) -> torch.Tensor:
+        g = get_moe_ep_group()
+        x_all = g.all_gather(hidden_states, dim=0)
+        w_all = g.all_gather(topk_output[0], dim=0)
+        ids_all = g.all_gather(topk_output[1], dim=0)
+        dispatch_output = self.dispatcher.dispatch(x_all, StandardTopKOutput(w_all, ids_all, None))
+        out_all = self.dispatcher.combine(self.quant_method.apply(self, dispatch_output))
+        return g.reduce_scatter(out_all)

@@ -70,9 +70,15 @@ def _worker(rank, world, port, ret):
             moe.load_full_weights(codes_to_fp8(w13q, dev), torch.from_numpy(w13s).to(dev), codes_to_fp8(wdq, dev),
                                   torch.from_numpy(wds).to(dev))
             outs[backend] = moe(xi.to(dev), StandardTopKOutput(wi.to(dev), ii.to(dev), None)).float().cpu().numpy()
+        # decode-sized batches of equal size per rank: all-gather, local experts, reduce-scatter
+        moe = FusedMoE(E, Hm, Im, topk, quant_config=cfg, a2a_backend="nccl", device=dev,
+                       equal_tokens_gather_below=1024)
+        moe.load_full_weights(codes_to_fp8(w13q, dev), torch.from_numpy(w13s).to(dev), codes_to_fp8(wdq, dev),
+                              torch.from_numpy(wds).to(dev))
+        outs["gather"] = moe(xt[:33].to(dev), StandardTopKOutput(tw[:33].to(dev), ti[:33].to(dev), None)).float().cpu().numpy()
         torch.cuda.synchronize()
         from sglang_b200 import ops
-        ret[rank] = dict(y=y.float().cpu().numpy(), gu=gu.float().cpu().numpy(), moe_a2a=outs["nccl"],
+        ret[rank] = dict(moe_gather=outs["gather"], y=y.float().cpu().numpy(), gu=gu.float().cpu().numpy(), moe_a2a=outs["nccl"],
                          moe_std=outs["none"], x=to_f32_np(xt), tw=tw.numpy(), ti=ti.numpy(), status=ops.gemm_status())
     finally:
         dist.destroy_process_group()
@@ -104,6 +110,8 @@ def test_tp_and_ep_on_two_gpus():
         assert_close_fp(d["y"], y_ref, rtol=2e-2, atol=2e-2, min_cos=0.9995)
         ref = O.fused_experts_block_fp8(d["x"], w13q, w13s, wdq, wds, d["tw"], d["ti"], 1.0)
         assert_close_fp(d["moe_a2a"], ref, rtol=2e-2, atol=2e-2)
+        assert d["moe_gather"].shape == (33, Hm)
+        assert_close_fp(d["moe_gather"], ref[:33], rtol=2e-2, atol=2e-2)
     ref0 = O.fused_experts_block_fp8(ret[0]["x"], w13q, w13s, wdq, wds, ret[0]["tw"], ret[0]["ti"], 1.0)
     for r in range(world):
         assert_close_fp(ret[r]["moe_std"], ref0, rtol=2e-2, atol=2e-2)
@@ -139,7 +147,7 @@ def _fused_worker(rank, world, port, ret):
         assert comm.supports(sizes[0], N) and comm.supports(sizes[3], N) and not comm.supports(70, N)
         fused = [down(x)[0].clone() for x in xs]           # 70 rows fall back to the plain path
         fused2 = [down(x)[0].clone() for x in xs]          # flags and staging are reused by later calls
-        comm.min_waves, comm.min_comm_ratio = 0, 0.0       # cut into row chunks wherever the row count allows:
+        comm.pipeline, comm.min_waves, comm.min_comm_ratio = True, 0, 0.0  # row chunks wherever the row count allows:
         piped = [down(x)[0].clone() for x in xs]           # reduce-and-gather of a chunk beside the next chunk's GEMM
         assert comm._chunks(sizes[3], N, k) == 4 and comm._chunks(sizes[0], N, k) == 2 and comm._chunks(sizes[1], N, k) == 1
         torch.cuda.synchronize()

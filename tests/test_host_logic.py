@@ -121,7 +121,9 @@ def _tp_worker(rank, world, port, ret):
         row.load_full_weight(w2, s2)
         x = torch.full((2, 3), float(rank + 1))
         tensor_model_parallel_all_reduce(x)
-        ret[rank] = dict(
+        from sglang_b200.srt.distributed import get_tp_group
+        rs = get_tp_group().reduce_scatter(torch.arange(4.0).reshape(4, 1) * (rank + 1))  # rows [2r, 2r+2) of the sum
+        ret[rank] = dict(rs=rs.numpy(),
             col_w=col.weight.view(torch.uint8).numpy(), col_s=col.weight_scale_inv.numpy(),
             row_w=row.weight.view(torch.uint8).numpy(), row_s=row.weight_scale_inv.numpy(),
             full_w=w.view(torch.uint8).numpy(), full_s=s.numpy(), full_w2=w2.view(torch.uint8).numpy(),
@@ -145,6 +147,7 @@ def test_tp_sharding_two_gloo_ranks():
         assert np.array_equal(d["row_w"], d["full_w2"][:, 256 * r : 256 * r + 256])
         assert np.array_equal(d["row_s"], d["full_s2"][:, 2 * r : 2 * r + 2])
         assert np.all(d["ar"] == 3.0)
+        assert np.array_equal(d["rs"], 3.0 * np.arange(4.0).reshape(4, 1)[2 * r : 2 * r + 2])
 
 
 def test_sgl_kernel_ops_have_shape_only_implementations():
