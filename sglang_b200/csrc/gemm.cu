@@ -24,9 +24,12 @@
 // each promotion warp owns as many columns as the register file allows (fewer warps = less per-slab overhead).
 // The epilogue rounds to bf16/fp16, parks the tile in swizzled shared memory and writes it with TMA
 // stores that drain during the next tile; in grouped "scatter" mode it multiplies by the routing
-// weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids.  Split tiles
-// (every tile when there are few of them and K is long; the tiles of a short last wave otherwise) write
-// float32 partial sums that a second kernel adds in a fixed order.
+// weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids.  With few tiles
+// and a long K (weight streaming at small M) the tiles x slabs space is cut into one equal run of slabs
+// per SM (stream-K); otherwise the tiles of a short last wave are split along K.  Split work writes
+// float32 partial sums that a second kernel adds in ascending K order.  In push mode (row-parallel
+// layers under tensor parallelism) a tile is stored through the tensor map of the staging buffer of
+// the GPU that owns its rows, which folds the reduce-scatter of the all-reduce into the epilogue.
 //
 // Every mbarrier wait is bounded; on expiry the CTA raises a status word, unwinds, frees its TMEM
 // and returns (sglb200_gemm_status() reports it).
