@@ -99,6 +99,15 @@ int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num
                                  int64_t workspace_bytes, void* stream);
 
 /*
+ * Inputs of 2049 to 1 048 576 ids are sorted by ONE cooperative kernel (histogram, grid barrier, scatter).  Where
+ * cooperative launches are not available (the device attribute is off, or the CTAs would not all be resident) the
+ * same work runs as three ordinary launches; sglb200_moe_align_set_cooperative(0) forces that form, (1) restores
+ * the default.  Process-wide; no counterpart in the reference, whose sort is always two launches
+ * (sgl-kernel/csrc/moe/moe_align_kernel.cu:339-364).
+ */
+void sglb200_moe_align_set_cooperative(int on);
+
+/*
  * moe_align_block_size for callers that cannot allocate device memory when they need the sort: code running
  * while a CUDA graph is being captured with the allocator frozen, a server whose memory pool is fully committed
  * to the KV cache, or a host program without torch's allocator.  No counterpart in the reference (its op always

@@ -7,13 +7,18 @@
 // permutation inside each expert segment; this order is one of its valid outputs and is the
 // order of the reference's CPU implementation and test oracle).
 //
-// The ids are cut into chunks of consecutive entries, one CTA per chunk (8192 ids, or longer chunks
-// when the input would otherwise need more than two CTAs per SM); inside a CTA each of the 32 warps
+// The ids are cut into chunks of consecutive entries, one CTA per chunk (1024 ids, or longer chunks
+// when the input would otherwise need more than 128 CTAs: ranking costs about seven warp instructions per
+// id, so a chunk is bound by instruction issue on its SM and short chunks on many SMs finish first); inside
+// a CTA each of the 32 warps
 // owns one contiguous span of the chunk and walks it 32 ids at a time.  Rank of an
 // entry = (padded start of its bucket) + (entries of that bucket in earlier chunks) + (in
 // earlier warps of the chunk) + (in earlier steps of the warp) + (in lower lanes of the step,
-// from one ballot per id bit).  Up to kSingleMax ids run as ONE kernel; larger inputs run histogram ->
-// scan -> scatter over a small global workspace.  No global atomics anywhere.
+// from one ballot per id bit).  Up to kSingleMax ids run as ONE CTA; up to kLargeMin ids as one cooperative
+// kernel (histogram, grid barrier, scatter) or, where a cooperative launch is not possible, as histogram ->
+// scan -> scatter launches over a small global workspace; above that the tile-sorted path.  No global atomics.
+#include <cooperative_groups.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -22,8 +27,13 @@ namespace sglb200 {
 
 constexpr int kAlignThreads = 1024;
 constexpr int kAlignWarps = kAlignThreads / 32;
-constexpr int kChunk = kAlignWarps * 256;          // 8192 ids per CTA: the shortest chunk of the multi-CTA path
-constexpr int64_t kSingleMax = 8192;               // up to here one CTA sorts everything in one launch (measured cross-over)
+constexpr int kChunk = kAlignWarps * 256;          // 8192 ids per CTA: the longest chunk of the multi-CTA path (at 2^20 ids)
+constexpr int64_t kSingleMax = 2048;               // up to here one CTA sorts everything in one launch
+constexpr int kMidMaxChunks = 128;                 // CTAs of the multi-CTA path: at most one per SM, all resident
+#ifndef SGLB_ALIGN_COOP
+#define SGLB_ALIGN_COOP 1
+#endif
+constexpr bool kAlignCoop = SGLB_ALIGN_COOP != 0;  // one cooperative launch instead of three for 8192 < ids <= 1 M
 constexpr int kMaxChunks = 296;                    // about two CTAs per SM; longer inputs get longer chunks
 
 __device__ __forceinline__ int warp_incl_scan(int v) {
@@ -122,6 +132,7 @@ __device__ __forceinline__ void padded_prefix(int B, int block_size, const int* 
 }
 
 // Writes sorted_token_ids for the chunk.  base[b] = padded start of bucket b + entries in earlier chunks.
+template <int NBITS = 0>  // > 0: the number of key bits is known at compile time (unrolled ballots)
 __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ ids, int64_t chunk_begin, int64_t chunk_end,
                                               int span, int B, int* wc, const int* base, int32_t* __restrict__ sorted) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,7 +153,7 @@ __device__ __forceinline__ void scatter_chunk(const int32_t* __restrict__ ids, i
       if (s0 + j * 32 >= seg_end) break;  // uniform
       const int b = v[j];
       const int key = b >= 0 ? b : B + lane;  // invalid lanes match nobody
-      const unsigned peers = peers_of(key, nbits);
+      const unsigned peers = NBITS > 0 ? peers_of_fixed<(NBITS > 0 ? NBITS : 1)>(key) : peers_of(key, nbits);
       const int rank = __popc(peers & ((1u << lane) - 1u));
       int start = 0;
       if (b >= 0) start = wc[warp * B + b];
@@ -271,6 +282,105 @@ __global__ void __launch_bounds__(kAlignThreads)
   scatter_chunk(ids, begin, end, span, B, wc, base, sorted);
 }
 
+// ---- kSingleMax < numel <= kLargeMin, one launch ------------------------------------------------
+// The same three steps in ONE cooperative kernel: every CTA counts its chunk, publishes the chunk's histogram,
+// all CTAs meet at a grid barrier, then every CTA sums the histograms of the chunks before it (and of all chunks)
+// for itself and scatters, reusing the per-warp counts it already holds in shared memory.  Saves two launches
+// and the second count; the grid barrier is legal because the launch is cooperative (all CTAs are resident).
+template <int NBITS>
+__global__ void __launch_bounds__(kAlignThreads)
+    moe_align_coop_kernel(const int32_t* __restrict__ ids, int64_t numel, int span, int B, int block_size,
+                          int* __restrict__ chunk_hist, int32_t* __restrict__ sorted, int32_t* __restrict__ expert_ids,
+                          int32_t* __restrict__ post_pad, int32_t* __restrict__ cumsum, bool pad_sorted) {
+  extern __shared__ int smem[];
+  int* wc = smem;                       // [32][B]
+  int* tot = wc + kAlignWarps * B;      // [B]   this chunk's totals, then the totals over all chunks
+  int* prefix = tot + B;                // [B+1]
+  int* base = prefix + B + 1;           // [B]
+  int* scratch = base + B;              // [33]
+  for (int i = threadIdx.x; i < kAlignWarps * B; i += kAlignThreads) wc[i] = 0;
+  __syncthreads();
+  const int64_t chunk_len = (int64_t)span * kAlignWarps;
+  const int64_t begin = (int64_t)blockIdx.x * chunk_len;
+  const int64_t end = begin + chunk_len < numel ? begin + chunk_len : numel;
+  count_chunk(ids, begin, end, span, B, wc);
+  __syncthreads();
+  scan_over_warps(B, wc, tot);  // wc becomes the exclusive prefix over the warps of this chunk
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += kAlignThreads) chunk_hist[(int64_t)blockIdx.x * B + b] = tot[b];
+  __threadfence();
+  cooperative_groups::this_grid().sync();
+  // totals over all chunks and entries in earlier chunks, per bucket: all threads walk the [chunks][B] table once
+  // (coalesced, independent loads) and add into shared memory
+  for (int b = threadIdx.x; b < B; b += kAlignThreads) tot[b] = 0, base[b] = 0;
+  __syncthreads();
+  {
+    const int n = (int)gridDim.x * B, mine_end = (int)blockIdx.x * B;
+    constexpr int kU = 4;
+    for (int i0 = threadIdx.x; i0 < n; i0 += kAlignThreads * kU) {
+      int v[kU];
+#pragma unroll
+      for (int k = 0; k < kU; ++k) {
+        const int i = i0 + k * kAlignThreads;
+        v[k] = i < n ? __ldcg(chunk_hist + i) : 0;  // written by other CTAs: read through L2
+      }
+#pragma unroll
+      for (int k = 0; k < kU; ++k) {
+        const int i = i0 + k * kAlignThreads;
+        if (i < n && v[k] != 0) {
+          const int b = i % B;
+          atomicAdd(&tot[b], v[k]);
+          if (i < mine_end) atomicAdd(&base[b], v[k]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  padded_prefix(B, block_size, tot, prefix, scratch);
+  for (int b = threadIdx.x; b < B; b += kAlignThreads) base[b] += prefix[b];
+  if (blockIdx.x == 0) {
+    for (int b = threadIdx.x; b <= B; b += kAlignThreads) cumsum[b] = prefix[b];
+    if (threadIdx.x == 0) *post_pad = prefix[B];
+  }
+  fill_meta(B, block_size, numel, prefix, tot, expert_ids, sorted, pad_sorted, blockIdx.x, gridDim.x);
+  __syncthreads();
+  scatter_chunk<NBITS>(ids, begin, end, span, B, wc, base, sorted);
+}
+
+static bool g_align_coop_enabled = true;  // sglb200_moe_align_set_cooperative
+
+using CoopKernel = void (*)(const int32_t*, int64_t, int, int, int, int*, int32_t*, int32_t*, int32_t*, int32_t*, bool);
+static CoopKernel coop_kernel_for(int B) {
+  switch (32 - __builtin_clz((unsigned)(B + 31))) {  // keys run up to B + 31
+    case 6: return moe_align_coop_kernel<6>;
+    case 7: return moe_align_coop_kernel<7>;
+    case 8: return moe_align_coop_kernel<8>;
+    case 9: return moe_align_coop_kernel<9>;
+    case 10: return moe_align_coop_kernel<10>;
+    default: return moe_align_coop_kernel<0>;
+  }
+}
+
+// Whether `chunks` CTAs of the cooperative kernel can be resident at once on the current device (cached per device
+// and shared-memory size class).
+static bool coop_fits(CoopKernel kern, int64_t chunks, size_t smem) {
+  static thread_local int last_dev = -1;
+  static thread_local size_t last_smem = 0;
+  static thread_local int64_t last_cap = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (dev != last_dev || smem != last_smem) {
+    int coop = 0, per_sm = 0;
+    int64_t cap = 0;
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && coop &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kAlignThreads, smem) ==
+            cudaSuccess)
+      cap = (int64_t)per_sm * sm_count();
+    last_dev = dev, last_smem = smem, last_cap = cap;
+  }
+  return chunks <= last_cap;
+}
+
 // ---- numel > kLargeMin: tile-sorted scatter ---------------------------------------------------
 // With the per-warp scatter above every (CTA, warp, bucket) is an output stream of its own that grows four
 // bytes at a time; at tens of millions of ids those streams (millions of half-written 32-byte sectors) no
@@ -397,8 +507,8 @@ static void align_plan(int64_t numel, int64_t* chunks, int* span) {
     if (*span == 0) *span = 32;
     return;
   }
-  int64_t c = (numel + kChunk - 1) / kChunk;
-  if (c > kMaxChunks) c = kMaxChunks;
+  int64_t c = (numel + 1023) / 1024;
+  if (c > kMidMaxChunks) c = kMidMaxChunks;
   int64_t chunk_len = (numel + c - 1) / c;
   chunk_len = (chunk_len + 1023) / 1024 * 1024;  // 32 warps x a multiple of 32 ids
   *span = (int)(chunk_len / kAlignWarps);
@@ -410,6 +520,8 @@ static size_t align_smem_bytes(int B) { return sizeof(int) * ((size_t)kAlignWarp
 }  // namespace sglb200
 
 using namespace sglb200;
+
+extern "C" void sglb200_moe_align_set_cooperative(int on) { g_align_coop_enabled = on != 0; }
 
 extern "C" int64_t sglb200_moe_align_workspace_bytes(int64_t numel, int num_experts) {
   if (numel <= kSingleMax) return 0;
@@ -501,6 +613,19 @@ extern "C" int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t num
                 (long long)workspace_bytes);
   int* chunk_hist = static_cast<int*>(workspace);
   int* totals = chunk_hist + chunks * B;
+  if (kAlignCoop && g_align_coop_enabled) {
+    const CoopKernel kern = coop_kernel_for(B);
+    if (smem > 48 * 1024)
+      SGLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    if (coop_fits(kern, chunks, smem)) {
+      bool pad = pad_sorted_token_ids != 0;
+      void* args[] = {&topk_ids, &numel, &span, (void*)&B, &block_size, &chunk_hist, &sorted_token_ids, &expert_ids,
+                      &num_tokens_post_pad, &cumsum_buffer, &pad};
+      SGLB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern),
+                                            dim3((unsigned)chunks), dim3(kAlignThreads), args, smem, st));
+      return SGLB200_OK;
+    }
+  }
   moe_align_hist_kernel<<<(unsigned)chunks, kAlignThreads, smem, st>>>(topk_ids, numel, span, B, chunk_hist);
   moe_align_scan_kernel<<<(unsigned)((B + kAlignWarps - 1) / kAlignWarps), kAlignThreads, 0, st>>>(chunk_hist, totals,
                                                                                                    (int)chunks, B);

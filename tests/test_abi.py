@@ -35,7 +35,7 @@ def test_abi_version_and_error_channel():
     with pytest.raises(RuntimeError):
         check(rc)
     assert lib.sglb200_moe_align_workspace_bytes(100, 257) == 0
-    assert lib.sglb200_moe_align_workspace_bytes(131072, 257) == (16 + 1) * 257 * 4
+    assert lib.sglb200_moe_align_workspace_bytes(131072, 257) == (128 + 1) * 257 * 4  # 128 chunks of 1024 ids
 
 
 def test_product_never_imports_the_oracle():

@@ -33,7 +33,7 @@ def test_documented_example(ops):
 
 
 @pytest.mark.parametrize("block", [32, 64, 128, 256])
-@pytest.mark.parametrize("tokens", [1, 2, 33, 257, 1024, 1025, 4096])
+@pytest.mark.parametrize("tokens", [1, 2, 33, 256, 257, 1024, 1025, 4096])
 @pytest.mark.parametrize("topk,E", [(1, 64), (8, 256), (6, 160), (9, 257), (8, 8)])
 def test_random_ids(ops, block, tokens, topk, E):
     rng = np.random.default_rng(tokens * 131 + topk * 7 + E + block)
@@ -56,6 +56,18 @@ def test_all_one_expert_and_empty(ops):
     _check(ops, np.full((7, 8), -1, dtype=np.int32), 128, 256)
     s, e, n = ops.moe_align_block_size(torch.zeros((0, 8), dtype=torch.int32, device="cuda"), 128, 256)
     assert int(n.item()) == 0
+
+
+def test_three_launch_form(ops):
+    """The histogram / scan / scatter launches that stand in where a cooperative launch is not possible."""
+    from sglang_b200._lib import lib
+    lib.sglb200_moe_align_set_cooperative(0)
+    try:
+        rng = np.random.default_rng(11)
+        for tokens, topk, E in ((300, 8, 256), (4096, 8, 256), (16384, 8, 128), (100000, 6, 160)):
+            _check(ops, rng.integers(-1, E, size=(tokens, topk)).astype(np.int32), 128, E)
+    finally:
+        lib.sglb200_moe_align_set_cooperative(1)
 
 
 def test_large_input_properties(ops):
