@@ -126,7 +126,7 @@ def gemm_sweep(args, ctx, peaks):
 
 
 def tp_layer(args, ctx, peaks):
-    """QKV (column) -> o_proj (row + all-reduce) -> gate_up (column) -> silu_and_mul -> down (row + all-reduce).
+    """QKV (column) -> o_proj (row + all-reduce) -> gate_up (column) -> silu_and_mul + quantizer -> down (row + all-reduce).
     Attention itself is not on this path: o_proj is fed a tensor of the attention output's shape."""
     from sglang_b200 import ops
     from sglang_b200.srt.distributed import initialize_model_parallel
@@ -157,9 +157,8 @@ def tp_layer(args, ctx, peaks):
                 qkv(x)
                 h, _ = o_proj(attn)
                 gu, _ = gate_up(h)
-                act = torch.empty(M, gu.shape[1] // 2, device=dev, dtype=gu.dtype)
-                ops.silu_and_mul_out(act, gu)
-                down(act)
+                # activation and the 1x128 quantisation of down's input in one pass; `apply` takes (codes, scales)
+                down(ops.silu_and_mul_quant_fp8(gu, 128))
 
             ms = _time(layer, 10 if M >= 2048 else 20, 3, world, dev)
             res.setdefault(str(M), {"allreduce_bytes": 2 * M * H * 2})[key] = ms
@@ -230,9 +229,7 @@ def moe_layer(args, ctx, peaks):
         def layer():
             routed = moe(x, top)
             gu, _ = sh_gate_up(x)
-            act = torch.empty(T, I, device=dev, dtype=gu.dtype)
-            ops.silu_and_mul_out(act, gu)
-            shared, _ = sh_down(act)
+            shared, _ = sh_down(ops.silu_and_mul_quant_fp8(gu, 128))
             return routed + shared
 
         ms = _time(layer, 10, 3, world, dev)
