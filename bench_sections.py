@@ -170,7 +170,7 @@ def tp_layer(args, ctx, peaks):
     run_all("ms_nccl" if world > 1 else "ms")
     if world > 1:
         # the same layer with the all-reduce of o_proj and down fused into their GEMMs where the shape allows
-        # (rows a multiple of 128 x world); other sizes keep the NCCL all-reduce and repeat the number above
+        # (at least 128 x world rows); smaller batches keep the NCCL all-reduce and repeat the number above
         from sglang_b200.srt.distributed import destroy_model_parallel, enable_fused_row_parallel
         from sglang_b200.srt.distributed.fused_row_parallel import comm_status
         comm = enable_fused_row_parallel(max(sizes) * H)

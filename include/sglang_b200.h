@@ -271,17 +271,20 @@ int sglb200_stream_status(void);
  *   sglb200_comm_ipc_open    maps a peer's buffer into this process; sglb200_comm_ipc_close unmaps it
  *   sglb200_comm_flag_bytes  size of the flag buffer each rank must provide (zero-filled once)
  *
- * sglb200_fp8_blockwise_scaled_mm_push: the dense block GEMM of this rank's K slice, M % (world * 128) == 0;
- *   output tile rows [m0, m0+128) go to rank m0 / (M / world)'s staging buffer, block `rank`, instead of to a
- *   local C.  stage_ptrs: HOST array of `world` device pointers, entry d = rank d's staging buffer
- *   [world][M / world][N] of out_dtype as mapped in THIS process.  The first call for a given set of buffers and
- *   shape allocates and fills a small device table (do it before any stream capture).
+ * Output rows are owned in blocks of rpo = sglb200_push_rows_per_owner(M, world) rows (M / world rounded up to whole
+ * 128-row tiles): rank d owns rows [d * rpo, min((d + 1) * rpo, M)), possibly none for the last ranks.
+ * sglb200_fp8_blockwise_scaled_mm_push: the dense block GEMM of this rank's K slice; output tile rows [m0, m0+128) go
+ *   to rank m0 / rpo's staging buffer, block `rank`, instead of to a local C.  stage_ptrs: HOST array of `world`
+ *   device pointers, entry d = rank d's staging buffer [world][rpo][N] of out_dtype as mapped in THIS process.  The
+ *   first call for a given set of buffers and shape allocates and fills a small device table (do it before any
+ *   stream capture).
  * sglb200_reduce_gather: after the push GEMM on the same stream.  Waits (bounded) until every rank's GEMM has
  *   finished, sums the `world` blocks of this rank's staging buffer in rank order in float32 into
- *   reduced_ptrs[rank] and `out`, waits for the other ranks, then copies their reduced rows from
+ *   reduced_ptrs[rank] ([rpo][N]) and `out`, waits for the other ranks, then copies their reduced rows from
  *   reduced_ptrs[peer] into `out` [M][N] (private memory of this rank).  flag_ptrs[d] = rank d's flag buffer.
  *   `epoch` must be non-zero, the same on every rank for one call and different from the previous call's
- *   (a counter).  Every rank must make the same sequence of calls.
+ *   (a counter).  Every rank must make the same sequence of calls.  sglb200_comm_status() is 1 after a wait
+ *   for a peer expired (the kernel then returns without touching peer data; the output is incomplete).
  *   Pipelining over row chunks: `sm_margin` SMs are left free by the push GEMM and `max_blocks` (> 0; the same on
  *   every rank) caps the CTAs of sglb200_reduce_gather, so that the reduce-and-gather of chunk c (issued on a second
  *   stream, on its own slices of the buffers) runs beside the GEMM of chunk c + 1.  0 / 0 = no pipelining.  sglb200_comm_status() is 1 after a wait
@@ -294,12 +297,13 @@ int sglb200_comm_ipc_open(const void* handle64, void** out);
 int sglb200_comm_ipc_close(void* p);
 int64_t sglb200_comm_flag_bytes(void);
 int sglb200_comm_status(void);
+int64_t sglb200_push_rows_per_owner(int64_t M, int world);
 int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B, const float* a_s, const float* b_s,
                                          void* const* stage_ptrs, int world, int rank, int64_t M, int64_t N, int64_t K,
                                          int64_t as_stride_m, int64_t as_stride_k, int out_dtype, int sm_margin,
                                          void* stream);
 int sglb200_reduce_gather(const void* stage, void* const* reduced_ptrs, void* const* flag_ptrs, void* out, int world,
-                          int rank, int64_t rows_own, int64_t N, int dtype, uint32_t epoch, int max_blocks,
+                          int rank, int64_t M, int64_t N, int dtype, uint32_t epoch, int max_blocks,
                           void* stream);
 
 #ifdef __cplusplus

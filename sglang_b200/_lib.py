@@ -51,6 +51,7 @@ SIGNATURES = {
     "sglb200_comm_ipc_close": (_i32, [_vp]),
     "sglb200_comm_flag_bytes": (_i64, []),
     "sglb200_comm_status": (_i32, []),
+    "sglb200_push_rows_per_owner": (_i64, [_i64, _i32]),
     "sglb200_fp8_blockwise_scaled_mm_push": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(_vp), _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "sglb200_reduce_gather": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp), _vp, _i32, _i32, _i64, _i64, _i32, C.c_uint32, _i32, _vp]),
 }

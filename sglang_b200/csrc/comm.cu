@@ -82,10 +82,12 @@ __device__ __forceinline__ void add_packed(float (&acc)[8], const uint4& v) {
   }
 }
 
-// out [world * rows_own][N]: this rank's private result.  chunks = rows_own * N / 8 (16-byte pieces per block of rows).
+// out [M][N]: this rank's private result.  chunks = rows_per_owner * N / 8 (16-byte pieces per owner's block of rows),
+// total_chunks = M * N / 8: owner d holds the pieces [d * chunks, min((d + 1) * chunks, total_chunks)).
 template <bool kFp16>
 __global__ void __launch_bounds__(kCommThreads)
-    reduce_gather_kernel(CommPeers c, uint16_t* __restrict__ out, int64_t chunks, int world, int rank, uint32_t epoch) {
+    reduce_gather_kernel(CommPeers c, uint16_t* __restrict__ out, int64_t chunks, int64_t total_chunks, int world,
+                         int rank, uint32_t epoch) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   // (cross_rank_barrier starts with a __syncthreads)
@@ -98,7 +100,12 @@ __global__ void __launch_bounds__(kCommThreads)
   uint4* mine = reinterpret_cast<uint4*>(c.reduced[rank]);
   uint4* out4 = reinterpret_cast<uint4*>(out);
   const int64_t stride = (int64_t)gridDim.x * kCommThreads;
-  for (int64_t i = (int64_t)blockIdx.x * kCommThreads + threadIdx.x; i < chunks; i += stride) {
+  auto owned = [&](int d) {  // pieces of owner d's block that lie inside the output
+    const int64_t left = total_chunks - (int64_t)d * chunks;
+    return left < 0 ? (int64_t)0 : (left < chunks ? left : chunks);
+  };
+  const int64_t my_chunks = owned(rank);
+  for (int64_t i = (int64_t)blockIdx.x * kCommThreads + threadIdx.x; i < my_chunks; i += stride) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     uint4 v[kCommMaxWorld];
 #pragma unroll
@@ -132,16 +139,17 @@ __global__ void __launch_bounds__(kCommThreads)
     const int peer = (rank + d) % world;
     const uint4* src = reinterpret_cast<const uint4*>(c.reduced[peer]);
     uint4* dst = out4 + (int64_t)peer * chunks;
+    const int64_t peer_chunks = owned(peer);
     int64_t i = (int64_t)blockIdx.x * kCommThreads + threadIdx.x;
     constexpr int kFlight = 8;  // peer loads in flight per thread: a small grid must still cover the NVLink latency
-    for (; i + (kFlight - 1) * stride < chunks; i += kFlight * stride) {
+    for (; i + (kFlight - 1) * stride < peer_chunks; i += kFlight * stride) {
       uint4 v[kFlight];
 #pragma unroll
       for (int k = 0; k < kFlight; ++k) v[k] = src[i + k * stride];
 #pragma unroll
       for (int k = 0; k < kFlight; ++k) dst[i + k * stride] = v[k];
     }
-    for (; i < chunks; i += stride) dst[i] = src[i];
+    for (; i < peer_chunks; i += stride) dst[i] = src[i];
   }
 }
 
@@ -197,12 +205,13 @@ extern "C" int sglb200_comm_status(void) {
 }
 
 extern "C" int sglb200_reduce_gather(const void* stage, void* const* reduced_ptrs, void* const* flag_ptrs, void* out,
-                                     int world, int rank, int64_t rows_own, int64_t N, int dtype, uint32_t epoch,
+                                     int world, int rank, int64_t M, int64_t N, int dtype, uint32_t epoch,
                                      int max_blocks, void* stream) {
   SGLB_REQUIRE(world >= 2 && world <= kCommMaxWorld && rank >= 0 && rank < world, "reduce_gather: world %d, rank %d",
                world, rank);
-  SGLB_REQUIRE(rows_own > 0 && N > 0 && N % 8 == 0, "reduce_gather: rows %lld, N %lld (N must be a multiple of 8)",
-               (long long)rows_own, (long long)N);
+  SGLB_REQUIRE(M > 0 && N > 0 && N % 8 == 0, "reduce_gather: rows %lld, N %lld (N must be a multiple of 8)",
+               (long long)M, (long long)N);
+  const int64_t rows_own = sglb200_push_rows_per_owner(M, world);
   SGLB_REQUIRE(dtype == 0 || dtype == 1, "reduce_gather: dtype %d (0 bf16, 1 fp16)", dtype);
   SGLB_REQUIRE(epoch != 0, "reduce_gather: epoch 0 is the cleared state of the flags");
   SGLB_REQUIRE(stage && reduced_ptrs && flag_ptrs && out && aligned16(stage) && aligned16(out),
@@ -214,7 +223,7 @@ extern "C" int sglb200_reduce_gather(const void* stage, void* const* reduced_ptr
     c.reduced[i] = static_cast<uint16_t*>(reduced_ptrs[i]);
     c.flags[i] = static_cast<uint32_t*>(flag_ptrs[i]);
   }
-  const int64_t chunks = rows_own * N / 8;
+  const int64_t chunks = rows_own * N / 8, total_chunks = M * N / 8;
   int64_t blocks = (chunks + kCommThreads - 1) / kCommThreads;
   const int sms = sm_count();
   if (blocks > sms) blocks = sms;
@@ -222,11 +231,11 @@ extern "C" int sglb200_reduce_gather(const void* stage, void* const* reduced_ptr
   if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;  // (the same on every rank: block b pairs with block b)
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
-    reduce_gather_kernel<false><<<(unsigned)blocks, kCommThreads, 0, st>>>(c, static_cast<uint16_t*>(out), chunks, world,
-                                                                           rank, epoch);
+    reduce_gather_kernel<false><<<(unsigned)blocks, kCommThreads, 0, st>>>(c, static_cast<uint16_t*>(out), chunks,
+                                                                           total_chunks, world, rank, epoch);
   else
-    reduce_gather_kernel<true><<<(unsigned)blocks, kCommThreads, 0, st>>>(c, static_cast<uint16_t*>(out), chunks, world,
-                                                                          rank, epoch);
+    reduce_gather_kernel<true><<<(unsigned)blocks, kCommThreads, 0, st>>>(c, static_cast<uint16_t*>(out), chunks,
+                                                                          total_chunks, world, rank, epoch);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }

@@ -1019,14 +1019,20 @@ static int get_push_maps(void* const* stage_ptrs, int world, uint64_t N, uint64_
 
 }  // namespace sglb200
 
+extern "C" int64_t sglb200_push_rows_per_owner(int64_t M, int world) {
+  if (M <= 0 || world <= 0) return 0;
+  const int64_t per = (M + world - 1) / world;
+  return (per + BM - 1) / BM * BM;
+}
+
 extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B, const float* a_s, const float* b_s,
                                                     void* const* stage_ptrs, int world, int rank, int64_t M, int64_t N,
                                                     int64_t K, int64_t as_stride_m, int64_t as_stride_k, int out_dtype,
                                                     int sm_margin, void* stream) {
   SGLB_REQUIRE(world >= 2 && world <= 8 && rank >= 0 && rank < world, "mm_push: world %d, rank %d", world, rank);
   SGLB_REQUIRE(sm_margin >= 0 && sm_margin < sm_count(), "mm_push: sm_margin %d", sm_margin);
-  SGLB_REQUIRE(M > 0 && N > 0 && K > 0 && M % ((int64_t)world * BM) == 0,
-               "mm_push: M=%lld must be a positive multiple of world * %d", (long long)M, BM);
+  SGLB_REQUIRE(M > 0 && N > 0 && K > 0, "mm_push: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N,
+               (long long)K);
   SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, "mm_push: K=%lld must be a multiple of 16 and N=%lld of 8", (long long)K,
                (long long)N);
   SGLB_REQUIRE(out_dtype == 0 || out_dtype == 1, "mm_push: out_dtype %d (0 bf16, 1 fp16)", out_dtype);
@@ -1048,15 +1054,17 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.group_m = choose_group_m(M, K);
   p.out_fp16 = out_dtype;
-  const int64_t tiles = (M / BM) * p.tiles_n;
+  const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
   p.full_units = (int)tiles, p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;  // one unit per tile
   p.tma_out = 1;
-  // every owner's staging buffer is [world][M / world][N]: M rows in all
-  rc = get_push_maps(stage_ptrs, world, (uint64_t)N, (uint64_t)M, out_dtype, &p.push_maps);
+  // rows are owned in blocks of rpo = ceil(M / world) rounded up to whole tiles (the last owners may hold fewer
+  // rows, or none); every owner's staging buffer is [world][rpo][N]
+  const int64_t rpo = sglb200_push_rows_per_owner(M, world);
+  rc = get_push_maps(stage_ptrs, world, (uint64_t)N, (uint64_t)(rpo * world), out_dtype, &p.push_maps);
   if (rc) return rc;
-  p.push_rows_per_owner = (int)(M / world), p.push_rank = rank;
+  p.push_rows_per_owner = (int)rpo, p.push_rank = rank;
   CUtensorMap mc = {};
-  rc = get_out_map(stage_ptrs[rank], (uint64_t)N, (uint64_t)M, out_dtype, &mc);  // unused by the stores; keeps map_c valid
+  rc = get_out_map(stage_ptrs[rank], (uint64_t)N, (uint64_t)(rpo * world), out_dtype, &mc);  // unused by the stores; keeps map_c valid
   if (rc) return rc;
   return launch_gemm<false>(ma, mb, mc, p, tiles, static_cast<cudaStream_t>(stream), sm_margin);
 }

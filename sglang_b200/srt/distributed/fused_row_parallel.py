@@ -57,7 +57,7 @@ class FusedRowParallelComm:
         self.max_elems = int(max_elems)
         with torch.cuda.device(device):
             self._stage = _alloc(self.max_elems * 2)
-            self._reduced = _alloc((self.max_elems + world - 1) // world * 2)
+            self._reduced = _alloc(((self.max_elems + world - 1) // world + 8) * 2)
             self._flags = _alloc(lib.sglb200_comm_flag_bytes())
             self.stage_ptrs = _exchange(group, world, rank, self._stage)
             self.reduced_ptrs = _exchange(group, world, rank, self._reduced)
@@ -79,7 +79,11 @@ class FusedRowParallelComm:
         dist.barrier(group=group)  # nobody launches before every rank has mapped every buffer
 
     def supports(self, M: int, N: int) -> bool:
-        return M > 0 and M % (self.world * _BM) == 0 and N % 8 == 0 and M * N <= self.max_elems
+        """At least one tile of rows per rank; the staging buffer holds world x (M / world rounded up to whole tiles)
+        rows."""
+        if M < self.world * _BM or N % 8 != 0:
+            return False
+        return self.world * lib.sglb200_push_rows_per_owner(M, self.world) * N <= self.max_elems
 
     def _chunks(self, M: int, N: int, K: int) -> int:
         """Row chunks to pipeline over: the reduce-and-gather of chunk c runs beside the GEMM of chunk c + 1 on the
@@ -127,7 +131,7 @@ class FusedRowParallelComm:
             self.epoch = self.epoch % 0x7FFFFFFF + 1  # never 0, never equal to the previous call's
             check(lib.sglb200_reduce_gather(
                 self._stage + stage_off, reduced, self._flag_arr, out.data_ptr() + c * Mc * N * 2, self.world,
-                self.rank, Mc // self.world, N, dt, self.epoch, self.sm_margin if c < C_ - 1 else 0,
+                self.rank, Mc, N, dt, self.epoch, self.sm_margin if c < C_ - 1 else 0,
                 side.cuda_stream))
         if C_ > 1:
             done = torch.cuda.Event()

@@ -96,8 +96,8 @@ _FUSED_ROW = None
 
 def enable_fused_row_parallel(max_elems: int, device=None):
     """Row-parallel linears of the tensor-parallel group sum their partial outputs with the GEMM-fused all-reduce
-    (`fused_row_parallel.FusedRowParallelComm`) whenever the output has at most `max_elems` elements and its row
-    count is a multiple of 128 x world; other shapes keep the NCCL all-reduce.  Collective: every rank of the
+    (`fused_row_parallel.FusedRowParallelComm`) whenever the output has at least 128 x world rows and its
+    staging copy (world x rows-per-owner x N) fits `max_elems` elements; other shapes keep the NCCL all-reduce.  Collective: every rank of the
     group calls it, after `initialize_model_parallel`.  Returns the communicator (None for a single rank)."""
     global _FUSED_ROW
     tp = get_tp_group()

@@ -118,7 +118,9 @@ def test_tp_and_ep_on_two_gpus():
 
 
 def _fused_sizes(world):
-    return (4 * 128 * world // 2, 128 * world, 70, 4 * 128 * world)
+    # whole multiples of 128 x world, one size below the fused path's minimum, and two ragged row counts (the last
+    # owners hold a partial block of rows; with 8 ranks and 128 x world + 44 rows six of them hold none)
+    return (4 * 128 * world // 2, 128 * world, 70, 4 * 128 * world, 128 * world + 44, 4 * 128 * world - 24)
 
 
 def _fused_worker(rank, world, port, ret):
@@ -144,6 +146,7 @@ def _fused_worker(rank, world, port, ret):
               for i, M in enumerate(sizes)]
         nccl = [down(x)[0].clone() for x in xs]            # plain path: GEMM, then NCCL all-reduce
         comm = enable_fused_row_parallel(max(sizes) * N)
+        assert comm.supports(sizes[4], N) and comm.supports(sizes[5], N)
         assert comm.supports(sizes[0], N) and comm.supports(sizes[3], N) and not comm.supports(70, N)
         fused = [down(x)[0].clone() for x in xs]           # 70 rows fall back to the plain path
         fused2 = [down(x)[0].clone() for x in xs]          # flags and staging are reused by later calls
