@@ -1,10 +1,11 @@
 // 1 x G activation quantizer (float8_e4m3fn codes + float32 scales) and the fused
 // silu_and_mul + quantizer, for sm_100a.
 //
-// Both kernels are pure streaming kernels: every input byte is read once with a 128-bit
-// load, the group maximum is reduced with warp shuffles, and codes leave as 64-bit stores.
-// Each thread keeps UNROLL independent 16-byte loads in flight so that a full SM holds
-// enough bytes in flight to cover HBM latency.
+// Both are streaming kernels on one skeleton: persistent CTAs walk tiles of 8192 elements that one thread
+// stages with bulk copies (cp.async.bulk) into a ring of shared-memory buffers completing on mbarriers, so
+// the bytes in flight per SM do not depend on registers or occupancy; every input byte is read from HBM
+// once; a thread owns 32 elements of one group per tile, the group maximum takes two shuffle rounds, and
+// every quad of lanes writes one full 32-byte sector of codes.
 //
 // Arithmetic contract (bit-exact with the reference CUDA kernel built without fast-math):
 //   amax  = max(|x|, eps)            scale = amax / fp8_max      (div.rn.f32)
@@ -13,82 +14,6 @@
 #include "ptx_sm100.cuh"
 
 namespace sglb200 {
-
-template <int TPG>
-__device__ __forceinline__ float group_max(float v) {
-#pragma unroll
-  for (int off = TPG / 2; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
-  return v;
-}
-
-template <typename T>
-__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
-
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
-  uint4 raw = ld_nc_16(p);
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-template <>
-__device__ __forceinline__ void load8<__half>(const __half* p, float (&v)[8]) {
-  uint4 raw = ld_nc_16(p);
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    v[2 * i] = f.x;
-    v[2 * i + 1] = f.y;
-  }
-}
-template <>
-__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
-  uint4 a = ld_nc_16(p), b = ld_nc_16(p + 4);
-  v[0] = __uint_as_float(a.x), v[1] = __uint_as_float(a.y), v[2] = __uint_as_float(a.z), v[3] = __uint_as_float(a.w);
-  v[4] = __uint_as_float(b.x), v[5] = __uint_as_float(b.y), v[6] = __uint_as_float(b.z), v[7] = __uint_as_float(b.w);
-}
-
-// Quantise 8 values held by this thread given the group scale; returns 8 packed codes.
-//
-// The contract is code = e4m3(min(max(RN(x / scale), qmin), qmax)) with an IEEE float32 division.  A
-// div.rn.f32 costs about ten instructions per element, which makes the kernel issue-bound, so the quotient
-// is formed without dividing: with r = RN(1/scale) computed once per group,
-//     q0 = RN(x*r);  e = fma(-q0, scale, x) (exact residual);  q = fma(e, r, q0);  q = copysign(q, x)
-// equals RN(x / scale) bit for bit whenever |q| >= 2^-20 (checked exhaustively for every bf16 / fp16 input
-// pair and on ~1e8 random float32 pairs by tests/exact_div_check.c); smaller quotients may differ in float32
-// but encode as the same signed zero.  copysign restores the sign of a zero numerator.  Scales outside
-// [1e-30, 1e36] (an infinite group maximum, or a caller-chosen eps near zero) take the IEEE division.
-// With the standard range +-448 the upper clamp is what the saturating conversion does anyway and is
-// dropped; the lower clamp stays because it is also what turns a NaN quotient into -448, as in the reference.
-template <bool kStdRange>
-__device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale, float qmin, float qmax) {
-  float q[8];
-  if (scale >= 1e-30f && scale <= 1e36f) {
-    const float r = __frcp_rn(scale);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float q0 = __fmul_rn(v[i], r);
-      const float e = __fmaf_rn(-q0, scale, v[i]);
-      q[i] = copysignf(__fmaf_rn(e, r, q0), v[i]);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(v[i], scale);
-  }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    q[i] = fmaxf(q[i], qmin);
-    if (!kStdRange) q[i] = fminf(q[i], qmax);
-  }
-  uint2 out;
-  out.x = pack_e4m3x4(q[0], q[1], q[2], q[3]);
-  out.y = pack_e4m3x4(q[4], q[5], q[6], q[7]);
-  return out;
-}
 
 // ---- streaming skeleton shared by the quantizer and the fused activation + quantizer ----------------
 //
@@ -179,7 +104,7 @@ __device__ __forceinline__ void chunk_signs(const uint4& raw, uint32_t* s) {
 }
 
 // Codes of one chunk when every element of the group is finite and the scale is in the range where the
-// division-free quotient is exact (see quant8).  With the standard range no clamp is needed: a quotient can
+// division-free quotient is exact (see quant_chunk_careful).  With the standard range no clamp is needed: a quotient can
 // exceed 448 only by rounding and the conversion saturates; the sign of a zero quotient is taken from the
 // input bits (it is the only case in which the computed sign can differ from the numerator's).
 template <typename T, bool kStdRange>
@@ -204,7 +129,17 @@ __device__ __forceinline__ void quant_chunk_fast(const uint4& raw, const float* 
   }
 }
 
-// Codes of one chunk by the full contract (any input, any scale): the arithmetic of quant8.
+// Codes of one chunk by the full contract (any input, any scale).
+//
+// The contract is code = e4m3(min(max(RN(x / scale), qmin), qmax)) with an IEEE float32 division.  A
+// div.rn.f32 costs about ten instructions per element, which makes the kernel issue-bound, so the quotient
+// is formed without dividing: with r = RN(1/scale) computed once per group,
+//     q0 = RN(x*r);  e = fma(-q0, scale, x) (exact residual);  q = fma(e, r, q0);  q = copysign(q, x)
+// equals RN(x / scale) bit for bit whenever |q| >= 2^-20 (checked exhaustively for every bf16 / fp16 input
+// pair and on ~1e8 random float32 pairs by tests/exact_div_check.c); smaller quotients may differ in float32
+// but encode as the same signed zero.  copysign restores the sign of a zero numerator.  Scales outside
+// [1e-30, 1e36] (an infinite group maximum, or a caller-chosen eps near zero) take the IEEE division.
+// Both clamps are applied: the lower one is also what turns a NaN quotient into -448, as in the reference.
 template <typename T>
 __device__ __forceinline__ void quant_chunk_careful(const float* v, float scale, float qmin, float qmax,
                                                     uint32_t* codes) {
