@@ -170,6 +170,27 @@ int sglb200_moe_sum_reduce(const void* x, void* out, int dtype, int64_t tokens, 
                            float scale, void* stream);
 
 /*
+ * The same sum over the slots k with topk_ids[t, k] >= 0 only ([tokens, topk] int32, ids local to this rank): under
+ * expert parallelism the slots of experts that live on other ranks are never written and are skipped here instead
+ * of being zero-filled and read.  The reference reaches the same result by writing zeros for filtered experts
+ * (python/sglang/srt/layers/moe/fused_moe_triton/fused_moe_triton_kernels.py:421-437) and summing every slot.
+ */
+int sglb200_moe_sum_reduce_masked(const void* x, const int32_t* topk_ids, void* out, int dtype, int64_t tokens,
+                                  int64_t topk, int64_t hidden, float scale, void* stream);
+
+/*
+ * Removes the leading segment of filtered ids (bucket 0 = expert -1, the experts of other ranks) from the outputs of
+ * sglb200_moe_align_block_size: sorted_out / expert_ids_out / post_out describe only the rows of local experts, in the
+ * same order.  cumsum = the cumsum_buffer written by the sort (cumsum[1] is the padded length of bucket 0).  Outputs must
+ * not alias inputs; max_rows bounds the entries of sorted_in.  The reference keeps the segment and lets its GEMM
+ * kernel write zeros for it (fused_moe_triton_kernels.py:421-437); dropping it keeps every row of a foreign expert out
+ * of the gather, both GEMMs and the activation kernel.
+ */
+int sglb200_moe_align_drop_filtered(const int32_t* sorted_in, const int32_t* expert_ids_in, const int32_t* cumsum,
+                                    const int32_t* post_in, int32_t* sorted_out, int32_t* expert_ids_out,
+                                    int32_t* post_out, int64_t max_rows, int block_size, void* stream);
+
+/*
  * Combine step of the expert-parallel layer: out[t, :] = T( scale * sum_j src[slot[t, j], :] ), float32 accumulation in
  * ascending j; entries of `slot` [tokens, per_token] (int64) outside [0, src_rows) contribute nothing.  Replaces the
  * per-rank gather-and-add that follows `buffer.combine` in the reference's DeepEP dispatcher

@@ -33,6 +33,8 @@ SIGNATURES = {
     "sglb200_moe_align_set_cooperative": (None, [_i32]),
     "sglb200_moe_align_block_size_noalloc": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _i32, _vp]),
     "sglb200_moe_sum_reduce": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _f32, _vp]),
+    "sglb200_moe_sum_reduce_masked": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _f32, _vp]),
+    "sglb200_moe_align_drop_filtered": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "sglb200_gather_sum_rows": (_i32, [_vp, _vp, _vp, _i32, _i64, _i32, _i64, _i64, _f32, _vp]),
     "sglb200_shuffle_mul_sum": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _vp]),
     "sglb200_topk_softmax": (_i32, [_vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp]),

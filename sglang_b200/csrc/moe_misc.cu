@@ -75,6 +75,58 @@ __global__ void __launch_bounds__(256)
   reinterpret_cast<uint4*>(out)[c] = pack8<T>(acc);
 }
 
+// The same sum over the slots whose expert id is not negative: under expert parallelism a token's slots for experts
+// of other ranks are never written by the grouped GEMM and must not be read.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    moe_sum_reduce_masked_kernel(const T* __restrict__ x, const int32_t* __restrict__ ids, T* __restrict__ out,
+                                 int64_t total_chunks, int chunks_per_row, int topk, float scale) {
+  const int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (c >= total_chunks) return;
+  const int64_t t = c / chunks_per_row;
+  const int64_t cc = c - t * chunks_per_row;
+  const T* src = x + (t * topk) * (int64_t)chunks_per_row * 8 + cc * 8;
+  const int32_t* id = ids + t * topk;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < topk; k0 += 4) {  // up to four independent loads in flight
+    uint4 raw[4];
+    bool on[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      on[j] = k0 + j < topk && __ldg(id + k0 + j) >= 0;
+      if (on[j]) raw[j] = ld_nc_16(src + (int64_t)(k0 + j) * chunks_per_row * 8);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (on[j]) {
+        float v[8];
+        unpack8<T>(raw[j], v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] *= scale;
+  reinterpret_cast<uint4*>(out)[c] = pack8<T>(acc);
+}
+
+// Sorted order without its leading segment of filtered ids (bucket 0 = expert -1): everything after it moves to the
+// front, so that the kernels bounded by num_tokens_post_pad never touch rows of experts that are not on this rank.
+__global__ void __launch_bounds__(256)
+    drop_filtered_kernel(const int32_t* __restrict__ sorted_in, const int32_t* __restrict__ eids_in,
+                         const int32_t* __restrict__ cumsum, const int32_t* __restrict__ post_in,
+                         int32_t* __restrict__ sorted_out, int32_t* __restrict__ eids_out, int32_t* __restrict__ post_out,
+                         int block) {
+  const int begin = cumsum[1];  // padded length of bucket 0, a multiple of `block`
+  const int n = *post_in - begin;
+  const int stride = gridDim.x * 256;
+  for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += stride) sorted_out[i] = sorted_in[begin + i];
+  const int nb = n / block, b0 = begin / block;
+  for (int j = blockIdx.x * 256 + threadIdx.x; j < nb; j += stride) eids_out[j] = eids_in[b0 + j];
+  if (blockIdx.x == 0 && threadIdx.x == 0) *post_out = n;
+}
+
 // out[t, 8c..] = T(scale * sum_j src[slot[t, j], 8c..]) over the j with 0 <= slot[t, j] < src_rows, ascending j,
 // float32 accumulation; one thread per 8 outputs.
 template <typename T>
@@ -262,6 +314,48 @@ extern "C" int sglb200_gather_rows_fp8(const void* src_q, const float* src_s, vo
   gather_rows_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src_q), src_s, static_cast<uint4*>(dst_q), dst_s, sorted_token_ids, num_rows_dev, numel,
       topk, (int)(hidden / 16), (int)groups);
+  SGLB_CUDA(cudaGetLastError());
+  return SGLB200_OK;
+}
+
+extern "C" int sglb200_moe_sum_reduce_masked(const void* x, const int32_t* topk_ids, void* out, int dtype, int64_t tokens,
+                                             int64_t topk, int64_t hidden, float scale, void* stream) {
+  SGLB_REQUIRE(tokens >= 0 && topk >= 1 && hidden > 0 && hidden % 8 == 0,
+               "moe_sum_reduce_masked: tokens=%lld topk=%lld hidden=%lld (hidden must be a multiple of 8)",
+               (long long)tokens, (long long)topk, (long long)hidden);
+  if (tokens == 0) return SGLB200_OK;
+  SGLB_REQUIRE(x && topk_ids && out && aligned16(x) && aligned16(out), "moe_sum_reduce_masked: null or misaligned pointer");
+  const int64_t total = tokens * (hidden / 8);
+  const int64_t blocks = (total + 255) / 256;
+  SGLB_REQUIRE(blocks < (1ll << 31), "moe_sum_reduce_masked: input too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    moe_sum_reduce_masked_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), topk_ids, static_cast<__nv_bfloat16*>(out), total, (int)(hidden / 8),
+        (int)topk, scale);
+  else if (dtype == 1)
+    moe_sum_reduce_masked_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const __half*>(x), topk_ids, static_cast<__half*>(out), total, (int)(hidden / 8), (int)topk, scale);
+  else
+    return fail(SGLB200_E_UNSUPPORTED, "moe_sum_reduce_masked: dtype code %d (0 bf16, 1 fp16)", dtype);
+  SGLB_CUDA(cudaGetLastError());
+  return SGLB200_OK;
+}
+
+extern "C" int sglb200_moe_align_drop_filtered(const int32_t* sorted_in, const int32_t* expert_ids_in,
+                                               const int32_t* cumsum, const int32_t* post_in, int32_t* sorted_out,
+                                               int32_t* expert_ids_out, int32_t* post_out, int64_t max_rows,
+                                               int block_size, void* stream) {
+  SGLB_REQUIRE(sorted_in && expert_ids_in && cumsum && post_in && sorted_out && expert_ids_out && post_out,
+               "moe_align_drop_filtered: null pointer");
+  SGLB_REQUIRE(sorted_in != sorted_out && expert_ids_in != expert_ids_out, "moe_align_drop_filtered: outputs must not alias inputs");
+  SGLB_REQUIRE(max_rows >= 0 && max_rows < (1ll << 31) && block_size >= 1, "moe_align_drop_filtered: bad sizes");
+  int64_t blocks = (max_rows + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  const int64_t cap = (int64_t)sm_count() * 4;
+  if (blocks > cap) blocks = cap;
+  drop_filtered_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      sorted_in, expert_ids_in, cumsum, post_in, sorted_out, expert_ids_out, post_out, block_size);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }

@@ -140,6 +140,21 @@ def moe_sum_reduce_out(x: torch.Tensor, out: torch.Tensor, routed_scaling_factor
     check(lib.sglb200_moe_sum_reduce(x.data_ptr(), out.data_ptr(), _dt(x), t, k, h, float(routed_scaling_factor), _stream(x)))
 
 
+def moe_sum_reduce_masked_out(x: torch.Tensor, topk_ids: torch.Tensor, out: torch.Tensor,
+                              routed_scaling_factor: float) -> None:
+    """moe_sum_reduce over the slots whose id in `topk_ids` [tokens, topk] (int32) is not negative."""
+    _cuda_contig(x, "input")
+    _cuda_contig(out, "output")
+    _cuda_contig(topk_ids, "topk_ids")
+    if x.dim() != 3 or out.dim() != 2 or out.shape[0] != x.shape[0] or out.shape[1] != x.shape[2]:
+        raise RuntimeError("moe_sum_reduce: input [tokens, topk, hidden], output [tokens, hidden]")
+    if out.dtype != x.dtype or topk_ids.dtype != torch.int32 or tuple(topk_ids.shape) != tuple(x.shape[:2]):
+        raise RuntimeError("moe_sum_reduce: dtype or shape mismatch")
+    t, k, h = x.shape
+    check(lib.sglb200_moe_sum_reduce_masked(x.data_ptr(), topk_ids.data_ptr(), out.data_ptr(), _dt(x), t, k, h,
+                                            float(routed_scaling_factor), _stream(x)))
+
+
 def gather_sum_rows(src: torch.Tensor, slot: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     """out[t] = scale * sum_j src[slot[t, j]] (float32 accumulation); slots outside [0, len(src)) are skipped."""
     _cuda_contig(src, "src")
@@ -296,6 +311,23 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     cumsum = torch.empty((num_experts + 2,), dtype=torch.int32, device=dev)
     moe_align_block_size_out(topk_ids, num_experts + 1, block_size, sorted_ids, expert_ids, post, cumsum, True)
     return sorted_ids, expert_ids, post
+
+
+def moe_align_block_size_local(topk_ids: torch.Tensor, block_size: int, num_experts: int):
+    """The sort without its segment of filtered ids (-1 = expert of another rank): rows of local experts only."""
+    max_padded = topk_ids.numel() + (num_experts + 1) * (block_size - 1)
+    dev = topk_ids.device
+    nblk = (max_padded + block_size - 1) // block_size
+    sorted_ids = torch.empty((2, max_padded), dtype=torch.int32, device=dev)
+    expert_ids = torch.empty((2, nblk), dtype=torch.int32, device=dev)
+    post = torch.empty((2,), dtype=torch.int32, device=dev)
+    cumsum = torch.empty((num_experts + 2,), dtype=torch.int32, device=dev)
+    moe_align_block_size_out(topk_ids, num_experts + 1, block_size, sorted_ids[0], expert_ids[0], post[0:1], cumsum, True)
+    check(lib.sglb200_moe_align_drop_filtered(
+        sorted_ids[0].data_ptr(), expert_ids[0].data_ptr(), cumsum.data_ptr(), post[0:1].data_ptr(),
+        sorted_ids[1].data_ptr(), expert_ids[1].data_ptr(), post[1:2].data_ptr(), max_padded, int(block_size),
+        _stream(topk_ids)))
+    return sorted_ids[1], expert_ids[1], post[1:2]
 
 
 # --------------------------------------------------------------------------------------------

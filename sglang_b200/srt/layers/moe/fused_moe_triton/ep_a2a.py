@@ -117,7 +117,7 @@ def ep_all_to_all_forward(layer, hidden_states: torch.Tensor, topk_output) -> to
         out_rows = fused_experts_impl(
             q, layer.w13_weight, layer.w2_weight, w, local_ids, inplace=False, use_fp8_w8a8=True,
             w1_scale=layer.w13_weight_scale_inv, w2_scale=layer.w2_weight_scale_inv, block_shape=[128, 128],
-            routed_scaling_factor=1.0, a1_scale=s, out_dtype=hidden_states.dtype)
+            routed_scaling_factor=1.0, a1_scale=s, out_dtype=hidden_states.dtype, has_filtered_ids=True)
     else:
         out_rows = torch.empty((0, hidden_states.shape[1]), dtype=hidden_states.dtype, device=hidden_states.device)
     rsf = layer.moe_runner_config.routed_scaling_factor or 1.0

@@ -49,9 +49,12 @@ def fused_experts_impl(
     routed_scaling_factor: Optional[float] = None,
     a1_scale: Optional[torch.Tensor] = None,
     out_dtype: Optional[torch.dtype] = None,
+    has_filtered_ids: bool = False,
 ):
     """`a1_scale` given: `hidden_states` already holds e4m3 codes with these 1x128 scales (rows that
-    arrived quantised from other ranks); the output dtype is then `out_dtype`."""
+    arrived quantised from other ranks); the output dtype is then `out_dtype`.  `has_filtered_ids`: `topk_ids` may
+    hold -1 (experts of other ranks, expert parallelism); their rows are then kept out of every kernel instead of
+    being carried along and written as zeros."""
     if not use_fp8_w8a8 or block_shape is None or list(block_shape) != [128, 128]:
         raise NotImplementedError("only use_fp8_w8a8 with block_shape [128, 128] is on this path")
     if activation != "silu" or not is_gated:
@@ -99,25 +102,34 @@ def fused_experts_impl(
             xq, xs = x, a1_scale[begin:end]
         else:
             xq, xs = _ops.per_token_group_quant_fp8(x, 128)
-        sorted_ids, expert_ids, post = _ops.moe_align_block_size(ids, _ops.ALIGN_BLOCK, E)
+        direct = no_combine or (topk == 1 and routed_scaling_factor == 1.0)
+        drop = has_filtered_ids and not direct  # (the direct forms need the zero rows of filtered slots in `out`)
+        if drop:
+            # rows of experts that live on other ranks (id -1) are dropped from the sorted order: they would only be
+            # gathered, zero-filled and read back by every kernel below
+            sorted_ids, expert_ids, post = _ops.moe_align_block_size_local(ids, _ops.ALIGN_BLOCK, E)
+        else:
+            sorted_ids, expert_ids, post = _ops.moe_align_block_size(ids, _ops.ALIGN_BLOCK, E)
         max_rows = _max_padded_rows(numel, E, _ops.ALIGN_BLOCK)
         a1, a1s = _ops.gather_rows_fp8(xq, xs, sorted_ids, post, numel, topk, max_rows)
         ic1 = _ops.grouped_block_fp8_matmul(a1, a1s, w1, w1_scale, sorted_ids, expert_ids, post, numel=numel,
                                             scatter=False, output_dtype=act_dtype)
         a2, a2s = _ops.silu_and_mul_quant_fp8(ic1, 128, num_rows=post)
-        direct = no_combine or (topk == 1 and routed_scaling_factor == 1.0)
         ic3 = out[begin:end].view(numel, -1) if direct else None
         ic3 = _ops.grouped_block_fp8_matmul(a2, a2s, w2, w2_scale, sorted_ids, expert_ids, post, numel=numel,
                                             scatter=True,
                                             row_weights=None if apply_router_weight_on_input else wts,
                                             out=ic3, output_dtype=act_dtype)
         if not direct:
-            _ops.moe_sum_reduce_out(ic3.view(t, topk, -1), out[begin:end], routed_scaling_factor)
+            if drop:
+                _ops.moe_sum_reduce_masked_out(ic3.view(t, topk, -1), ids, out[begin:end], routed_scaling_factor)
+            else:
+                _ops.moe_sum_reduce_out(ic3.view(t, topk, -1), out[begin:end], routed_scaling_factor)
     return out
 
 
 def fused_experts(hidden_states, w13_weight, w2_weight, topk_output, moe_runner_config, *, w13_scale, w2_scale,
-                  block_shape):
+                  block_shape, has_filtered_ids: bool = False):
     """`fused_experts` (:261-319) with the quantisation info spelled out."""
     topk_weights, topk_ids = topk_output[0], topk_output[1]
     return fused_experts_impl(
@@ -127,4 +139,5 @@ def fused_experts(hidden_states, w13_weight, w2_weight, topk_output, moe_runner_
         apply_router_weight_on_input=moe_runner_config.apply_router_weight_on_input,
         use_fp8_w8a8=True, w1_scale=w13_scale, w2_scale=w2_scale, block_shape=block_shape,
         no_combine=moe_runner_config.no_combine, routed_scaling_factor=moe_runner_config.routed_scaling_factor,
+        has_filtered_ids=has_filtered_ids,
     )

@@ -212,5 +212,6 @@ class Fp8MoEMethod:
         output = fused_experts(
             dispatch_output.hidden_states, layer.w13_weight, layer.w2_weight, dispatch_output.topk_output, cfg,
             w13_scale=layer.w13_weight_scale_inv, w2_scale=layer.w2_weight_scale_inv,
-            block_shape=self.quant_config.weight_block_size)
+            block_shape=self.quant_config.weight_block_size,
+            has_filtered_ids=getattr(layer, "moe_ep_size", 1) > 1)
         return StandardCombineInput(hidden_states=output)

@@ -122,6 +122,24 @@ def test_fused_experts_matches_oracle(ops, T, E, H, I, topk, filtered):
     assert ops.gemm_status() == 0
     # intermediate fp8 codes may differ by one code where silu's expf differs by an ulp: same tolerance
     assert_close_fp(to_f32_np(out), ref, atol=2e-2)
+    # the expert-parallel form, which drops the rows of filtered (-1) ids instead of carrying them as zeros, must
+    # give the very same bits (also when there is nothing to drop)
+    out2 = fused_experts_impl(
+        x.cuda(), codes_to_fp8(w13q), codes_to_fp8(w2q), w.cuda(), ids.cuda(), use_fp8_w8a8=True,
+        w1_scale=torch.from_numpy(w13s).cuda(), w2_scale=torch.from_numpy(w2s).cuda(), block_shape=[128, 128],
+        has_filtered_ids=True)
+    assert torch.equal(out, out2)
+
+
+def test_fused_experts_all_ids_filtered(ops):
+    from sglang_b200.srt.layers.moe.fused_moe_triton.fused_moe import fused_experts_impl
+    x, w13q, w13s, w2q, w2s, w, ids = _moe_inputs(40, 8, 512, 256, 4, seed=5)
+    ids = torch.full_like(ids, -1)
+    out = fused_experts_impl(
+        x.cuda(), codes_to_fp8(w13q), codes_to_fp8(w2q), w.cuda(), ids.cuda(), use_fp8_w8a8=True,
+        w1_scale=torch.from_numpy(w13s).cuda(), w2_scale=torch.from_numpy(w2s).cuda(), block_shape=[128, 128],
+        has_filtered_ids=True)
+    assert out.shape == (40, 512) and not out.float().abs().any()
 
 
 def test_moe_golden_fixture(ops, golden_dir):
