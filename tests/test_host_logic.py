@@ -171,3 +171,23 @@ def test_sgl_kernel_ops_have_shape_only_implementations():
     tw = torch.empty(7, 4, device="meta")
     ti = torch.empty(7, 4, dtype=torch.int32, device="meta")
     assert torch.ops.sgl_kernel.topk_softmax.default(tw, ti, torch.empty(7, 64, device="meta"), True, 0.0, None) is None
+
+
+def test_fused_row_parallel_shape_rules():
+    """Which outputs the GEMM-fused all-reduce takes and how rows are owned (host logic only, no GPU)."""
+    from sglang_b200._lib import lib
+    from sglang_b200.srt.distributed.fused_row_parallel import FusedRowParallelComm
+    assert lib.sglb200_push_rows_per_owner(8192, 8) == 1024
+    assert lib.sglb200_push_rows_per_owner(300, 2) == 256      # owner 0: 256 rows, owner 1: 44
+    assert lib.sglb200_push_rows_per_owner(1068, 8) == 256     # owners 0-3 full, owner 4: 44 rows, owners 5-7: none
+    comm = object.__new__(FusedRowParallelComm)
+    comm.world, comm.max_elems = 8, 8192 * 8192
+    assert comm.supports(8192, 8192) and comm.supports(1024, 8192) and comm.supports(5000, 8192)
+    assert not comm.supports(1023, 8192)        # fewer than one tile of rows per rank
+    assert not comm.supports(8192, 8196)        # rows of 16-byte pieces only
+    assert not comm.supports(8192 + 1, 8192)    # its staging copy (8 x 1152 rows) does not fit
+    comm.pipeline, comm.min_comm_ratio, comm.min_waves, comm.sms, comm.sm_margin = False, 0.4, 3, 148, 16
+    assert comm._chunks(8192, 8192, 1024) == 1  # chunked pipelining is off by default
+    comm.pipeline = True
+    assert comm._chunks(8192, 8192, 1024) == 4 and comm._chunks(8192, 8192, 14336) == 1
+    assert comm._chunks(5000, 8192, 1024) == 1  # ragged row counts are never chunked
