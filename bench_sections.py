@@ -117,7 +117,9 @@ def gemm_sweep(args, ctx, peaks):
         torch.cuda.empty_cache()
     return {"gemm_sweep": {"unit": "us / TFLOP/s / GB/s (algorithmic bytes)", "l2": "weight copies rotated so that "
                            "consecutive launches exceed the 126 MB L2", "layers": out,
-                           "hbm_peak_gbs": peaks["hbm_gbs"], "fp8_peak_tflops": 2 * peaks["bf16"]}}
+                           "hbm_peak_gbs": peaks["hbm_gbs"],
+                           "fp8_peak_tflops": peaks.get("fp8_measured", 2 * peaks["bf16"]),
+                           "fp8_peak_source": "the same denominator as roofline.peak of this line"}}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -127,30 +129,37 @@ def gemm_sweep(args, ctx, peaks):
 
 def tp_layer(args, ctx, peaks):
     """QKV (column) -> o_proj (row + all-reduce) -> gate_up (column) -> silu_and_mul + quantizer -> down (row + all-reduce).
-    Attention itself is not on this path: o_proj is fed a tensor of the attention output's shape."""
+    Attention itself is not on this path: o_proj is fed a tensor of the attention output's shape.
+    With more than one rank: a parity check of the sharded layer first (`tp_parity`), then the unsharded layer timed
+    on every GPU by itself (`ms_1gpu_eager`, the numerator of the strong-scaling efficiency), then the sharded layer
+    with the NCCL all-reduce and with the GEMM-fused all-reduce.  Every size is timed from eager launches at every
+    rank count (`ms_eager`); on one GPU the launch-bound sizes are also replayed from a CUDA graph (`ms`)."""
     from sglang_b200 import ops
-    from sglang_b200.srt.distributed import initialize_model_parallel
+    from sglang_b200.srt.distributed import destroy_model_parallel, enable_fused_row_parallel, initialize_model_parallel
+    from sglang_b200.srt.distributed.fused_row_parallel import comm_status
     from sglang_b200.srt.layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
     from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
     rank, world, dev = ctx
-    initialize_model_parallel(world, world)
+    parity = tp_parity(ctx) if world > 1 else None
     cfg = Fp8Config()
     H, I, heads, kv_heads, hd = 8192, 28672, 64, 8, 128
-    gen = torch.Generator(device=dev).manual_seed(11 + rank)
-    qkv = QKVParallelLinear(H, hd, heads, kv_heads, quant_config=cfg, device=dev)
-    o_proj = RowParallelLinear(heads * hd, H, quant_config=cfg, device=dev)
-    gate_up = MergedColumnParallelLinear(H, [I, I], quant_config=cfg, device=dev)
-    down = RowParallelLinear(I, H, quant_config=cfg, device=dev)
-    for lin in (qkv, o_proj, gate_up, down):
-        _fill_weight(lin.weight.data, lin.weight_scale_inv.data, gen)
     flops_per_token = 2.0 * (H * (heads + 2 * kv_heads) * hd + heads * hd * H + H * 2 * I + I * H)
-    res = {}
     sizes = (8, 128, 2048, 8192)
-    inputs = {M: (torch.randn(M, H, device=dev, generator=gen).bfloat16(),
-                  torch.randn(M, heads * hd // world, device=dev, generator=gen).bfloat16()) for M in sizes}
+    res = {str(M): {"allreduce_bytes": 2 * M * H * 2} for M in sizes}
 
-    def run_all(key):
-        for M in sizes:
+    def build(tp):
+        initialize_model_parallel(tp, tp)
+        gen = torch.Generator(device=dev).manual_seed(11 + rank)
+        qkv = QKVParallelLinear(H, hd, heads, kv_heads, quant_config=cfg, device=dev)
+        o_proj = RowParallelLinear(heads * hd, H, quant_config=cfg, device=dev)
+        gate_up = MergedColumnParallelLinear(H, [I, I], quant_config=cfg, device=dev)
+        down = RowParallelLinear(I, H, quant_config=cfg, device=dev)
+        for lin in (qkv, o_proj, gate_up, down):
+            _fill_weight(lin.weight.data, lin.weight_scale_inv.data, gen)
+        inputs = {M: (torch.randn(M, H, device=dev, generator=gen).bfloat16(),
+                      torch.randn(M, heads * hd // tp, device=dev, generator=gen).bfloat16()) for M in sizes}
+
+        def layer_for(M):
             x, attn = inputs[M]
 
             def layer():
@@ -160,36 +169,54 @@ def tp_layer(args, ctx, peaks):
                 # activation and the 1x128 quantisation of down's input in one pass; `apply` takes (codes, scales)
                 down(ops.silu_and_mul_quant_fp8(gu, 128))
 
-            ms = _time(layer, 10 if M >= 2048 else 20, 3, world, dev)
-            res.setdefault(str(M), {"allreduce_bytes": 2 * M * H * 2})[key] = ms
-            if world == 1 and M <= 128:
-                res[str(M)]["ms_eager"] = ms
-                res[str(M)][key] = _time_graph(layer, 20, 3, dev)
-                res[str(M)]["launch"] = "cuda graph"
+            return layer
 
-    run_all("ms_nccl" if world > 1 else "ms")
-    if world > 1:
+        return layer_for
+
+    def time_all(layer_for, key, ranks):
+        for M in sizes:
+            res[str(M)][key] = _time(layer_for(M), 10 if M >= 2048 else 20, 3, ranks, dev)
+
+    status = 0
+    if world == 1:
+        layer_for = build(1)
+        time_all(layer_for, "ms_eager", 1)
+        for M in sizes:
+            r = res[str(M)]
+            r["ms"] = r["ms_eager"]
+            if M <= 128:
+                r["ms"] = _time_graph(layer_for(M), 20, 3, dev)
+                r["launch"] = "cuda graph"
+    else:
+        layer_for = build(1)  # the whole layer on this GPU alone: no collective, every rank times its own copy
+        time_all(layer_for, "ms_1gpu_eager", world)
+        del layer_for
+        torch.cuda.empty_cache()
+        layer_for = build(world)
+        time_all(layer_for, "ms_nccl", world)
         # the same layer with the all-reduce of o_proj and down fused into their GEMMs where the shape allows
         # (at least 128 x world rows); smaller batches keep the NCCL all-reduce and repeat the number above
-        from sglang_b200.srt.distributed import destroy_model_parallel, enable_fused_row_parallel
-        from sglang_b200.srt.distributed.fused_row_parallel import comm_status
         comm = enable_fused_row_parallel(max(sizes) * H)
-        run_all("ms_fused")
+        time_all(layer_for, "ms_fused", world)
         for M in sizes:
             r = res[str(M)]
             r["fused_all_reduce"] = bool(comm.supports(M, H))
             r["ms"] = r["ms_fused"] if r["fused_all_reduce"] else r["ms_nccl"]
+            r["ms_eager"] = r["ms"]
+            r["efficiency_vs_1gpu"] = r["ms_1gpu_eager"] / (world * r["ms"])
         status = comm_status()
         destroy_model_parallel()
-    else:
-        status = 0
     for M in sizes:
         res[str(M)]["tflops"] = flops_per_token * M / res[str(M)]["ms"] / 1e9
-    return {"tp_layer": {"config": "BASELINE config 2: Llama-3-70B layer (hidden 8192, inter 28672, 64q/8kv x 128), "
-                                   "QKV + gate_up column-parallel, o_proj + down row-parallel; the sum over ranks is "
-                                   "an NCCL all-reduce (ms_nccl) or the GEMM-fused all-reduce over peer memory "
-                                   "(ms_fused); ms is the fused form where the shape allows it",
-                         "tp": world, "scaling": "strong", "comm_status": status, "results": res}}
+    out = {"config": "BASELINE config 2: Llama-3-70B layer (hidden 8192, inter 28672, 64q/8kv x 128), "
+                     "QKV + gate_up column-parallel, o_proj + down row-parallel; the sum over ranks is "
+                     "an NCCL all-reduce (ms_nccl) or the GEMM-fused all-reduce over peer memory "
+                     "(ms_fused); ms is the fused form where the shape allows it; ms_1gpu_eager = the unsharded "
+                     "layer on one GPU of this box in this run",
+           "tp": world, "scaling": "strong", "comm_status": status, "results": res}
+    if parity is not None:
+        out["parity"] = parity
+    return {"tp_layer": out}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -198,6 +225,8 @@ def tp_layer(args, ctx, peaks):
 
 
 def moe_layer(args, ctx, peaks):
+    """With more than one rank: `ep_parity` first, then the whole layer (all 256 experts) timed on every GPU by itself
+    (`ms_1gpu_eager`: the numerator of the weak-scaling efficiency), then the expert-parallel layer."""
     from sglang_b200 import ops
     from sglang_b200.srt.distributed import initialize_model_parallel
     from sglang_b200.srt.layers.linear import ColumnParallelLinear
@@ -206,44 +235,69 @@ def moe_layer(args, ctx, peaks):
     from sglang_b200.srt.layers.moe.topk import biased_grouped_topk
     from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
     rank, world, dev = ctx
-    initialize_model_parallel(1, world)
+    parity = ep_parity(ctx) if world > 1 else None
     cfg = Fp8Config()
     E, H, I, topk = 256, 7168, 2048, 8
-    gen = torch.Generator(device=dev).manual_seed(23 + rank)
-    # (every rank holds the same number of tokens here, so decode-sized batches may take the gather form)
-    moe = FusedMoE(E, H, I, topk, quant_config=cfg, a2a_backend="nccl", device=dev, equal_tokens_gather_below=2048)
-    _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
-    _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
-    # the shared expert is a dense block-FP8 MLP replicated on every rank (models/deepseek_v2.py:826-882)
-    sh_gate_up = ColumnParallelLinear(H, 2 * I, quant_config=cfg, device=dev)
-    sh_down = ColumnParallelLinear(I, H, quant_config=cfg, device=dev)
-    for lin in (sh_gate_up, sh_down):
-        _fill_weight(lin.weight.data, lin.weight_scale_inv.data, gen)
-    res = {}
-    for T in (1, 64, 512, 4096):
-        x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
-        logits = torch.randn(T, E, device=dev, generator=gen)
-        w, ids = biased_grouped_topk(logits, None, topk, True, 8, 4)
-        top = StandardTopKOutput(w, ids, None)
+    sizes = (1, 64, 512, 4096)
+    res = {str(T): {} for T in sizes}
 
-        def layer():
-            routed = moe(x, top)
-            gu, _ = sh_gate_up(x)
-            shared, _ = sh_down(ops.silu_and_mul_quant_fp8(gu, 128))
-            return routed + shared
+    def build(ep):
+        initialize_model_parallel(1, ep)
+        gen = torch.Generator(device=dev).manual_seed(23 + rank)
+        # (every rank holds the same number of tokens here, so decode-sized batches may take the gather form)
+        moe = FusedMoE(E, H, I, topk, quant_config=cfg, a2a_backend="nccl", device=dev, equal_tokens_gather_below=2048)
+        _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
+        _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
+        # the shared expert is a dense block-FP8 MLP replicated on every rank (models/deepseek_v2.py:826-882)
+        sh_gate_up = ColumnParallelLinear(H, 2 * I, quant_config=cfg, device=dev)
+        sh_down = ColumnParallelLinear(I, H, quant_config=cfg, device=dev)
+        for lin in (sh_gate_up, sh_down):
+            _fill_weight(lin.weight.data, lin.weight_scale_inv.data, gen)
 
+        def layer_for(T):
+            x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
+            logits = torch.randn(T, E, device=dev, generator=gen)
+            w, ids = biased_grouped_topk(logits, None, topk, True, 8, 4)
+            top = StandardTopKOutput(w, ids, None)
+
+            def layer():
+                routed = moe(x, top)
+                gu, _ = sh_gate_up(x)
+                shared, _ = sh_down(ops.silu_and_mul_quant_fp8(gu, 128))
+                return routed + shared
+
+            return layer
+
+        return layer_for
+
+    if world > 1:
+        layer_for = build(1)
+        for T in sizes:
+            res[str(T)]["ms_1gpu_eager"] = _time(layer_for(T), 10, 3, world, dev)
+        del layer_for
+        torch.cuda.empty_cache()
+    layer_for = build(world)
+    for T in sizes:
+        layer = layer_for(T)
         ms = _time(layer, 10, 3, world, dev)
-        extra = {}
+        r = res[str(T)]
+        r["ms_eager"] = r["ms"] = ms
         if world == 1 and T <= 512:
-            extra = {"ms_eager": ms, "launch": "cuda graph"}
-            ms = _time_graph(layer, 10, 3, dev)
+            r["launch"] = "cuda graph"
+            r["ms"] = _time_graph(layer, 10, 3, dev)
+        if world > 1:
+            r["efficiency_vs_1gpu"] = r["ms_1gpu_eager"] / ms
         flops = 6.0 * T * topk * H * I + 6.0 * T * H * I
-        res[str(T)] = {"ms": ms, "tokens_per_s": world * T / ms * 1e3, "tflops_per_gpu": flops / ms / 1e9, **extra}
-    return {"moe_layer": {"config": "BASELINE config 3: DeepSeek-V3 MoE, 256 routed experts + 1 shared, hidden 7168, "
-                                    "moe_intermediate 2048, top-8 grouped sigmoid routing (8 groups, top-4), "
-                                    "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine (batches of at "
-                                    "most 2048 tokens over all ranks: all-gather, local experts, reduce-scatter)",
-                          "ep": world, "scaling": "weak", "results": res}}
+        r.update({"tokens_per_s": world * T / r["ms"] * 1e3, "tflops_per_gpu": flops / r["ms"] / 1e9})
+    out = {"config": "BASELINE config 3: DeepSeek-V3 MoE, 256 routed experts + 1 shared, hidden 7168, "
+                     "moe_intermediate 2048, top-8 grouped sigmoid routing (8 groups, top-4), "
+                     "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine (batches of at "
+                     "most 2048 tokens over all ranks: all-gather, local experts, reduce-scatter); ms_1gpu_eager = "
+                     "the layer with all experts on one GPU of this box in this run",
+           "ep": world, "scaling": "weak", "results": res}
+    if parity is not None:
+        out["parity"] = parity
+    return {"moe_layer": out}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -254,48 +308,69 @@ def moe_layer(args, ctx, peaks):
 def moe_layer_skewed(args, ctx, peaks):
     """128 experts, hidden 2048, moe_intermediate 768, top-8 softmax routing; the logits carry log(p_e) with
     p_e ~ rank^-1.2 over a seeded permutation of the experts.  Reports the layer time (max over ranks), this
-    rank's own time and the spread of tokens per local expert, i.e. the load-imbalance tail."""
+    rank's own time and the spread of tokens per local expert, i.e. the load-imbalance tail.  With more than one
+    rank the whole layer (all experts) is first timed on every GPU by itself (`ms_1gpu_eager`)."""
     from sglang_b200.srt.distributed import initialize_model_parallel
     from sglang_b200.srt.layers.moe.fused_moe_triton.layer import FusedMoE
     from sglang_b200.srt.layers.moe.token_dispatcher import StandardTopKOutput
     from sglang_b200.srt.layers.moe.topk import fused_topk
     from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
     rank, world, dev = ctx
-    initialize_model_parallel(1, world)
     E, H, I, topk = 128, 2048, 768, 8
-    gen = torch.Generator(device=dev).manual_seed(41 + rank)
-    moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="nccl", device=dev,
-                   equal_tokens_gather_below=2048)
-    _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
-    _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
+    sizes = (32, 1024, 16384)
     perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))  # the same popularity order on every rank
     logp = torch.empty(E)
     logp[perm] = -1.2 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
     logp = logp.to(dev)
-    res = {}
-    for T in (32, 1024, 16384):
-        x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
-        logits = torch.randn(T, E, device=dev, generator=gen) + logp
-        w, ids = fused_topk(logits, topk, True)
-        top = StandardTopKOutput(w, ids, None)
-        counts = torch.bincount(ids.flatten().long(), minlength=E).float()
-        ms = _time(lambda: moe(x, top), 10, 3, world, dev)
-        extra = {}
+    res = {str(T): {} for T in sizes}
+
+    def build(ep):
+        initialize_model_parallel(1, ep)
+        gen = torch.Generator(device=dev).manual_seed(41 + rank)
+        moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="nccl", device=dev,
+                       equal_tokens_gather_below=2048)
+        _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
+        _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
+
+        def layer_for(T):
+            x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
+            logits = torch.randn(T, E, device=dev, generator=gen) + logp
+            w, ids = fused_topk(logits, topk, True)
+            top = StandardTopKOutput(w, ids, None)
+            counts = torch.bincount(ids.flatten().long(), minlength=E).float()
+            return (lambda: moe(x, top)), counts
+
+        return layer_for
+
+    if world > 1:
+        layer_for = build(1)
+        for T in sizes:
+            res[str(T)]["ms_1gpu_eager"] = _time(layer_for(T)[0], 10, 3, world, dev)
+        del layer_for
+        torch.cuda.empty_cache()
+    layer_for = build(world)
+    for T in sizes:
+        layer, counts = layer_for(T)
+        ms = _time(layer, 10, 3, world, dev)
+        r = res[str(T)]
+        r["ms_eager"] = r["ms"] = ms
         if world == 1 and T <= 1024:
-            extra = {"ms_eager": ms, "launch": "cuda graph"}
-            ms = _time_graph(lambda: moe(x, top), 10, 3, dev)
+            r["launch"] = "cuda graph"
+            r["ms"] = _time_graph(layer, 10, 3, dev)
+        if world > 1:
+            r["efficiency_vs_1gpu"] = r["ms_1gpu_eager"] / ms
         # this rank alone, without the barrier-and-max: the gap to `ms` at EP > 1 is the wait for the busiest rank
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
         for _ in range(10):
-            moe(x, top)
+            layer()
         e1.record()
         torch.cuda.synchronize()
-        res[str(T)] = {"ms": ms, "ms_this_rank": e0.elapsed_time(e1) / 10, "tokens_per_s": world * T / ms * 1e3,
-                       "tflops_per_gpu": 6.0 * T * topk * H * I / ms / 1e9,
-                       "routed_per_expert_max_over_mean": float(counts.max() / counts.mean()),
-                       "experts_hit": int((counts > 0).sum()), **extra}
+        r.update({"ms_this_rank": e0.elapsed_time(e1) / 10, "tokens_per_s": world * T / r["ms"] * 1e3,
+                  "tflops_per_gpu": 6.0 * T * topk * H * I / r["ms"] / 1e9,
+                  "routed_per_expert_max_over_mean": float(counts.max() / counts.mean()),
+                  "experts_hit": int((counts > 0).sum())})
     return {"moe_layer_skewed": {"config": "BASELINE config 4: Qwen3-30B-A3B MoE, 128 experts, hidden 2048, "
                                            "moe_intermediate 768, top-8 softmax routing, Zipf(1.2) expert popularity, "
                                            "tokens per GPU as keyed",
@@ -363,6 +438,161 @@ def hbm_kernels(args, ctx, peaks):
     return {"hbm_kernels": {"unit": "us, GB/s of algorithmic bytes, fraction of MEASURED_PEAKS hbm_gbs", "kernels": out}}
 
 
+# ------------------------------------------------------------------------------------------------
+# parity of the sharded paths, checked inside the run (no second GPU is needed to see the result: it is part of
+# the JSON line, and a mismatch fails the run)
+# ------------------------------------------------------------------------------------------------
+
+
+class ParityError(AssertionError):
+    pass
+
+
+def _close(out: torch.Tensor, ref: torch.Tensor, what: str, rtol=2e-2, atol=2e-2, min_cos=0.9995):
+    """The tolerance of the multi-GPU tests: |out - ref| <= atol + rtol |ref| everywhere, cosine >= min_cos."""
+    o, r = out.double(), ref.double()
+    bad = (o - r).abs() > atol + rtol * r.abs()
+    den = (o * o).sum().sqrt() * (r * r).sum().sqrt()
+    cos = float((o * r).sum() / den) if float(den) > 0 else 1.0
+    if bool(bad.any()) or cos < min_cos or not bool(torch.isfinite(o).all()):
+        raise ParityError(f"{what}: {int(bad.sum())} of {bad.numel()} elements outside rtol {rtol} / atol {atol}, "
+                          f"cosine {cos:.6f} (needs {min_cos}), max |diff| {float((o - r).abs().max()):.4g}")
+    return cos
+
+
+def _same_on_all_ranks(t: torch.Tensor, world: int, what: str):
+    import torch.distributed as dist
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous())
+    for r, q in enumerate(parts):
+        if not torch.equal(q, parts[0]):
+            raise ParityError(f"{what}: rank {r} differs from rank 0 bit for bit")
+
+
+def tp_parity(ctx):
+    """A small tensor-parallel MLP (gate_up column-parallel -> silu_and_mul + quantiser -> down row-parallel) against
+    the same layer computed on this GPU alone from the unsharded weights; with the fused all-reduce, every rank's
+    rows bit-identical, and at two ranks bit-identical to GEMM + NCCL."""
+    from sglang_b200 import ops
+    from sglang_b200.srt.distributed import destroy_model_parallel, enable_fused_row_parallel, initialize_model_parallel
+    from sglang_b200.srt.distributed.fused_row_parallel import comm_status
+    from sglang_b200.srt.layers.linear import MergedColumnParallelLinear, RowParallelLinear
+    from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+    from bench import make_block_fp8_weight
+    rank, world, dev = ctx
+    initialize_model_parallel(world, world)
+    cfg = Fp8Config()
+    H, I = 1024, 2048
+    gen = torch.Generator(device=dev).manual_seed(97)  # the same full weights and tokens on every rank
+    w1q, w1s = make_block_fp8_weight(2 * I, H, dev, gen)
+    w2q, w2s = make_block_fp8_weight(H, I, dev, gen)
+    gate_up = MergedColumnParallelLinear(H, [I, I], quant_config=cfg, device=dev)
+    down = RowParallelLinear(I, H, quant_config=cfg, device=dev)
+    gate_up.load_full_weight(w1q, w1s)
+    down.load_full_weight(w2q, w2s)
+    sizes = (70, 128 * world + 44, 4 * 128 * world)
+    xs = [torch.randn(M, H, device=dev, generator=gen).bfloat16() for M in sizes]
+
+    def alone(x):
+        xq, xsc = ops.per_token_group_quant_fp8(x, 128)
+        gu = ops.w8a8_block_fp8_matmul(xq, w1q, xsc, w1s, [128, 128], torch.bfloat16)
+        hq, hs = ops.silu_and_mul_quant_fp8(gu, 128)
+        return ops.w8a8_block_fp8_matmul(hq, w2q, hs, w2s, [128, 128], torch.bfloat16)
+
+    def sharded(x):
+        gu, _ = gate_up(x)
+        y, _ = down(ops.silu_and_mul_quant_fp8(gu, 128))
+        return y
+
+    refs = [alone(x) for x in xs]
+    nccl = [sharded(x).clone() for x in xs]
+    comm = enable_fused_row_parallel(max(sizes) * H)
+    fused = [sharded(x).clone() for x in xs]
+    fused2 = [sharded(x).clone() for x in xs]  # flags and staging are reused by later calls
+    torch.cuda.synchronize()
+    cos = 1.0
+    for M, r, a, b, b2 in zip(sizes, refs, nccl, fused, fused2):
+        cos = min(cos, _close(a, r, f"TP layer, NCCL all-reduce, M={M}"), _close(b, r, f"TP layer, fused all-reduce, M={M}"))
+        if not torch.equal(b, b2):
+            raise ParityError(f"TP layer, fused all-reduce, M={M}: a repeated call differs")
+        if comm.supports(M, H):
+            _same_on_all_ranks(b, world, f"TP layer, fused all-reduce, M={M}")
+            if world == 2 and not torch.equal(a, b):
+                raise ParityError(f"TP layer, M={M}: fused all-reduce differs from GEMM + NCCL at two ranks")
+    status = (ops.gemm_status(), comm_status())
+    destroy_model_parallel()
+    if status != (0, 0):
+        raise ParityError(f"TP parity: status words {status}")
+    return {"ok": True, "min_cosine": cos, "sizes": list(sizes)}
+
+
+def ep_parity(ctx):
+    """A small expert-parallel MoE layer in its three forms (all-to-all, gather, replicate + all-reduce) against
+    fused_experts_impl on this GPU alone with all experts."""
+    from sglang_b200 import ops
+    from sglang_b200.srt.distributed import initialize_model_parallel
+    from sglang_b200.srt.layers.moe.fused_moe_triton.fused_moe import fused_experts_impl
+    from sglang_b200.srt.layers.moe.fused_moe_triton.layer import FusedMoE
+    from sglang_b200.srt.layers.moe.token_dispatcher import StandardTopKOutput
+    from sglang_b200.srt.layers.moe.topk import fused_topk
+    from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
+    from bench import make_block_fp8_weight
+    rank, world, dev = ctx
+    initialize_model_parallel(1, world)
+    E, H, I, topk = 16, 512, 256, 2
+    gen = torch.Generator(device=dev).manual_seed(131)  # the same full weights on every rank
+    w13q, w13s = make_block_fp8_weight(2 * I, H, dev, gen, std=0.05, experts=E)
+    w2q, w2s = make_block_fp8_weight(H, I, dev, gen, std=0.05, experts=E)
+    gen_r = torch.Generator(device=dev).manual_seed(1000 + rank)  # this rank's own tokens
+    cos = 1.0
+    for form, T in (("a2a", 33 + rank), ("gather", 32), ("allreduce", 32)):
+        g = gen if form == "allreduce" else gen_r  # the replicate form holds the same tokens on every rank
+        x = torch.randn(T, H, device=dev, generator=g).bfloat16()
+        w, ids = fused_topk(torch.randn(T, E, device=dev, generator=g), topk, True)
+        moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="none" if form == "allreduce" else "nccl",
+                       device=dev, equal_tokens_gather_below=1024 if form == "gather" else None)
+        moe.load_full_weights(w13q, w13s, w2q, w2s)
+        out = moe(x, StandardTopKOutput(w, ids, None))
+        ref = fused_experts_impl(x, w13q, w2q, w, ids, use_fp8_w8a8=True, w1_scale=w13s, w2_scale=w2s,
+                                 block_shape=[128, 128])
+        torch.cuda.synchronize()
+        cos = min(cos, _close(out, ref, f"EP layer, {form} form, {T} tokens"))
+    if ops.gemm_status() != 0:
+        raise ParityError("EP parity: a GEMM pipeline wait expired")
+    return {"ok": True, "min_cosine": cos}
+
+
+def sharded_summary(out, world):
+    """The sharded layers of one run in a few hundred characters, printed as the LAST key of the JSON line: per size
+    the eager time (max over ranks) and its efficiency against the same layer timed on ONE GPU of the same box in
+    the same run with the same (eager) protocol: strong scaling t1 / (N tN) for the tensor-parallel layer, weak
+    scaling t1 / tN for the expert-parallel layers (tokens per GPU fixed)."""
+    s = {}
+    tp = out.get("tp_layer", {}).get("results", {})
+    for M in ("8192", "2048", "128"):
+        r = tp.get(M)
+        if r and "ms_eager" in r:
+            d = {"ms": round(r["ms_eager"], 4)}
+            if "ms_1gpu_eager" in r:
+                d["eff"] = round(r["ms_1gpu_eager"] / (world * r["ms_eager"]), 3)
+            s[f"tp_M{M}"] = d
+    for key, name, sizes in (("moe_layer", "ep3", ("4096", "64", "1")), ("moe_layer_skewed", "ep4", ("16384", "32"))):
+        res = out.get(key, {}).get("results", {})
+        for T in sizes:
+            r = res.get(T)
+            if r and "ms_eager" in r:
+                d = {"ms": round(r["ms_eager"], 4)}
+                if "ms_1gpu_eager" in r:
+                    d["eff"] = round(r["ms_1gpu_eager"] / r["ms_eager"], 3)
+                s[f"{name}_T{T}"] = d
+    par = [out.get(k, {}).get("parity") for k in ("tp_layer", "moe_layer")]
+    par = [p for p in par if p is not None]
+    s["parity"] = (all(p.get("ok") for p in par) if par else None) if world > 1 else None
+    s["n_gpus"] = world
+    s["protocol"] = "eager launches, CUDA events, max over ranks; eff vs 1 GPU of this box, same run"
+    return s
+
+
 def run(sections, args, ctx, peaks):
     out = {}
     rank, world, dev = ctx
@@ -380,4 +610,6 @@ def run(sections, args, ctx, peaks):
         torch.cuda.empty_cache()
         out.update(moe_layer_skewed(args, ctx, peaks))
         torch.cuda.empty_cache()
+    if "tp" in sections or "moe" in sections:
+        out["sharded"] = sharded_summary(out, world)  # last key of the JSON line
     return out

@@ -88,8 +88,9 @@ int sglb200_silu_and_mul_quant_fp8(const void* input, int dtype, void* output_q,
  * topk_ids [numel] int32; sorted_token_ids [numel + num_experts*(block_size-1)] int32;
  * expert_ids [ceil(that / block_size)] int32; num_tokens_post_pad [1] int32; cumsum_buffer [num_experts+1]
  * int32 (receives the padded exclusive prefix, as in the reference before its scatter).
- * workspace: device scratch of at least sglb200_moe_align_workspace_bytes(numel, num_experts) bytes, 16-byte
- * aligned; may be NULL when that function returns 0.  Contents need no initialisation.
+ * workspace: device scratch of at least sglb200_moe_align_workspace_bytes(numel, num_experts) bytes, 4-byte
+ * aligned (only 32-bit words are accessed); may be NULL when that function returns 0.  Contents need no
+ * initialisation.
  * Entries of sorted_token_ids / expert_ids past num_tokens_post_pad are left untouched.
  */
 int64_t sglb200_moe_align_workspace_bytes(int64_t numel, int num_experts);
@@ -269,6 +270,17 @@ int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s, const void
  * sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:164-171.
  */
 int sglb200_gemm_status(void);
+/* Sets the status word back to 0 on the current device (after the failure has been handled).  Synchronises. */
+int sglb200_gemm_status_clear(void);
+
+/*
+ * Number of barrier probes (a few microseconds each) after which a pipeline wait inside the GEMM kernels gives
+ * up; 0 restores the default (about 4 million: seconds); UINT32_MAX makes every wait give up at once.  Applies to
+ * GEMMs launched afterwards by this process.  A diagnostic knob: with UINT32_MAX a healthy GEMM gives up before it
+ * has loaded anything, which exercises the give-up path (status word, drain, tensor-memory release) without any
+ * fault.  No counterpart in the reference.
+ */
+void sglb200_gemm_set_wait_probes(uint32_t probes);
 
 /*
  * Health of the streaming kernels (the quantizer and the fused silu_and_mul + quantizer stage their input
@@ -278,6 +290,15 @@ int sglb200_gemm_status(void);
  * (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-217) would surface at the next synchronisation.
  */
 int sglb200_stream_status(void);
+int sglb200_stream_status_clear(void); /* back to 0 on the current device; synchronises */
+
+/*
+ * Number of barrier probes (a few microseconds each) after which a streaming kernel gives up waiting for a staged
+ * tile; 0 restores the default (seconds); UINT32_MAX makes every wait give up at once.  A diagnostic knob like
+ * sglb200_gemm_set_wait_probes: with UINT32_MAX a healthy call gives up before its first tile has landed, sets the
+ * status word and returns after its copies in flight have landed.  No counterpart in the reference.
+ */
+void sglb200_stream_set_wait_probes(uint32_t probes);
 
 /*
  * Fused row-parallel all-reduce (tensor-parallel o_proj / down): the sum over ranks of a row-parallel layer as a
@@ -303,13 +324,17 @@ int sglb200_stream_status(void);
  *   finished, sums the `world` blocks of this rank's staging buffer in rank order in float32 into
  *   reduced_ptrs[rank] ([rpo][N]) and `out`, waits for the other ranks, then copies their reduced rows from
  *   reduced_ptrs[peer] into `out` [M][N] (private memory of this rank).  flag_ptrs[d] = rank d's flag buffer.
- *   `epoch` must be non-zero, the same on every rank for one call and different from the previous call's
- *   (a counter).  Every rank must make the same sequence of calls.  sglb200_comm_status() is 1 after a wait
- *   for a peer expired (the kernel then returns without touching peer data; the output is incomplete).
+ *   The call's epoch (the value the flag words are compared with) is counted on the device, per block, in this
+ *   rank's own flag buffer, so a CUDA graph that replays the call sees a new epoch at every replay.  Every rank must
+ *   make the same sequence of calls (with the same `max_blocks`).  sglb200_comm_status() is 1 after a wait
+ *   for a peer expired (the kernel then returns without touching peer data; the output is incomplete; the next
+ *   well-formed call works again).
  *   Pipelining over row chunks: `sm_margin` SMs are left free by the push GEMM and `max_blocks` (> 0; the same on
  *   every rank) caps the CTAs of sglb200_reduce_gather, so that the reduce-and-gather of chunk c (issued on a second
- *   stream, on its own slices of the buffers) runs beside the GEMM of chunk c + 1.  0 / 0 = no pipelining.  sglb200_comm_status() is 1 after a wait
- *   for a peer expired (the kernel then returns without touching peer data; the output is incomplete).
+ *   stream, on its own slices of the buffers) runs beside the GEMM of chunk c + 1.  0 / 0 = no pipelining.
+ * sglb200_comm_set_wait_probes: probes (about 0.25 us each) after which a wait for a peer's flag gives up; 0 restores
+ *   the default (about a second).  A diagnostic knob: with a small limit and a peer that never arrives the kernel
+ *   returns within milliseconds with the status word set.
  */
 int sglb200_comm_alloc(int64_t bytes, void** out);
 int sglb200_comm_free(void* p);
@@ -318,14 +343,19 @@ int sglb200_comm_ipc_open(const void* handle64, void** out);
 int sglb200_comm_ipc_close(void* p);
 int64_t sglb200_comm_flag_bytes(void);
 int sglb200_comm_status(void);
+int sglb200_comm_status_clear(void); /* back to 0 on the current device; synchronises */
+void sglb200_comm_set_wait_probes(uint32_t probes);
 int64_t sglb200_push_rows_per_owner(int64_t M, int world);
+/* Builds (and keeps) the device table of tensor maps that sglb200_fp8_blockwise_scaled_mm_push needs for outputs of
+ * M x N through these staging buffers: the small allocation and synchronous copy of a shape's first push call, done
+ * at set-up time instead.  No counterpart in the reference. */
+int sglb200_push_prepare(void* const* stage_ptrs, int world, int64_t M, int64_t N, int out_dtype);
 int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B, const float* a_s, const float* b_s,
                                          void* const* stage_ptrs, int world, int rank, int64_t M, int64_t N, int64_t K,
                                          int64_t as_stride_m, int64_t as_stride_k, int out_dtype, int sm_margin,
                                          void* stream);
 int sglb200_reduce_gather(const void* stage, void* const* reduced_ptrs, void* const* flag_ptrs, void* out, int world,
-                          int rank, int64_t M, int64_t N, int dtype, uint32_t epoch, int max_blocks,
-                          void* stream);
+                          int rank, int64_t M, int64_t N, int dtype, int max_blocks, void* stream);
 
 #ifdef __cplusplus
 }

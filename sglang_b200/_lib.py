@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libsglang_b200.so")
+# SGLANG_B200_LIB names another build of the same C ABI (a library compiled with different tuning constants)
+LIB_PATH = os.environ.get("SGLANG_B200_LIB") or os.path.join(_PKG, "lib", "libsglang_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -45,7 +46,12 @@ SIGNATURES = {
     "sglb200_fp8_blockwise_scaled_mm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp]),
     "sglb200_fp8_blockwise_grouped_mm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i32, _i32, _vp]),
     "sglb200_gemm_status": (_i32, []),
+    "sglb200_gemm_status_clear": (_i32, []),
+    "sglb200_stream_status_clear": (_i32, []),
+    "sglb200_comm_status_clear": (_i32, []),
+    "sglb200_gemm_set_wait_probes": (None, [C.c_uint32]),
     "sglb200_stream_status": (_i32, []),
+    "sglb200_stream_set_wait_probes": (None, [C.c_uint32]),
     "sglb200_comm_alloc": (_i32, [_i64, C.POINTER(_vp)]),
     "sglb200_comm_free": (_i32, [_vp]),
     "sglb200_comm_ipc_export": (_i32, [_vp, _vp]),
@@ -55,7 +61,9 @@ SIGNATURES = {
     "sglb200_comm_status": (_i32, []),
     "sglb200_push_rows_per_owner": (_i64, [_i64, _i32]),
     "sglb200_fp8_blockwise_scaled_mm_push": (_i32, [_vp, _vp, _vp, _vp, C.POINTER(_vp), _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
-    "sglb200_reduce_gather": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp), _vp, _i32, _i32, _i64, _i64, _i32, C.c_uint32, _i32, _vp]),
+    "sglb200_push_prepare": (_i32, [C.POINTER(_vp), _i32, _i64, _i64, _i32]),
+    "sglb200_reduce_gather": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp), _vp, _i32, _i32, _i64, _i64, _i32, _i32, _vp]),
+    "sglb200_comm_set_wait_probes": (None, [C.c_uint32]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -31,7 +31,7 @@ extern "C" {
 
 const char* sglb200_last_error(void) { return sglb200::g_err; }
 
-int sglb200_abi_version(void) { return 1; }
+int sglb200_abi_version(void) { return 2; }
 
 int sglb200_check_device(int device) {
   int major = 0;

@@ -21,14 +21,16 @@ namespace sglb200 {
 constexpr int kCommThreads = 512;
 constexpr int kCommMaxBlocks = 148;
 constexpr int kCommMaxWorld = 8;
-constexpr unsigned kCommSpinLimit = 1u << 22;  // probes of about 0.25 us each: around a second
+constexpr unsigned kCommSpinLimit = 1u << 22;  // default probes of about 0.25 us each: around a second
 
 __device__ int g_comm_status = 0;  // 0 ok, 1 = a wait for a peer's flag expired
 
 struct CommPeers {
   const uint16_t* stage;               // this rank's staging buffer [world][rows_own][N]
   uint16_t* reduced[kCommMaxWorld];    // every rank's buffer of reduced rows [rows_own][N]
-  uint32_t* flags[kCommMaxWorld];      // every rank's flag words [2][kCommMaxBlocks][kCommMaxWorld]
+  uint32_t* flags[kCommMaxWorld];      // every rank's flag words [2][kCommMaxBlocks][kCommMaxWorld], then this
+                                       // rank's own call counters [kCommMaxBlocks]
+  unsigned spin_limit;                 // probes after which a wait for a peer gives up
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -38,6 +40,22 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+
+// The epoch of a call lives on the device: block b of a rank counts its own calls in a word of the rank's flag
+// buffer that only it touches.  Every rank launches the same sequence of calls with the same grid, so block b
+// of every rank reads the same number, and a CUDA graph that replays a call gets a fresh epoch on every replay
+// (a host-side counter would be frozen into the graph).  0 is the cleared state of the flags and is skipped.
+__device__ __forceinline__ uint32_t next_epoch(const CommPeers& c, int rank, uint32_t* s_epoch) {
+  if (threadIdx.x == 0) {
+    uint32_t* counter = c.flags[rank] + (size_t)2 * kCommMaxBlocks * kCommMaxWorld + blockIdx.x;
+    uint32_t e = *counter + 1u;
+    if (e == 0u) e = 1u;
+    *counter = e;
+    *s_epoch = e;
+  }
+  __syncthreads();
+  return *s_epoch;
 }
 
 // Block-level barrier across the ranks: block b of every rank tells block b of every other rank that it has
@@ -54,7 +72,7 @@ __device__ __forceinline__ bool cross_rank_barrier(const CommPeers& c, int world
     const uint32_t* mine = c.flags[rank] + slot + peer;
     unsigned n = 0;
     while (ld_acquire_sys(mine) != epoch) {
-      if (++n > kCommSpinLimit) {
+      if (++n > c.spin_limit) {
         *s_ok = 0;
         break;
       }
@@ -87,10 +105,11 @@ __device__ __forceinline__ void add_packed(float (&acc)[8], const uint4& v) {
 template <bool kFp16>
 __global__ void __launch_bounds__(kCommThreads)
     reduce_gather_kernel(CommPeers c, uint16_t* __restrict__ out, int64_t chunks, int64_t total_chunks, int world,
-                         int rank, uint32_t epoch) {
+                         int rank) {
   __shared__ int s_ok;
+  __shared__ uint32_t s_epoch;
   if (threadIdx.x == 0) s_ok = 1;
-  // (cross_rank_barrier starts with a __syncthreads)
+  const uint32_t epoch = next_epoch(c, rank, &s_epoch);
   if (!cross_rank_barrier(c, world, rank, 0, epoch, &s_ok)) {
     if (threadIdx.x == 0) atomicExch(&g_comm_status, 1);
     return;
@@ -195,7 +214,16 @@ extern "C" int sglb200_comm_ipc_close(void* p) {
 }
 
 extern "C" int64_t sglb200_comm_flag_bytes(void) {
-  return (int64_t)2 * kCommMaxBlocks * kCommMaxWorld * (int64_t)sizeof(uint32_t);
+  return ((int64_t)2 * kCommMaxBlocks * kCommMaxWorld + kCommMaxBlocks) * (int64_t)sizeof(uint32_t);
+}
+
+static unsigned g_comm_spin_limit = kCommSpinLimit;
+extern "C" void sglb200_comm_set_wait_probes(uint32_t probes) { g_comm_spin_limit = probes == 0 ? kCommSpinLimit : probes; }
+
+extern "C" int sglb200_comm_status_clear(void) {
+  const int zero = 0;
+  SGLB_CUDA(cudaMemcpyToSymbol(g_comm_status, &zero, sizeof(int)));
+  return SGLB200_OK;
 }
 
 extern "C" int sglb200_comm_status(void) {
@@ -205,18 +233,18 @@ extern "C" int sglb200_comm_status(void) {
 }
 
 extern "C" int sglb200_reduce_gather(const void* stage, void* const* reduced_ptrs, void* const* flag_ptrs, void* out,
-                                     int world, int rank, int64_t M, int64_t N, int dtype, uint32_t epoch,
-                                     int max_blocks, void* stream) {
+                                     int world, int rank, int64_t M, int64_t N, int dtype, int max_blocks,
+                                     void* stream) {
   SGLB_REQUIRE(world >= 2 && world <= kCommMaxWorld && rank >= 0 && rank < world, "reduce_gather: world %d, rank %d",
                world, rank);
   SGLB_REQUIRE(M > 0 && N > 0 && N % 8 == 0, "reduce_gather: rows %lld, N %lld (N must be a multiple of 8)",
                (long long)M, (long long)N);
   const int64_t rows_own = sglb200_push_rows_per_owner(M, world);
   SGLB_REQUIRE(dtype == 0 || dtype == 1, "reduce_gather: dtype %d (0 bf16, 1 fp16)", dtype);
-  SGLB_REQUIRE(epoch != 0, "reduce_gather: epoch 0 is the cleared state of the flags");
   SGLB_REQUIRE(stage && reduced_ptrs && flag_ptrs && out && aligned16(stage) && aligned16(out),
                "reduce_gather: null or unaligned pointer");
   CommPeers c{};
+  c.spin_limit = g_comm_spin_limit;
   c.stage = static_cast<const uint16_t*>(stage);
   for (int i = 0; i < world; ++i) {
     SGLB_REQUIRE(reduced_ptrs[i] && flag_ptrs[i] && aligned16(reduced_ptrs[i]), "reduce_gather: peer %d buffers", i);
@@ -232,10 +260,10 @@ extern "C" int sglb200_reduce_gather(const void* stage, void* const* reduced_ptr
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
     reduce_gather_kernel<false><<<(unsigned)blocks, kCommThreads, 0, st>>>(c, static_cast<uint16_t*>(out), chunks,
-                                                                           total_chunks, world, rank, epoch);
+                                                                           total_chunks, world, rank);
   else
     reduce_gather_kernel<true><<<(unsigned)blocks, kCommThreads, 0, st>>>(c, static_cast<uint16_t*>(out), chunks,
-                                                                          total_chunks, world, rank, epoch);
+                                                                          total_chunks, world, rank);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }

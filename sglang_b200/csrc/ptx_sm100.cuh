@@ -32,23 +32,31 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-// Bounded wait (about one second of SM clocks).  `abort_flag` (shared memory) is raised by whichever
-// thread gives up first so that every other waiter leaves promptly; returns false when the wait was
-// abandoned.
-
-// Bounded wait as one asm block: each probe may suspend the thread for up to `kProbeHintNs` (it resumes at
-// once when the phase completes), so a waiting warp spends a couple of instructions per microsecond instead of
-// competing for issue slots with the warps that have work.  Gives up after kProbeLimit probes (tens of
-// milliseconds at the very least, seconds if every probe suspends) and returns false.
-constexpr uint32_t kProbeHintNs = 4000;
-constexpr uint32_t kProbeLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity) {
+// Bounded waits.  Each probe (mbarrier.try_wait with a time hint) may suspend the thread for up to `kProbeHintNs`
+// and resumes at once when the phase completes, so a waiting warp spends a couple of instructions per microsecond
+// instead of competing for issue slots with the warps that have work.
+#ifndef SGLB_PROBE_HINT_NS
+#define SGLB_PROBE_HINT_NS 4000
+#endif
+constexpr uint32_t kProbeHintNs = SGLB_PROBE_HINT_NS;
+constexpr uint32_t kProbeLimit = 1u << 22;  // default number of probes after which a wait gives up (seconds)
+constexpr uint32_t kProbesFast = 8, kProbesSlow = 64;
+constexpr uint32_t kProbesNone = 0xffffffffu;  // as a limit: give up without probing (exercises the give-up paths)
+// Up to `limit` probes in one asm block; true when the phase completed.
+__device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity, uint32_t limit) {
+  if (limit == kProbesNone) return false;
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
       "mov.u32 n, 0;\n"
       "QUIET_LOOP:\n\t"
+#if defined(SGLB_PROBE_POLL)
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#elif SGLB_PROBE_HINT_NS > 0
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+#else
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "@p bra QUIET_DONE;\n\t"
       "add.u32 n, n, 1;\n\t"
       "setp.lt.u32 p, n, %4;\n\t"
@@ -57,9 +65,23 @@ __device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity) {
       "QUIET_DONE:\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kProbeHintNs), "r"(kProbeLimit)
+      : "r"(bar), "r"(parity), "r"(kProbeHintNs), "r"(limit)
       : "memory");
   return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity) { return mbar_probe(bar, parity, kProbeLimit); }
+// The wait of the GEMM's pipeline roles: a short run of probes (all that an undisturbed pipeline ever needs), then
+// longer runs between which the CTA's abort flag is polled, so that when one role gives up the others leave
+// promptly instead of sitting out their own limits.  Returns false when the wait was abandoned.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint32_t limit) {
+  if (limit == kProbesNone) return false;
+  if (mbar_probe(bar, parity, kProbesFast)) return true;
+  for (uint32_t n = kProbesFast; n < limit; n += kProbesSlow) {
+    if (*abort_flag != 0) return false;
+    if (mbar_probe(bar, parity, kProbesSlow)) return true;
+  }
+  return false;
 }
 // Arrive from the threads whose `pred` is set, without a branch around the instruction.
 __device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
@@ -74,6 +96,15 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
   return v;
+}
+
+__device__ __forceinline__ float4 lds_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 // Two 32-bit words as one 64-bit register (shared-memory matrix descriptors are built from halves).
@@ -116,6 +147,10 @@ __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.b
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Orders this thread's ordinary shared-memory writes before later reads by the TMA engine.
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Named barrier over `threads` threads (a multiple of 32; every participating warp arrives whole).
+__device__ __forceinline__ void bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 __device__ __forceinline__ void sts_128(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -147,6 +182,72 @@ __device__ __forceinline__ void mma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, uin
 // The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+
+// ---- CTA pairs (a cluster of two CTAs that share one tcgen05.mma.cta_group::2) ---------------------------
+// Each CTA fetches its own tiles; nothing here uses a cluster-wide (multicast) load.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of both CTAs (the hardware barrier of the cluster; every thread reaches it unconditionally).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// Arrive on an mbarrier of a CTA of the cluster (address from mapa) from the threads whose `pred` is set.
+__device__ __forceinline__ void mbar_arrive_cluster_if(uint32_t bar_cluster, uint32_t pred) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "@p mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n\t}" ::"r"(bar_cluster),
+      "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr_cluster, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr_cluster), "r"(v) : "memory");
+}
+// TMA tile loads of a CTA pair: the data lands in THIS CTA's shared memory, the bytes are counted on the mbarrier
+// `bar_cluster` of the pair's leader (shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int c0, int c1,
+                                                 int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// D[tmem of both CTAs] (+)= A[each CTA's own rows] * B[half of the columns from each CTA], issued by ONE thread of
+// the leader CTA; M = 256 over the pair.
+__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the mbarrier at this offset in BOTH CTAs of the pair when every tcgen05.mma issued so far by this
+// thread has finished (a signal, not a load).
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
+               : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base_lane + i).

@@ -31,6 +31,19 @@ template <typename T>
 constexpr int kStagesOf = sizeof(T) == 4 ? 3 : 4;  // 64 KB (16-bit types) or 96 KB (float32) of ring per CTA
 
 __device__ int g_stream_status = 0;  // 0 ok, 1 = a wait for a staged tile expired
+static uint32_t g_stream_wait_probes = ptx::kProbeLimit;  // sglb200_stream_set_wait_probes
+
+// A CTA that gave up a wait: it records the failure and then holds its shared memory for about a millisecond, so
+// that bulk copies it has already issued into other ring slots land before the SM hands the memory to another CTA.
+__device__ __forceinline__ void stream_give_up(int tid) {
+  if (tid == 0) {
+    atomicExch(&g_stream_status, 1);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  __syncthreads();
+}
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -213,7 +226,7 @@ template <typename T, int LPG, bool kStdRange>
 __global__ void __launch_bounds__(kStreamThreads, 3)
     quant_stream_kernel(const T* __restrict__ x, uint8_t* __restrict__ out_q, float* __restrict__ out_s,
                         int64_t total_elems, int groups_per_row, int64_t s_stride_token, int64_t s_stride_group,
-                        bool s_contiguous, float eps, float qmin, float qmax) {
+                        bool s_contiguous, float eps, float qmin, float qmax, uint32_t probes) {
   constexpr int CE = Chunk<T>::kElems, NCH = Chunk<T>::kPerThread, GC = LPG * NCH;
   constexpr int G = LPG * kThreadElems;
   constexpr int kStreamStages = kStagesOf<T>;
@@ -254,14 +267,14 @@ __global__ void __launch_bounds__(kStreamThreads, 3)
   for (int64_t i = 0; i < my_tiles; ++i) {
     const int slot = (int)(i % kStreamStages);
     const uint32_t parity = (uint32_t)((i / kStreamStages) & 1);
-    if (!ptx::mbar_wait_quiet(ptx::smem_u32(&bars[slot]), parity)) s_abort = 1;
+    if (!ptx::mbar_probe(ptx::smem_u32(&bars[slot]), parity, probes)) s_abort = 1;
     uint4 raw[NCH];
     const uint32_t src = smem_base + slot * kTileBytes + (uint32_t)(g_local * GC) * 16u;
 #pragma unroll
     for (int j = 0; j < NCH; ++j) raw[j] = lds_128(src + (uint32_t)cj[j] * 16u);
     __syncthreads();  // every thread holds its part of the slot in registers: the slot can be refilled
-    if (s_abort) {
-      if (tid == 0) atomicExch(&g_stream_status, 1);
+    if (s_abort) {  // (uniform: read after the barrier)
+      stream_give_up(tid);
       return;
     }
     if (tid == 0 && i + kStreamStages < my_tiles) issue(i + kStreamStages);
@@ -327,7 +340,7 @@ template <typename T, int LPG>
 __global__ void __launch_bounds__(kStreamThreads, 3)
     silu_mul_quant_stream_kernel(const T* __restrict__ x, uint8_t* __restrict__ out_q, float* __restrict__ out_s,
                                  int64_t rows, int d, const int32_t* __restrict__ num_rows_dev, float eps, float qmin,
-                                 float qmax) {
+                                 float qmax, uint32_t probes) {
   static_assert(sizeof(T) == 2, "16-bit inputs only");
   constexpr int CE = 8, NCH = 4, GC = LPG * NCH, G = LPG * kThreadElems;
   constexpr uint32_t kHalfBytes = kTileElems * 2;  // gate part of a stage; the up part follows it
@@ -384,7 +397,7 @@ __global__ void __launch_bounds__(kStreamThreads, 3)
   for (int64_t i = 0; i < my_tiles; ++i) {
     const int slot = (int)(i % kSiluStages);
     const uint32_t parity = (uint32_t)((i / kSiluStages) & 1);
-    if (!ptx::mbar_wait_quiet(ptx::smem_u32(&bars[slot]), parity)) s_abort = 1;
+    if (!ptx::mbar_probe(ptx::smem_u32(&bars[slot]), parity, probes)) s_abort = 1;
     uint4 graw[NCH], uraw[NCH];
     const uint32_t src = smem_base + slot * (2 * kHalfBytes) + (uint32_t)(g_local * GC) * 16u;
 #pragma unroll
@@ -393,8 +406,8 @@ __global__ void __launch_bounds__(kStreamThreads, 3)
       uraw[j] = lds_128(src + kHalfBytes + (uint32_t)cj[j] * 16u);
     }
     __syncthreads();  // the slot is in registers and can be refilled
-    if (s_abort) {
-      if (tid == 0) atomicExch(&g_stream_status, 1);
+    if (s_abort) {  // (uniform: read after the barrier)
+      stream_give_up(tid);
       return;
     }
     if (tid == 0 && i + kSiluStages < my_tiles) issue(i + kSiluStages);
@@ -439,7 +452,7 @@ static int launch_quant_inst(const void* input, void* output_q, float* output_s,
   const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
   kern<<<grid, kStreamThreads, smem, stream>>>(static_cast<const T*>(input), static_cast<uint8_t*>(output_q), output_s,
                                                total_elems, groups_per_row, s_stride_token, s_stride_group, contiguous,
-                                               eps, qmin, qmax);
+                                               eps, qmin, qmax, g_stream_wait_probes);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }
@@ -480,7 +493,7 @@ static int launch_silu_mul_quant_inst(const void* input, void* output_q, float* 
   const int64_t resident = (int64_t)sm_count() * 3;
   const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
   kern<<<grid, kStreamThreads, smem, stream>>>(static_cast<const T*>(input), static_cast<uint8_t*>(output_q), output_s,
-                                               rows, (int)d, num_rows_dev, eps, -448.0f, 448.0f);
+                                               rows, (int)d, num_rows_dev, eps, -448.0f, 448.0f, g_stream_wait_probes);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }
@@ -550,6 +563,16 @@ extern "C" int sglb200_silu_and_mul_quant_fp8(const void* input, int dtype, void
     default:
       return fail(SGLB200_E_UNSUPPORTED, "silu_mul_quant: dtype code %d (0 bf16, 1 fp16)", dtype);
   }
+}
+
+extern "C" void sglb200_stream_set_wait_probes(uint32_t probes) {
+  g_stream_wait_probes = probes == 0 ? ptx::kProbeLimit : probes;
+}
+
+extern "C" int sglb200_stream_status_clear(void) {
+  const int zero = 0;
+  SGLB_CUDA(cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int)));
+  return SGLB200_OK;
 }
 
 extern "C" int sglb200_stream_status(void) {

@@ -94,7 +94,13 @@ def _op_prepare_moe_input(topk_ids, expert_offsets, blockscale_offsets, problem_
     numel, topk = topk_ids.numel(), topk_ids.shape[1]
     order, _, _ = _ops.moe_align_block_size(topk_ids, 1, num_experts)
     order = order[:numel]
-    counts = torch.bincount(topk_ids.reshape(-1), minlength=num_experts)[:num_experts].to(torch.int32)
+    # rows per expert without a data-dependent shape (nothing synchronises, negative ids = filtered slots are
+    # counted in a bucket of their own and dropped)
+    counts = torch.zeros(num_experts + 1, dtype=torch.int32, device=topk_ids.device)
+    flat = topk_ids.reshape(-1)
+    bucket = torch.where((flat >= 0) & (flat < num_experts), flat + 1, torch.zeros_like(flat)).long()
+    counts.scatter_add_(0, bucket, torch.ones_like(flat))
+    counts = counts[1:]
     expert_offsets[0] = 0
     expert_offsets[1 : num_experts + 1] = torch.cumsum(counts, 0)
     if blockscale_offsets is not None:

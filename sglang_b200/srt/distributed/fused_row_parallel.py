@@ -66,7 +66,6 @@ class FusedRowParallelComm:
         self._stage_arr = arr(*self.stage_ptrs)
         self._reduced_arr = arr(*self.reduced_ptrs)
         self._flag_arr = arr(*self.flag_ptrs)
-        self.epoch = 0
         # Cutting large outputs into row chunks (see `_chunks`) is off: measured on 8 GPUs (8192 x 8192 outputs, K
         # per rank 1024 and 3584) the chunked form took 2.14 ms per layer against 1.73 ms unchunked, because 16 CTAs
         # do not keep NVLink busy and the chunked GEMMs lose SMs and waves; on 2 GPUs 4.87 against 4.65 ms.
@@ -128,19 +127,38 @@ class FusedRowParallelComm:
                 ev = torch.cuda.Event()
                 ev.record(main)
                 side.wait_event(ev)
-            self.epoch = self.epoch % 0x7FFFFFFF + 1  # never 0, never equal to the previous call's
             check(lib.sglb200_reduce_gather(
                 self._stage + stage_off, reduced, self._flag_arr, out.data_ptr() + c * Mc * N * 2, self.world,
-                self.rank, Mc, N, dt, self.epoch, self.sm_margin if c < C_ - 1 else 0,
-                side.cuda_stream))
+                self.rank, Mc, N, dt, self.sm_margin if c < C_ - 1 else 0, side.cuda_stream))
         if C_ > 1:
             done = torch.cuda.Event()
             done.record(side)
             main.wait_event(done)
         return out
 
+    def prepare(self, M: int, N: int, out_dtype: torch.dtype = torch.bfloat16) -> None:
+        """Builds the device table of per-owner tensor maps for outputs of `M` x `N` now (a small allocation and a
+        synchronous copy) instead of inside the first `linear` call of that shape, where it would delay this rank
+        against its peers.  Call it for the shapes the layer will serve, before the first forward pass."""
+        if self.supports(M, N):
+            check(lib.sglb200_push_prepare(self._stage_arr, self.world, M, N, 0 if out_dtype == torch.bfloat16 else 1))
+
+    def check_status(self) -> None:
+        """Raises if a wait for a peer (or a GEMM pipeline wait) has expired since the library was loaded: the outputs
+        of the affected calls are incomplete.  Synchronises the device."""
+        if lib.sglb200_comm_status() != 0:
+            raise RuntimeError("fused all-reduce: a wait for a peer's flag expired (a rank stalled for about a second); "
+                               "outputs of that call are incomplete")
+        if lib.sglb200_gemm_status() != 0:
+            raise RuntimeError("fused all-reduce: a GEMM pipeline wait expired; outputs of that call are incomplete")
+
     def close(self) -> None:
         torch.cuda.synchronize(self.device)
+        failed = None
+        try:
+            self.check_status()
+        except RuntimeError as e:  # release the buffers first, then report
+            failed = e
         dist.barrier(group=self.group)
         for ptrs in (self.stage_ptrs, self.reduced_ptrs, self.flag_ptrs):
             for r, p in enumerate(ptrs):
@@ -149,6 +167,8 @@ class FusedRowParallelComm:
         dist.barrier(group=self.group)
         for p in (self._stage, self._reduced, self._flags):
             check(lib.sglb200_comm_free(p))
+        if failed is not None:
+            raise failed
 
 
 def comm_status() -> int:

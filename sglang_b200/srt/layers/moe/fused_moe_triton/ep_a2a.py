@@ -33,9 +33,11 @@ def plan_dispatch(topk_ids: torch.Tensor, num_local_experts: int, group: GroupCo
     T, _ = topk_ids.shape
     p = group.world_size
     dest = torch.div(topk_ids.long(), num_local_experts, rounding_mode="floor")
-    valid = topk_ids >= 0
-    mask = torch.zeros((T, p), dtype=torch.bool, device=topk_ids.device)
-    mask.scatter_(1, dest.clamp(0, p - 1), valid)
+    valid = (topk_ids >= 0) & (dest < p)  # -1 (no expert) and ids past the last expert go nowhere
+    # a token goes to rank r if ANY of its valid slots names an expert of r (an OR over the slots: a row that
+    # mixes a filtered slot with a valid one must not depend on which write lands last)
+    ranks = torch.arange(p, device=topk_ids.device)
+    mask = ((dest.unsqueeze(-1) == ranks) & valid.unsqueeze(-1)).any(dim=1)
     pairs = torch.nonzero(mask.t())            # rows sorted by (rank, token)
     send_token = pairs[:, 1].contiguous()
     counts = mask.sum(0).to(torch.int64)
@@ -43,10 +45,22 @@ def plan_dispatch(topk_ids: torch.Tensor, num_local_experts: int, group: GroupCo
     group.all_to_all_single(recv_counts, counts, [1] * p, [1] * p)
     both = torch.stack([counts, recv_counts]).cpu()
     send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+    _check_kernel_status(topk_ids)  # the device has just been synchronised: a cheap place to notice a failed kernel
     S = int(send_token.numel())
     slot = torch.full((T, p), S, dtype=torch.int64, device=topk_ids.device)
     slot[pairs[:, 1], pairs[:, 0]] = torch.arange(S, device=topk_ids.device)
     return EPDispatchPlan(send_token, send_splits, recv_splits, slot)
+
+
+def _check_kernel_status(t: torch.Tensor) -> None:
+    """Raises if a bounded wait inside one of this library's kernels has expired (their outputs are then
+    incomplete).  Called where the host has synchronised with the device anyway."""
+    if not t.is_cuda:
+        return
+    from ..... import ops as _ops
+
+    if _ops.gemm_status() != 0 or _ops.stream_status() != 0:
+        raise RuntimeError("a pipeline wait inside a block-FP8 kernel expired: outputs of earlier calls are incomplete")
 
 
 def pack_rows(xq: torch.Tensor, xs: torch.Tensor, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

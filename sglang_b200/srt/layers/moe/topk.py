@@ -2,9 +2,9 @@
 
 After python/sglang/srt/layers/moe/topk.py: `fused_topk` (:459-489, `topk_softmax` kernel),
 `fused_topk_torch_native` (:427-456) and `biased_grouped_topk_gpu` / `biased_grouped_topk_impl`
-(:741-850, :665-738; `moe_fused_gate` kernel).  CUDA tensors go through this library's routing kernels;
-the torch expressions below them are the reference's native forms, kept for CPU tensors (host-side tests of
-the expert-parallel logic run on CPU ranks).
+(:741-850, :665-738; `moe_fused_gate` kernel).  Inputs are CUDA tensors and go through this library's routing
+kernels; there is no CPU form.  The one torch expression left is the reference's own native form of the grouped
+routing WITHOUT renormalisation, which its fused kernel does not cover either (:741-850 falls back to it).
 """
 from __future__ import annotations
 
@@ -13,20 +13,20 @@ from typing import Optional, Tuple
 import torch
 
 
-def fused_topk(gating_output: torch.Tensor, topk: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
-    if gating_output.is_cuda:
-        from .... import ops
+def _need_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: gating_output must be a CUDA tensor (this path has no CPU implementation)")
 
-        g = gating_output.contiguous()
-        w = torch.empty(g.shape[0], topk, dtype=torch.float32, device=g.device)
-        ids = torch.empty(g.shape[0], topk, dtype=torch.int32, device=g.device)
-        ops.topk_softmax_out(w, ids, g, renormalize)
-        return w, ids
-    scores = torch.softmax(gating_output.float(), dim=-1)
-    w, ids = torch.topk(scores, topk, dim=-1)
-    if renormalize:
-        w = w / w.sum(dim=-1, keepdim=True)
-    return w.float(), ids.to(torch.int32)
+
+def fused_topk(gating_output: torch.Tensor, topk: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    from .... import ops
+
+    _need_cuda(gating_output, "fused_topk")
+    g = gating_output.contiguous()
+    w = torch.empty(g.shape[0], topk, dtype=torch.float32, device=g.device)
+    ids = torch.empty(g.shape[0], topk, dtype=torch.int32, device=g.device)
+    ops.topk_softmax_out(w, ids, g, renormalize)
+    return w, ids
 
 
 def biased_grouped_topk(
@@ -34,7 +34,8 @@ def biased_grouped_topk(
     num_expert_group: int, topk_group: int, routed_scaling_factor: Optional[float] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """`routed_scaling_factor` not None = scale the weights by it (apply_routed_scaling_factor_on_output)."""
-    if gating_output.is_cuda and renormalize:
+    _need_cuda(gating_output, "biased_grouped_topk")
+    if renormalize:
         from .... import ops
 
         g = gating_output.contiguous()

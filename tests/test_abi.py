@@ -27,7 +27,7 @@ def test_header_symbols_exported():
 
 def test_abi_version_and_error_channel():
     from sglang_b200._lib import check, lib
-    assert lib.sglb200_abi_version() == 1
+    assert lib.sglb200_abi_version() == 2
     # a rejected call launches nothing and reports through the message channel (no GPU needed)
     rc = lib.sglb200_per_token_group_quant_fp8(None, 0, None, None, 4, 100, 128, 1e-10, -448.0, 448.0, 1, 1, None)
     assert rc == -1

@@ -38,8 +38,11 @@ def _inputs(M, N, K, seed):
     return xq, xs, wq, ws.contiguous()
 
 
+# (from 512 rows on and beyond 12 K slabs, pairs of CTAs share 256-row tiles: 700 rows leave the last pair's second
+# CTA a partial block of rows, 520 rows leave it none)
 @pytest.mark.parametrize("M,N,K", [(4096, 7168, 2048), (2048, 4608, 7168), (513, 1536, 1536), (130, 24576, 1536),
-                                   (1024, 7168, 18432), (4, 512, 512), (128, 256, 128)])
+                                   (1024, 7168, 18432), (4, 512, 512), (128, 256, 128), (700, 1536, 2048),
+                                   (520, 768, 2048), (8192, 1280, 3584)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
 def test_bitwise_equal_to_reference_kernel(ref_mm, M, N, K, out_dtype):
     from sglang_b200 import ops
