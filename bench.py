@@ -558,6 +558,10 @@ def main():
     ap.add_argument("--cpu-baseline", type=int, default=1)
     ap.add_argument("--layers", default="", help="comma-separated subset of layer names (profiler captures only)")
     ap.add_argument("--m-tokens", type=int, default=M_TOKENS, help="smaller values are for profiler captures only")
+    ap.add_argument("--moe-experts", type=int, default=0, help="config-3 MoE section with this many experts "
+                                                                "(profiler captures only; 0 = the 256 of the config)")
+    ap.add_argument("--moe-tokens", type=int, default=0, help="config-3 MoE section at this one token count "
+                                                               "(profiler captures only; 0 = the sizes of the config)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

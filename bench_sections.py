@@ -122,6 +122,42 @@ def gemm_sweep(args, ctx, peaks):
                            "fp8_peak_source": "the same denominator as roofline.peak of this line"}}
 
 
+def config0_gpu(args, ctx, peaks):
+    """BASELINE config 0 on the GPU: one block-FP8 linear, M = 64, N = K = 4096 (quantizer + GEMM, graph-replayed,
+    weight copies rotated past L2); the CPU arm's time for the same shape is `config0_cpu` / the reference arm's
+    `config0`."""
+    from bench import make_block_fp8_weight
+    from sglang_b200 import ops
+    rank, world, dev = ctx
+    gen = torch.Generator(device=dev).manual_seed(0)
+    M, N, K = 64, 4096, 4096
+    wq, ws = make_block_fp8_weight(N, K, dev, gen)
+    copies = -(-2 * L2_BYTES // (N * K))
+    wqs = [wq] + [wq.clone() for _ in range(copies - 1)]
+    x = torch.randn(M, K, device=dev, generator=gen).bfloat16()
+    state = {"i": 0}
+
+    def run():
+        w = wqs[state["i"] % copies]
+        state["i"] += 1
+        xq, xs = ops.per_token_group_quant_fp8(x, 128)
+        ops.w8a8_block_fp8_matmul(xq, w, xs, ws, [128, 128], torch.bfloat16)
+
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(20):
+            run()
+    ms = _time(graph.replay, 3, 1, world, dev) / 20
+    del graph
+    nbytes = N * K + M * K * 3 + 2 * M * N
+    return {"config0": {"workload": "BASELINE config 0: M=64, N=K=4096 block-FP8 linear (quantizer + GEMM)",
+                        "us": ms * 1e3, "tflops": 2.0 * M * N * K / ms / 1e9, "gbs": nbytes / ms / 1e6,
+                        "frac_of_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}}
+
+
 # ------------------------------------------------------------------------------------------------
 # config 2: Llama-3-70B-shaped layer, tensor parallel
 # ------------------------------------------------------------------------------------------------
@@ -232,13 +268,17 @@ def moe_layer(args, ctx, peaks):
     from sglang_b200.srt.layers.linear import ColumnParallelLinear
     from sglang_b200.srt.layers.moe.fused_moe_triton.layer import FusedMoE
     from sglang_b200.srt.layers.moe.token_dispatcher import StandardTopKOutput
-    from sglang_b200.srt.layers.moe.topk import biased_grouped_topk
+    from sglang_b200.srt.layers.moe.topk import biased_grouped_topk, fused_topk
     from sglang_b200.srt.layers.quantization.fp8 import Fp8Config
     rank, world, dev = ctx
     parity = ep_parity(ctx) if world > 1 else None
     cfg = Fp8Config()
     E, H, I, topk = 256, 7168, 2048, 8
     sizes = (1, 64, 512, 4096)
+    reduced = bool(getattr(args, "moe_experts", 0) or getattr(args, "moe_tokens", 0))
+    if reduced:  # a reduced case for profiler captures (a few GB on the device, one size)
+        E = args.moe_experts or E
+        sizes = (args.moe_tokens,) if args.moe_tokens else sizes
     res = {str(T): {} for T in sizes}
 
     def build(ep):
@@ -257,7 +297,8 @@ def moe_layer(args, ctx, peaks):
         def layer_for(T):
             x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
             logits = torch.randn(T, E, device=dev, generator=gen)
-            w, ids = biased_grouped_topk(logits, None, topk, True, 8, 4)
+            w, ids = biased_grouped_topk(logits, None, topk, True, 8, min(4, max(1, E // 8 // 2))) if E % 8 == 0 and E >= 64 \
+                else fused_topk(logits, topk, True)
             top = StandardTopKOutput(w, ids, None)
 
             def layer():
@@ -295,6 +336,8 @@ def moe_layer(args, ctx, peaks):
                      "most 2048 tokens over all ranks: all-gather, local experts, reduce-scatter); ms_1gpu_eager = "
                      "the layer with all experts on one GPU of this box in this run",
            "ep": world, "scaling": "weak", "results": res}
+    if reduced:
+        out["reduced_case"] = {"experts": E, "tokens": list(sizes)}
     if parity is not None:
         out["parity"] = parity
     return {"moe_layer": out}
@@ -597,6 +640,7 @@ def run(sections, args, ctx, peaks):
     out = {}
     rank, world, dev = ctx
     if "sweep" in sections and world == 1:
+        out.update(config0_gpu(args, ctx, peaks))
         out.update(gemm_sweep(args, ctx, peaks))
         torch.cuda.empty_cache()
     if "hbm" in sections and world == 1:
@@ -608,8 +652,9 @@ def run(sections, args, ctx, peaks):
     if "moe" in sections:
         out.update(moe_layer(args, ctx, peaks))
         torch.cuda.empty_cache()
-        out.update(moe_layer_skewed(args, ctx, peaks))
-        torch.cuda.empty_cache()
+        if not (getattr(args, "moe_experts", 0) or getattr(args, "moe_tokens", 0)):  # (not in a profiler's reduced case)
+            out.update(moe_layer_skewed(args, ctx, peaks))
+            torch.cuda.empty_cache()
     if "tp" in sections or "moe" in sections:
         out["sharded"] = sharded_summary(out, world)  # last key of the JSON line
     return out

@@ -52,15 +52,21 @@ constexpr int BM = 128, BK = 128;
 constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarp0 = 4;              // warp 0 TMA, warp 1 MMA + TMEM owner, warps 4.. promotion + epilogue
-constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = kEpiWarp0 * 32 + kEpiWarps * 32;
+#ifndef SGLB_EPI_WARPS_128
+#define SGLB_EPI_WARPS_128 8              // promotion warps of the 128-wide tile (8 or 16); the 192-wide tile has 8
+#endif
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 constexpr int kBChunk = 64;                // slabs of weight-block scales a promotion warp stages at a time
 #ifndef SGLB_LOOKAHEAD_ALL
 #define SGLB_LOOKAHEAD_ALL 0
 #endif
+#ifndef SGLB_FMA2
+#define SGLB_FMA2 1                        // promotion with packed float32 FMAs (two columns per instruction)
+#endif
 #ifndef SGLB_SHORT_K
-#define SGLB_SHORT_K 12                    // problems with at most this many K slabs use the 128-wide tile
+#define SGLB_SHORT_K 1000000               // problems with at most this many K slabs use the 128-wide tile (all of
+                                           // them: measured equal to the 192-wide tile at M >= 1024 and 10-30 % ahead
+                                           // of it below, dense and grouped; the 192-wide tile stays selectable)
 #endif
 
 // kPair: two CTAs (a cluster of two SMs) share 256 x BN tiles through tcgen05.mma.cta_group::2; each stages its own
@@ -75,7 +81,10 @@ struct TileCfg {
   static constexpr int kStages = kPair_ ? (BN_ >= 192 ? 6 : 7) : (BN_ >= 192 ? 4 : 5);
   static constexpr int kAccBufs = kTmemCols / BN_;   // TMEM accumulator buffers in flight
   static constexpr int kAccStride = BN_;             // TMEM columns between buffers
-  static constexpr int kEpiCols = BN_ / 2;           // columns of a buffer owned by one promotion warp
+  static constexpr int kEpiWarps = BN_ == 128 ? SGLB_EPI_WARPS_128 : 8;  // promotion + epilogue warps
+  static constexpr int kColGroups = kEpiWarps / 4;   // promotion warps per TMEM lane quadrant
+  static constexpr int kThreads = kEpiWarp0 * 32 + kEpiWarps * 32;
+  static constexpr int kEpiCols = BN_ / kColGroups;  // columns of a buffer owned by one promotion warp
   static constexpr int kPieces = kEpiCols / 32;      // 32-column pieces per warp
   static constexpr uint32_t kTileBytesB = kBRows * BK;
   static constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
@@ -84,12 +93,26 @@ struct TileCfg {
   static constexpr int kOutGroups = BN_ / 64;
   static constexpr uint32_t kGroupBytes = 32 * 64 * 2;
   static constexpr uint32_t kOutBytes = 4 * kOutGroups * kGroupBytes;
-  static_assert(kEpiCols % 32 == 0 && BN_ % 64 == 0 && (4 % kAccBufs) == 0 && kAccBufs * kAccStride <= kTmemCols && BN_ <= 256 &&
+  static_assert(kEpiWarps % 4 == 0 && kEpiCols % 32 == 0 && BN_ % 64 == 0 && (4 % kAccBufs) == 0 && kAccBufs * kAccStride <= kTmemCols && BN_ <= 256 &&
                     kStageBytes % 1024 == 0,
                 "accumulator layout");
 };
 
 __device__ int g_gemm_status = 0;  // 0 ok, 1 = a pipeline wait expired
+
+#ifdef SGLB_TRACE
+// Development builds only: per-slab clock stamps of the roles of CTAs 0 and 1 (sglb200_debug_trace copies them out).
+constexpr int kTraceSlabs = 256, kTraceEvents = 4, kTraceRoles = 3;
+__device__ long long g_trace[2][kTraceRoles][kTraceSlabs][kTraceEvents];
+#define SGLB_STAMP(role, n, ev)                                                                  \
+  do {                                                                                           \
+    if (blockIdx.x < 2 && (n) < kTraceSlabs) g_trace[blockIdx.x][role][n][ev] = clock64();       \
+  } while (0)
+#else
+#define SGLB_STAMP(role, n, ev) \
+  do {                          \
+  } while (0)
+#endif
 
 struct GemmParams {
   const float* a_s;
@@ -108,7 +131,8 @@ struct GemmParams {
   int full_units;              // dense: the first `full_units` tiles are one unit each ...
   int splits;                  // ... and every later tile is cut into `splits` units along K (1 = none)
   int kb_per_split;            // K slabs per unit of a split tile
-  float* partial;              // float32 partial sums of the split tiles: [slot][BM][BN]
+  float* partial;              // float32 partial sums of the split tiles: [slot][BM x BN block]
+  int partial_rowmajor;        // layout of a block: 1 = [row][BN] (few rows), 0 = [column / 4][row][4] (full tiles)
   int nb_total;                // ceil(N/128): weight scale blocks along N
   int tiles_n;                 // ceil(N/BN)
   int scatter;
@@ -132,7 +156,7 @@ struct GemmParams {
 
 template <class Cfg>
 struct SharedCtl {
-  float b_strip[kEpiWarps][2][2][kBChunk];  // per promotion warp: [buffer][weight block within the tile][slab]
+  float b_strip[Cfg::kEpiWarps][2][2][kBChunk];  // per promotion warp: [buffer][weight block within the tile][slab]
   uint64_t full[Cfg::kStages];
   uint64_t empty[Cfg::kStages];
   uint64_t tmem_full[Cfg::kAccBufs];
@@ -235,12 +259,18 @@ template <class Cfg, int B>
 __device__ __forceinline__ bool promote_slab(uint32_t bar_tfull0, uint32_t bar_tempty0, uint32_t taddr0,
                                              uint32_t (&par)[Cfg::kAccBufs], uint32_t lane0, bool active, float a_sc,
                                              const float (&bsc)[Cfg::kPieces], float (&acc)[Cfg::kEpiCols],
-                                             volatile int* abort_flag, uint32_t probes) {
+                                             volatile int* abort_flag, uint32_t probes, int tn = -1) {
+  (void)tn;  // (slab counter of the development trace: stamps only where tn >= 0)
   // (the 32 lanes probe the same word in the same instruction, so the outcome is uniform across the warp, as
   // the warp-wide tcgen05.ld below requires)
+  if (tn >= 0) SGLB_STAMP(2, tn, 0);
   if (!ptx::mbar_wait_bounded(bar_tfull0 + B * 8, par[B], abort_flag, probes)) return false;
+  if (tn >= 0) SGLB_STAMP(2, tn, 1);
   par[B] ^= 1u;
   ptx::tc_fence_after();
+#ifdef SGLB_DBG_NOLDTM
+  active = false;  // (development: promotion only hands the buffer back)
+#endif
   if (active) {
     // All pieces of the slab are requested before the one wait (tcgen05.wait::ld waits for every outstanding
     // load of the thread): one TMEM round trip per slab sits on the hand-off chain MMA -> commit -> promotion
@@ -251,12 +281,29 @@ __device__ __forceinline__ bool promote_slab(uint32_t bar_tfull0, uint32_t bar_t
     ptx::tmem_ld_wait();
     ptx::tc_fence_before();
     release_buffer<Cfg>(bar_tempty0 + B * 8, lane0);
+    if (tn >= 0) SGLB_STAMP(2, tn, 2);
+#ifdef SGLB_DBG_NOFMA
+    // (development: one add per piece keeps the loads alive)
+#pragma unroll
+    for (int i = 0; i < Cfg::kPieces; ++i) acc[32 * i] += __uint_as_float(r[i][0] ^ r[i][31]) * a_sc * bsc[i];
+#elif SGLB_FMA2
+    // two columns per instruction (packed float32 FMA): half the issue slots of the promotion
+#pragma unroll
+    for (int i = 0; i < Cfg::kPieces; ++i) {
+      const float sc = a_sc * bsc[i];
+#pragma unroll
+      for (int jj = 0; jj < 32; jj += 2)
+        ptx::fma2(acc[32 * i + jj], acc[32 * i + jj + 1], r[i][jj], r[i][jj + 1], sc);
+    }
+#else
 #pragma unroll
     for (int i = 0; i < Cfg::kPieces; ++i) {
       const float sc = a_sc * bsc[i];
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) acc[32 * i + jj] = fmaf(__uint_as_float(r[i][jj]), sc, acc[32 * i + jj]);
     }
+#endif
+    if (tn >= 0) SGLB_STAMP(2, tn, 3);
   } else {
     // a warp whose 32 rows all lie past M has nothing to add: it only keeps the buffer hand-off in step
     ptx::tc_fence_before();
@@ -266,12 +313,13 @@ __device__ __forceinline__ bool promote_slab(uint32_t bar_tfull0, uint32_t bar_t
 }
 
 template <bool kGrouped, int BN_, bool kPair>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
     fp8_blockscale_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   static_assert(!(kGrouped && kPair), "the rows of a pair tile share one weight matrix");
   using Cfg = TileCfg<BN_, kPair>;
   constexpr int kTileRows = kPair ? 2 * BM : BM;  // rows of a scheduling tile
+  constexpr int kEpiWarps = Cfg::kEpiWarps;
   constexpr int BN = Cfg::BN, kStages = Cfg::kStages, kAccBufs = Cfg::kAccBufs, kEpiCols = Cfg::kEpiCols,
                 kPieces = Cfg::kPieces;
   constexpr uint32_t kStageBytes = Cfg::kStageBytes, kGroupBytes = Cfg::kGroupBytes;
@@ -339,6 +387,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t tiles0 = ptx::smem_u32(tiles);
       uint32_t s = 0, ph = 0;
       bool alive = true;
+      int tn = 0;
+      (void)tn;
       for (int u = unit0; u < num_units && alive; u += unit_step) {
         const Unit un = decode_unit<kGrouped>(p, u);
         const int kb_begin = un.kb_begin, kb_stop = un.kb_stop;
@@ -355,11 +405,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // spends per slab delays the loads, so the loop keeps only 32-bit counters that step
         const int row_a = m_tile * BM, row_b = n_tile * BN + (int)crank * Cfg::kBRows;
         for (int k0 = kb_begin * BK; k0 < kb_stop * BK; k0 += BK) {
+          SGLB_STAMP(0, tn, 0);
           if (!ptx::mbar_wait_bounded(bar_empty0 + s * 8, ph ^ 1u, abort_flag, probes)) {
             raise_abort();
             alive = false;
             break;
           }
+          SGLB_STAMP(0, tn, 1);
+          ++tn;
           const uint32_t dst_a = tiles0 + s * kStageBytes;
           if (kPair) {
             if (crank == 0) ptx::mbar_arrive_expect_tx(bar_full0 + s * 8, 2 * kStageBytes);
@@ -402,13 +455,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (p.expert_ids[m_tile] < 0) continue;
         }
         uint32_t buf = 0;  // every unit starts at buffer 0 (the promotion warps count on it)
+        bool ok = true;
         for (int kb = kb_begin; kb < kb_stop; ++kb) {
-          if (!ptx::mbar_wait_bounded(bar_tempty0 + buf * 8, ((tpar >> buf) & 1u) ^ 1u, abort_flag, probes) ||
-              !ptx::mbar_wait_bounded(bar_full0 + s * 8, ph, abort_flag, probes)) {
-            raise_abort();
-            alive = false;
-            break;
-          }
+          // (Measured: doing the next slab's waits between this slab's MMAs instead gains nothing with four TMEM
+          // buffers and loses a quarter with two, where the next buffer is still being read.)
+          ok = ptx::mbar_wait_bounded(bar_tempty0 + buf * 8, ((tpar >> buf) & 1u) ^ 1u, abort_flag, probes) &&
+               ptx::mbar_wait_bounded(bar_full0 + s * 8, ph, abort_flag, probes);
+          if (!ok) break;
           ptx::tc_fence_after();
           const uint32_t a_lo = desc_lo0 + s * (kStageBytes >> 4);
           const uint32_t b_lo = a_lo + (kTileBytesA >> 4);
@@ -437,6 +490,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tpar ^= 1u << buf;
           if (++buf == (uint32_t)kAccBufs) buf = 0;
         }
+        if (!ok) {
+          raise_abort();
+          alive = false;
+        }
       }
     }
   } else if (warp >= kEpiWarp0) {
@@ -459,6 +516,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
     for (int b = 0; b < kAccBufs; ++b) par[b] = 0;
     bool alive = true;
+#ifdef SGLB_TRACE
+    int tslab = 0;  // slabs this warp has promoted (development trace, first promotion warp's lane 0 only)
+#define SGLB_TN ((pw == 0 && lane == 0) ? tslab++ : -1)
+#else
+#define SGLB_TN (-1)
+#endif
 
     // what a promotion warp needs to know about a unit
     struct Hdr {
@@ -575,7 +638,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   {                                                                                                                 \
     _Pragma("unroll") for (int i = 0; i < kPieces; ++i) bsc[i] = ptx::lds_f32(b_addr + poff[i] + 4 * (J));          \
     alive = promote_slab<Cfg, (J) % kAccBufs>(bar_tfull0, bar_tempty0, taddr0, par, lane0, active, A_SC, bsc, acc,  \
-                                              abort_flag, probes);                                                  \
+                                              abort_flag, probes, SGLB_TN);                                         \
   }
             SGLB_SLAB(0, a_cur.x)
             if (alive) SGLB_SLAB(1, a_cur.y)
@@ -618,11 +681,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // fixed order, adds the bias and rounds once
         if (alive && row < rows) {  // (rows past M are never read back)
           // (a pair: the two CTAs' 128-row blocks of a unit follow each other)
+          // Layout of a block: with full tiles [column / 4][row][4], so that the 32 lanes of a warp (32 consecutive
+          // rows) write 512 contiguous bytes per store; with a handful of rows (weight streaming) [row][BN], where
+          // a row's columns stay together.  The reduction kernel reads it the same way.
           const int64_t blk = kPair ? (int64_t)cur.slot * 2 + crank : (int64_t)cur.slot;
-          float* dst = p.partial + blk * (BM * BN) + row_in_tile * BN + cgrp * kEpiCols;
+          if (p.partial_rowmajor) {
+            float* dst = p.partial + blk * (BM * BN) + row_in_tile * BN + cgrp * kEpiCols;
 #pragma unroll
-          for (int j = 0; j < kEpiCols / 4; ++j)
-            *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+            for (int j = 0; j < kEpiCols / 4; ++j)
+              *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          } else {
+            float* dst = p.partial + blk * (BM * BN) + ((int64_t)(cgrp * kEpiCols / 4) * BM + row_in_tile) * 4;
+#pragma unroll
+            for (int j = 0; j < kEpiCols / 4; ++j)
+              *reinterpret_cast<float4*>(dst + (int64_t)j * BM * 4) =
+                  make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          }
         }
         continue;
       }
@@ -636,7 +710,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // (A warp whose wait expired still joins both barriers; only the data movement is skipped.)
         const bool issuer = cgrp == 0 && lane == 0;
         if (issuer) ptx::tma_store_wait_read();
-        ptx::bar_sync(2 + q, 64);
+        ptx::bar_sync(2 + q, 32 * Cfg::kColGroups);
         const bool rows_in = (int64_t)cur.m_tile * BM + q * 32 < rows;
         if (alive && n0 < n_end && rows_in) {
           if (p.bias != nullptr) {
@@ -673,7 +747,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           ptx::fence_async_smem();
         }
-        ptx::bar_sync(2 + q, 64);
+        ptx::bar_sync(2 + q, 32 * Cfg::kColGroups);
         if (issuer && alive && rows_in) {
           const CUtensorMap* cmap = &map_c;
           int out_row0 = cur.m_tile * BM;
@@ -742,6 +816,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
+// Offset of element (row r of the tile, column c, a multiple of 4) inside a unit's partial sums: 128-row blocks one
+// after the other, each laid out [column / 4][row][4] or, with `rowmajor`, [row][BN]; `step` = distance between
+// the two float4 halves of an 8-column group.
+__device__ __forceinline__ int64_t partial_offset(int r, int c, int BN, int rowmajor) {
+  const int64_t blk = (int64_t)(r / BM) * (BM * BN);
+  return rowmajor ? blk + (int64_t)(r % BM) * BN + c : blk + ((int64_t)(c >> 2) * BM + (r % BM)) * 4;
+}
+// Thread i of a tile's reduction -> (row, first of 8 columns): columns fastest for the row-major layout, rows
+// fastest for the other, so that neighbouring threads read neighbouring words either way.
+__device__ __forceinline__ void reduce_coord(int i, int tile_rows, int BN, int rowmajor, int& r, int& c8) {
+  if (rowmajor) {
+    r = i / (BN / 8);
+    c8 = (i - r * (BN / 8)) * 8;
+  } else {
+    c8 = (i / tile_rows) * 8;
+    r = i - (i / tile_rows) * tile_rows;
+  }
+}
+
 // Sums the partial tiles of every split output tile in ascending split order (deterministic), adds the bias,
 // rounds once and writes the part of the tile that lies inside C.  One thread per 8 consecutive columns of a row;
 // grid = (split tiles, BM * BN / 8 / 256).
@@ -749,20 +842,22 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
     split_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
                         int64_t M, int64_t N, int BN, int tile_rows, int tiles_m, int tiles_n, int group_m,
-                        int full_units, int splits) {
+                        int full_units, int splits, int rowmajor) {
   const int tile = full_units + blockIdx.x;
   int m_tile, n_tile;
   tile_coord(tile, tiles_m, tiles_n, group_m, m_tile, n_tile);
-  const int i = blockIdx.y * 256 + threadIdx.x;  // 8-column group within the tile
-  const int r = i / (BN / 8), c8 = (i - r * (BN / 8)) * 8;
+  // one thread per (row, 8-column group)
+  int r, c8;
+  reduce_coord(blockIdx.y * 256 + threadIdx.x, tile_rows, BN, rowmajor, r, c8);
+  const int half = rowmajor ? 4 : BM * 4;
   const int64_t row = (int64_t)m_tile * tile_rows + r;
   const int64_t col = (int64_t)n_tile * BN + c8;
-  if (r >= tile_rows || row >= M || col >= N) return;  // N is a multiple of 8: a group is inside or outside as a whole
+  if (c8 >= BN || r >= tile_rows || row >= M || col >= N) return;  // N is a multiple of 8: a group is inside or outside as a whole
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const int64_t tile_elems = (int64_t)tile_rows * BN;  // (a pair's unit = two 128-row blocks one after the other)
-  const float* src = partial + (int64_t)blockIdx.x * splits * tile_elems + r * BN + c8;
+  const float* src = partial + (int64_t)blockIdx.x * splits * tile_elems + partial_offset(r, c8, BN, rowmajor);
   for (int s = 0; s < splits; ++s, src += tile_elems) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src + half));
     acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
     acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
   }
@@ -784,21 +879,22 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
     streamk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
                           int64_t M, int64_t N, int BN, int tile_rows, int tiles_m, int tiles_n, int group_m,
-                          int kb_total, int share, int ctas) {
+                          int kb_total, int share, int ctas, int rowmajor) {
   const int tile = blockIdx.x;
   int m_tile, n_tile;
   tile_coord(tile, tiles_m, tiles_n, group_m, m_tile, n_tile);
-  const int i = blockIdx.y * 256 + threadIdx.x;  // 8-column group within the tile
-  const int r = i / (BN / 8), c8 = (i - r * (BN / 8)) * 8;
+  int r, c8;
+  reduce_coord(blockIdx.y * 256 + threadIdx.x, tile_rows, BN, rowmajor, r, c8);
+  const int half = rowmajor ? 4 : BM * 4;
   const int64_t row = (int64_t)m_tile * tile_rows + r;
   const int64_t col = (int64_t)n_tile * BN + c8;
-  if (r >= tile_rows || row >= M || col >= N) return;
+  if (c8 >= BN || r >= tile_rows || row >= M || col >= N) return;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const int c_first = tile * kb_total / share, c_last = ((tile + 1) * kb_total - 1) / share;
   for (int c = c_first; c <= c_last; ++c) {
     const int slot = c + ctas * (tile - c * share / kb_total);
-    const float* src = partial + (int64_t)slot * tile_rows * BN + r * BN + c8;
-    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+    const float* src = partial + (int64_t)slot * tile_rows * BN + partial_offset(r, c8, BN, rowmajor);
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src + half));
     acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
     acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
   }
@@ -1052,7 +1148,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   if (sms < 1) sms = 1;
   if (!kPair) {
     const unsigned grid = (unsigned)(max_units < sms ? max_units : sms);
-    fp8_blockscale_gemm_kernel<kGrouped, BN, kPair><<<grid, kGemmThreads, smem, st>>>(ma, mb, mc, p);
+    fp8_blockscale_gemm_kernel<kGrouped, BN, kPair><<<grid, TileCfg<BN, kPair>::kThreads, smem, st>>>(ma, mb, mc, p);
     SGLB_CUDA(cudaGetLastError());
     return SGLB200_OK;
   }
@@ -1062,7 +1158,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   if (max_units < clusters) clusters = max_units;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.blockDim = dim3(TileCfg<BN, kPair>::kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -1104,6 +1200,7 @@ static int dense_mm(const DensePlan& dp, const void* A, const void* B, const flo
   p.full_units = pl.full_units, p.splits = pl.splits, p.kb_per_split = pl.kb_per_split;
   p.sk_share = pl.sk_share, p.sk_ctas = pl.sk_ctas, p.sk_pieces = pl.sk_pieces, p.sk_total = (int)(tiles * p.kb_total);
   p.partial = static_cast<float*>(workspace);
+  p.partial_rowmajor = M <= 32 ? 1 : 0;
   CUtensorMap mc{};
   p.tma_out = pl.sk_share == 0 && pl.full_units > 0;
   if (p.tma_out) {
@@ -1120,12 +1217,12 @@ static int dense_mm(const DensePlan& dp, const void* A, const void* B, const flo
     if (out_dtype == 0)
       streamk_reduce_kernel<__nv_bfloat16><<<sgrid, 256, 0, st>>>(
           p.partial, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, BN, kTileRows, tiles_m,
-          p.tiles_n, p.group_m, p.kb_total, pl.sk_share, pl.sk_ctas);
+          p.tiles_n, p.group_m, p.kb_total, pl.sk_share, pl.sk_ctas, p.partial_rowmajor);
     else
       streamk_reduce_kernel<__half><<<sgrid, 256, 0, st>>>(p.partial, static_cast<__half*>(C),
                                                            static_cast<const __half*>(bias), M, N, BN, kTileRows,
                                                            tiles_m, p.tiles_n, p.group_m, p.kb_total, pl.sk_share,
-                                                           pl.sk_ctas);
+                                                           pl.sk_ctas, p.partial_rowmajor);
     SGLB_CUDA(cudaGetLastError());
     return SGLB200_OK;
   }
@@ -1133,11 +1230,12 @@ static int dense_mm(const DensePlan& dp, const void* A, const void* B, const flo
   if (out_dtype == 0)
     split_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p.partial, static_cast<__nv_bfloat16*>(C),
                                                              static_cast<const __nv_bfloat16*>(bias), M, N, BN, kTileRows,
-                                                             tiles_m, p.tiles_n, p.group_m, pl.full_units, pl.splits);
+                                                             tiles_m, p.tiles_n, p.group_m, pl.full_units, pl.splits,
+                                                             p.partial_rowmajor);
   else
     split_reduce_kernel<__half><<<grid, 256, 0, st>>>(p.partial, static_cast<__half*>(C),
                                                       static_cast<const __half*>(bias), M, N, BN, kTileRows, tiles_m,
-                                                      p.tiles_n, p.group_m, pl.full_units, pl.splits);
+                                                      p.tiles_n, p.group_m, pl.full_units, pl.splits, p.partial_rowmajor);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }
@@ -1190,6 +1288,15 @@ extern "C" int sglb200_gemm_status(void) {
   if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
   return v;
 }
+
+#ifdef SGLB_TRACE
+extern "C" int sglb200_debug_trace(void* out, int64_t bytes) {
+  if (bytes > (int64_t)sizeof(long long) * 2 * kTraceRoles * kTraceSlabs * kTraceEvents)
+    bytes = (int64_t)sizeof(long long) * 2 * kTraceRoles * kTraceSlabs * kTraceEvents;
+  SGLB_CUDA(cudaMemcpyFromSymbol(out, g_trace, (size_t)bytes));
+  return SGLB200_OK;
+}
+#endif
 
 extern "C" void sglb200_gemm_set_wait_probes(uint32_t probes) { g_wait_probes = probes == 0 ? ptx::kProbeLimit : probes; }
 
@@ -1297,14 +1404,15 @@ static int get_push_maps(void* const* stage_ptrs, int world, uint64_t N, uint64_
   return SGLB200_OK;
 }
 
-template <int BN>
+template <int BN, bool kPair>
 static int push_mm(const void* A, const void* B, const float* a_s, const float* b_s, void* const* stage_ptrs, int world,
                    int rank, int64_t M, int64_t N, int64_t K, int64_t as_stride_m, int64_t as_stride_k, int out_dtype,
                    int sm_margin, cudaStream_t st) {
+  constexpr int kTileRows = kPair ? 2 * BM : BM;
   CUtensorMap ma, mb;
   int rc = get_tensor_map(A, (uint64_t)K, (uint64_t)M, 1, BM, 2, &ma);
   if (rc) return rc;
-  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, BN, 3, &mb);
+  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, TileCfg<BN, kPair>::kBRows, 3, &mb);
   if (rc) return rc;
   GemmParams p{};
   p.a_s = a_s, p.b_s = b_s, p.C = nullptr, p.bias = nullptr;
@@ -1312,10 +1420,10 @@ static int push_mm(const void* A, const void* B, const float* a_s, const float* 
   p.as_stride_m = as_stride_m, p.as_stride_k = as_stride_k;
   p.kb_total = (int)((K + BK - 1) / BK), p.nb_total = (int)((N + kScaleBlockN - 1) / kScaleBlockN);
   p.tiles_n = (int)((N + BN - 1) / BN);
-  p.group_m = choose_group_m(M, K);
+  p.group_m = choose_group_m(M, K, kTileRows);
   p.out_fp16 = out_dtype;
   p.wait_probes = g_wait_probes;
-  const int64_t tiles = ((M + BM - 1) / BM) * p.tiles_n;
+  const int64_t tiles = ((M + kTileRows - 1) / kTileRows) * p.tiles_n;
   p.full_units = (int)tiles, p.splits = 1, p.kb_per_split = p.kb_total, p.partial = nullptr;  // one unit per tile
   p.sk_pieces = 2;
   p.tma_out = 1;
@@ -1328,7 +1436,7 @@ static int push_mm(const void* A, const void* B, const float* a_s, const float* 
   CUtensorMap mc = {};
   rc = get_out_map(stage_ptrs[rank], (uint64_t)N, (uint64_t)(rpo * world), out_dtype, &mc);  // unused by the stores; keeps map_c valid
   if (rc) return rc;
-  return launch_gemm<false, BN, false>(ma, mb, mc, p, tiles, st, sm_margin);
+  return launch_gemm<false, BN, kPair>(ma, mb, mc, p, tiles, st, sm_margin);
 }
 
 }  // namespace sglb200
@@ -1366,7 +1474,13 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B
   SGLB_REQUIRE(aligned16(A) && aligned16(B), "mm_push: A and B must be 16-byte aligned");
   SGLB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "mm_push: dimension too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (choose_bn(K) == 128)
-    return push_mm<128>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, sm_margin, st);
-  return push_mm<192>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, sm_margin, st);
+  const DensePlan dp = plan_dense(M, N, K);  // (tile shape only: a pushed tile is never split along K)
+#define SGLB_PUSH(BN_, PAIR_)                                                                                        \
+  return push_mm<BN_, PAIR_>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, \
+                             sm_margin, st)
+  if (dp.bn == 128 && dp.pair) SGLB_PUSH(128, true);
+  if (dp.bn == 128) SGLB_PUSH(128, false);
+  if (dp.pair) SGLB_PUSH(192, true);
+  SGLB_PUSH(192, false);
+#undef SGLB_PUSH
 }

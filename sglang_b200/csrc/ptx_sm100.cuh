@@ -88,7 +88,11 @@ __device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.u32 p, %1, 0;\n\t"
+#ifdef SGLB_RELAXED_ARRIVE
+      "@p mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar),
+#else
       "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar),
+#endif
       "r"(pred)
       : "memory");
 }
@@ -105,6 +109,18 @@ __device__ __forceinline__ float4 lds_f32x4(uint32_t addr) {
 }
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// (a0, a1) += (r0, r1) * sc: one packed float32 FMA for two adjacent columns.
+__device__ __forceinline__ void fma2(float& a0, float& a1, uint32_t r0, uint32_t r1, float sc) {
+  asm("{\n\t.reg .b64 ra, rs, rc;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rs, {%4, %4};\n\t"
+      "mov.b64 rc, {%0, %1};\n\t"
+      "fma.rn.f32x2 rc, ra, rs, rc;\n\t"
+      "mov.b64 {%0, %1}, rc;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "r"(r0), "r"(r1), "f"(sc));
 }
 
 // Two 32-bit words as one 64-bit register (shared-memory matrix descriptors are built from halves).
@@ -208,7 +224,10 @@ __device__ __forceinline__ void mbar_arrive_cluster_if(uint32_t bar_cluster, uin
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.u32 p, %1, 0;\n\t"
-      "@p mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n\t}" ::"r"(bar_cluster),
+      // (relaxed: the arrival only says "my tensor-memory reads are done", which tcgen05.wait::ld has already made
+      // true; a release at cluster scope would first wait for every earlier store of the thread, over a thousand
+      // clocks per slab)
+      "@p mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n\t}" ::"r"(bar_cluster),
       "r"(pred)
       : "memory");
 }

@@ -101,6 +101,36 @@ def test_ep_dispatch_combine_two_gloo_ranks():
     assert ret[0]["send_splits"][1] == ret[1]["recv_splits"][0]
 
 
+def test_dispatch_mask_mixed_filtered_and_valid_ids():
+    """Rows that mix a filtered slot (-1), an id past the last expert and valid ids: a token goes to a rank exactly
+    when one of its VALID slots names an expert of that rank, whatever the order of its slots."""
+    from sglang_b200.srt.distributed import GroupCoordinator
+    from sglang_b200.srt.layers.moe.fused_moe_triton import ep_a2a
+
+    class FakeGroup(GroupCoordinator):  # four ranks' worth of planning on one process: only the mask is looked at
+        def __init__(self):
+            self.ranks, self.world_size, self.rank, self.rank_in_group, self.device_group = [0, 1, 2, 3], 4, 0, 0, None
+
+        def all_to_all_single(self, out, inp, out_splits, in_splits):
+            out.copy_(inp)
+            return out
+
+    E_local = 2  # experts 0-1 on rank 0, 2-3 on rank 1, 4-5 on rank 2, 6-7 on rank 3
+    ids = torch.tensor([[-1, 0, 1],      # filtered slot first, then two experts of rank 0 -> rank 0 only
+                        [1, -1, -1],     # valid slot first, filtered after it -> rank 0 (the -1s must not erase it)
+                        [-1, -1, -1],    # nothing valid -> nowhere
+                        [7, 8, 2],       # 8 is past the last expert -> ranks 3 and 1, not clamped onto rank 3 twice
+                        [9, -1, 100],    # nothing valid -> nowhere
+                        [6, 0, 3]], dtype=torch.int32)
+    plan = ep_a2a.plan_dispatch(ids, E_local, FakeGroup())
+    sent = {(int(t), r) for r, n in enumerate(plan.send_splits) for t in
+            plan.send_token[sum(plan.send_splits[:r]): sum(plan.send_splits[:r]) + n]}
+    assert sent == {(0, 0), (1, 0), (3, 1), (3, 3), (5, 0), (5, 1), (5, 3)}
+    assert plan.send_splits == [3, 2, 0, 2]
+    S = int(plan.send_token.numel())
+    assert (plan.slot[2] == S).all() and (plan.slot[4] == S).all()  # tokens that go nowhere point at the zero row
+
+
 def _tp_worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
