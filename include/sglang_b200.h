@@ -274,11 +274,11 @@ int sglb200_gemm_status(void);
 int sglb200_gemm_status_clear(void);
 
 /*
- * Number of barrier probes (a few microseconds each) after which a pipeline wait inside the GEMM kernels gives
- * up; 0 restores the default (about 4 million: seconds); UINT32_MAX makes every wait give up at once.  Applies to
- * GEMMs launched afterwards by this process.  A diagnostic knob: with UINT32_MAX a healthy GEMM gives up before it
- * has loaded anything, which exercises the give-up path (status word, drain, tensor-memory release) without any
- * fault.  No counterpart in the reference.
+ * Diagnostic knob of the GEMM kernels' pipeline waits (each a bounded run of barrier probes, seconds at most):
+ * UINT32_MAX makes every wait give up at once, so that a healthy GEMM gives up before it has loaded anything, which
+ * exercises the give-up path (status word, drain, tensor-memory release) without any fault; any other value
+ * restores the normal limit.  Applies to GEMMs launched afterwards by this process.  No counterpart in the
+ * reference.
  */
 void sglb200_gemm_set_wait_probes(uint32_t probes);
 

@@ -2,42 +2,39 @@
 //
 //   C[m,n] = out_t( sum_kb a_s[m,kb] * b_s[n/128,kb] * sum_{k in kb} A[m,k] * B[n,k] )
 //
-// One persistent CTA per SM walks 128 x BN output tiles.  BN = 192 for long K (a 128x128 tile needs 128 B/clk
-// per SM from L2 at full tensor rate, more than the fabric delivers; 128x192 needs 107, and its 32-column
-// pieces never straddle a 128-wide scale block); BN = 128 with four accumulator buffers for short K, where a
-// whole tile's partial sums fit in tensor memory and the MMAs of the next tile run under the epilogue of the
-// current one.  Per 128-wide K slab:
+// One persistent CTA per SM walks 128 x BN output tiles.  BN = 192 with two TMEM accumulator buffers where there
+// are waves of full tiles (fewest bytes per FLOP from L2, fewest tiles; its 32-column pieces never straddle a
+// 128-wide scale block), BN = 128 with four buffers for small and medium row counts and for the expert-grouped
+// form (more tiles to spread, a deeper hand-off between the MMAs and the promotion).  Per 128-wide K slab:
 //   * warp 0 (one elected lane) issues two TMA tile loads (A 128 rows x 128 B, B BN rows x 128 B,
 //     128-byte swizzle) into a shared-memory ring, signalled through `full` mbarriers;
 //   * warp 1 (one elected lane) issues four tcgen05.mma kind::f8f6f4 (128 x BN x 32) that write the
-//     slab's partial sums into one of the TMEM buffers, then commits the slab to the `empty` barrier of
-//     the ring slot and to the `tmem_full` barrier of the buffer;
+//     slab's partial sums into one of the TMEM buffers, then commits the slab to the
+//     `empty` barrier of the ring slot and to the `tmem_full` barrier of the buffer;
 //   * warps 4-11 (two per TMEM lane quadrant, BN/2 columns each) pull the partial sums out of TMEM with
 //     32-column tcgen05.ld issued back to back, release the buffer, and promote them into float32 register
 //     accumulators with the slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be
 //     folded into the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores, overlapped with
-//     the next slab's MMAs through the TMEM buffers).  The slab loop is unrolled four ways: every unit starts
-//     at buffer 0, so buffer, barrier and TMEM addresses are compile-time constants and the four activation
-//     scales of a group are the components of one 128-bit load issued a group ahead.  The weight-block scales
-//     of the tile are staged by each warp for itself in its own strip of shared memory (64 slabs at a time,
-//     double-buffered), so the slab loop has no barrier between warps.
-// The kernel runs power- and issue-limited rather than tensor-limited: every instruction a promotion warp
-// executes or a waiting warp spends polling costs time, so the per-slab code is kept short and waits suspend
-// in hardware (mbarrier.try_wait with a time hint).
-// Epilogue: each promotion warp rounds its 32 rows x BN/2 columns to bf16/fp16, parks them in its own part of
-// shared memory (32 x 32 pieces, 64-byte swizzle) and its lane 0 hands the pieces to the TMA engine; the
-// stores drain during the next tile, and no barrier spans the warps.  The scales of the NEXT unit are requested
-// before the epilogue so that they arrive under it.  In grouped "scatter" mode the epilogue multiplies by the
-// routing weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids.
-// Scheduling: with fewer than two waves of tiles and a long K the tiles x slabs space is cut into one equal
-// run of slabs per SM (stream-K; a run covers the end of one tile, possibly a whole tile, and the start of the
-// next); otherwise the tiles of a short last wave are split along K.  Split work writes float32 partial sums
-// that a second kernel adds in ascending K order.  In push mode (row-parallel layers under tensor parallelism)
-// a tile is stored through the tensor map of the staging buffer of the GPU that owns its rows, which folds the
+//     the next slabs' MMAs through the TMEM buffers), two columns per instruction (packed float32 FMA).  A
+//     thread's activation scales are prefetched into registers four slabs at a time; the weight-block scales of
+//     the tile are staged by each warp for itself in its own strip of shared memory, so the slab loop has no
+//     barrier between warps.
+// The kernel runs latency-, power- and issue-limited rather than tensor-limited (the tensor pipe is busy 40-50 %
+// of the cycles): every instruction a promotion warp executes or a waiting warp spends polling costs time,
+// so the per-slab loops are kept short, waits suspend in hardware (mbarrier.try_wait with a time hint) and
+// each promotion warp owns as many columns as the register file allows (fewer warps = less per-slab overhead).
+// The epilogue rounds to bf16/fp16, parks the tile in swizzled shared memory and writes it with TMA
+// stores that drain during the next tile; in grouped "scatter" mode it multiplies by the routing
+// weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids.
+// Scheduling: with fewer than two waves of tiles and a long K the tiles x slabs space is cut into one equal run
+// of slabs per SM (stream-K; a run covers the end of one tile, possibly a whole tile, and the start of the next);
+// otherwise the tiles of a short last wave are split along K.  Split work writes float32 partial sums that a
+// second kernel adds in ascending K order.  In push mode (row-parallel layers under tensor parallelism) a tile is
+// stored through the tensor map of the staging buffer of the GPU that owns its rows, which folds the
 // reduce-scatter of the all-reduce into the epilogue.
 //
-// Every mbarrier wait is bounded; on expiry the role raises a flag in shared memory that the other waiters
-// poll, the CTA sets a status word, drains, frees its TMEM and returns (sglb200_gemm_status() reports it).
+// Every mbarrier wait is bounded; on expiry the role raises a flag in shared memory that the other waiters poll,
+// the CTA sets a status word, drains, frees its TMEM and returns (sglb200_gemm_status() reports it).
 #include <cuda.h>
 
 #include <mutex>
@@ -52,67 +49,42 @@ constexpr int BM = 128, BK = 128;
 constexpr int kScaleBlockN = 128;         // weight scales cover 128 output rows
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarp0 = 4;              // warp 0 TMA, warp 1 MMA + TMEM owner, warps 4.. promotion + epilogue
-#ifndef SGLB_EPI_WARPS_128
-#define SGLB_EPI_WARPS_128 8              // promotion warps of the 128-wide tile (8 or 16); the 192-wide tile has 8
-#endif
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 128 + kEpiWarps * 32;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kColGroups = kEpiWarps / 4;  // promotion warps per TMEM lane quadrant
 constexpr uint32_t kTileBytesA = BM * BK;  // fp8
-constexpr int kBChunk = 64;                // slabs of weight-block scales a promotion warp stages at a time
-#ifndef SGLB_LOOKAHEAD_ALL
-#define SGLB_LOOKAHEAD_ALL 0
-#endif
+// A pipeline wait: a bounded run of suspending probes (seconds at most).  `p.wait_probes == kProbesNone` (a
+// diagnostic setting) makes every wait give up at once, which exercises the give-up path on a healthy GPU.
+// (Measured: also polling the CTA's abort flag between runs of probes, so that one role's expiry ends the others'
+// waits early, cost 5 % of the large-M rate; each role sits out its own limit instead.)
+#define SGLB_WAIT(bar, parity) (p.wait_probes != ptx::kProbesNone && ptx::mbar_wait_quiet(bar, parity))
 #ifndef SGLB_FMA2
 #define SGLB_FMA2 1                        // promotion with packed float32 FMAs (two columns per instruction)
 #endif
-#ifndef SGLB_SHORT_K
-#define SGLB_SHORT_K 1000000               // problems with at most this many K slabs use the 128-wide tile (all of
-                                           // them: measured equal to the 192-wide tile at M >= 1024 and 10-30 % ahead
-                                           // of it below, dense and grouped; the 192-wide tile stays selectable)
-#endif
 
-// kPair: two CTAs (a cluster of two SMs) share 256 x BN tiles through tcgen05.mma.cta_group::2; each stages its own
-// 128 rows of A and HALF of the BN rows of B, so a slab costs 28 KB of shared-memory writes and 28 KB of operand
-// reads per SM instead of 40 + 40 (shared memory moves 128 B/clk: a single CTA is capped at about 60 % of the
-// tensor rate by it).
-template <int BN_, bool kPair_ = false>
+// Tile width BN: 192 columns with two TMEM accumulator buffers (the fewest bytes per FLOP from L2 and the fewest
+// tiles: best where there are waves of full tiles), or 128 columns with four buffers (more tiles for the same
+// problem and a deeper hand-off between the MMAs and the promotion: best where tiles are few or short).
+template <int BN_>
 struct TileCfg {
   static constexpr int BN = BN_;
-  static constexpr bool kPair = kPair_;
-  static constexpr int kBRows = kPair_ ? BN_ / 2 : BN_;  // rows of B this CTA stages per slab
-  static constexpr int kStages = kPair_ ? (BN_ >= 192 ? 6 : 7) : (BN_ >= 192 ? 4 : 5);
+  static constexpr int kStages = BN_ >= 192 ? 4 : 5;
   static constexpr int kAccBufs = kTmemCols / BN_;   // TMEM accumulator buffers in flight
   static constexpr int kAccStride = BN_;             // TMEM columns between buffers
-  static constexpr int kEpiWarps = BN_ == 128 ? SGLB_EPI_WARPS_128 : 8;  // promotion + epilogue warps
-  static constexpr int kColGroups = kEpiWarps / 4;   // promotion warps per TMEM lane quadrant
-  static constexpr int kThreads = kEpiWarp0 * 32 + kEpiWarps * 32;
   static constexpr int kEpiCols = BN_ / kColGroups;  // columns of a buffer owned by one promotion warp
-  static constexpr int kPieces = kEpiCols / 32;      // 32-column pieces per warp
-  static constexpr uint32_t kTileBytesB = kBRows * BK;
+  static constexpr uint32_t kTileBytesB = BN_ * BK;
   static constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
-  // output staging for the TMA store: per TMEM lane quadrant and 64 columns a [32 rows][64 columns] 2-byte block in
-  // the 128-byte swizzle
+  // output staging for the TMA store: per 64 columns a [128 rows][64 columns] 2-byte tile in the 128-byte swizzle
   static constexpr int kOutGroups = BN_ / 64;
-  static constexpr uint32_t kGroupBytes = 32 * 64 * 2;
-  static constexpr uint32_t kOutBytes = 4 * kOutGroups * kGroupBytes;
-  static_assert(kEpiWarps % 4 == 0 && kEpiCols % 32 == 0 && BN_ % 64 == 0 && (4 % kAccBufs) == 0 && kAccBufs * kAccStride <= kTmemCols && BN_ <= 256 &&
-                    kStageBytes % 1024 == 0,
+  static constexpr uint32_t kOutGroupBytes = BM * 64 * 2;
+  static constexpr uint32_t kOutBytes = kOutGroups * kOutGroupBytes;
+  static_assert(kEpiWarps % 4 == 0 && BN_ % kColGroups == 0 && kEpiCols % 32 == 0 && BN_ % 64 == 0 &&
+                    kAccBufs * kAccStride <= kTmemCols && BN_ <= 256 && kStageBytes % 1024 == 0,
                 "accumulator layout");
 };
 
 __device__ int g_gemm_status = 0;  // 0 ok, 1 = a pipeline wait expired
-
-#ifdef SGLB_TRACE
-// Development builds only: per-slab clock stamps of the roles of CTAs 0 and 1 (sglb200_debug_trace copies them out).
-constexpr int kTraceSlabs = 256, kTraceEvents = 4, kTraceRoles = 3;
-__device__ long long g_trace[2][kTraceRoles][kTraceSlabs][kTraceEvents];
-#define SGLB_STAMP(role, n, ev)                                                                  \
-  do {                                                                                           \
-    if (blockIdx.x < 2 && (n) < kTraceSlabs) g_trace[blockIdx.x][role][n][ev] = clock64();       \
-  } while (0)
-#else
-#define SGLB_STAMP(role, n, ev) \
-  do {                          \
-  } while (0)
-#endif
 
 struct GemmParams {
   const float* a_s;
@@ -154,15 +126,21 @@ struct GemmParams {
   uint32_t wait_probes;          // probes after which a pipeline wait gives up
 };
 
+constexpr int kBChunk = 256;  // slabs of weight-block scales a promotion warp stages at a time
+
 template <class Cfg>
 struct SharedCtl {
-  float b_strip[Cfg::kEpiWarps][2][2][kBChunk];  // per promotion warp: [buffer][weight block within the tile][slab]
+  float b_stage[kEpiWarps][2][kBChunk];  // per promotion warp: [weight block within the tile][slab]
   uint64_t full[Cfg::kStages];
   uint64_t empty[Cfg::kStages];
   uint64_t tmem_full[Cfg::kAccBufs];
   uint64_t tmem_empty[Cfg::kAccBufs];
   uint32_t tmem_base;
   int abort_flag;
+};
+
+struct TileCoord {
+  int m_tile, n_tile, expert;
 };
 
 // tile index -> (m_tile, n_tile): groups of `group_m` m-tiles sweep over n together, m fastest inside a group.
@@ -245,105 +223,30 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, const
   }
 }
 
-// One K slab of one promotion warp: wait for the slab's partial sums in TMEM buffer B, pull this warp's columns
-// into registers, hand the buffer back, and add them, scaled, to the accumulators.  `bsc[i]` is the weight-block
-// scale of the warp's i-th 32-column piece for this slab.  Returns false when the wait expired.
-template <class Cfg>
-__device__ __forceinline__ void release_buffer(uint32_t bar, uint32_t lane0) {
-  if (Cfg::kPair)
-    ptx::mbar_arrive_cluster_if(bar, lane0);
-  else
-    ptx::mbar_arrive_if(bar, lane0);
-}
-template <class Cfg, int B>
-__device__ __forceinline__ bool promote_slab(uint32_t bar_tfull0, uint32_t bar_tempty0, uint32_t taddr0,
-                                             uint32_t (&par)[Cfg::kAccBufs], uint32_t lane0, bool active, float a_sc,
-                                             const float (&bsc)[Cfg::kPieces], float (&acc)[Cfg::kEpiCols],
-                                             volatile int* abort_flag, uint32_t probes, int tn = -1) {
-  (void)tn;  // (slab counter of the development trace: stamps only where tn >= 0)
-  // (the 32 lanes probe the same word in the same instruction, so the outcome is uniform across the warp, as
-  // the warp-wide tcgen05.ld below requires)
-  if (tn >= 0) SGLB_STAMP(2, tn, 0);
-  if (!ptx::mbar_wait_bounded(bar_tfull0 + B * 8, par[B], abort_flag, probes)) return false;
-  if (tn >= 0) SGLB_STAMP(2, tn, 1);
-  par[B] ^= 1u;
-  ptx::tc_fence_after();
-#ifdef SGLB_DBG_NOLDTM
-  active = false;  // (development: promotion only hands the buffer back)
-#endif
-  if (active) {
-    // All pieces of the slab are requested before the one wait (tcgen05.wait::ld waits for every outstanding
-    // load of the thread): one TMEM round trip per slab sits on the hand-off chain MMA -> commit -> promotion
-    // -> release.  The buffer goes back to the MMA thread as soon as the pieces are in registers.
-    uint32_t r[Cfg::kPieces][32];
-#pragma unroll
-    for (int i = 0; i < Cfg::kPieces; ++i) ptx::tmem_ld_32x32(taddr0 + B * Cfg::kAccStride + 32 * i, r[i]);
-    ptx::tmem_ld_wait();
-    ptx::tc_fence_before();
-    release_buffer<Cfg>(bar_tempty0 + B * 8, lane0);
-    if (tn >= 0) SGLB_STAMP(2, tn, 2);
-#ifdef SGLB_DBG_NOFMA
-    // (development: one add per piece keeps the loads alive)
-#pragma unroll
-    for (int i = 0; i < Cfg::kPieces; ++i) acc[32 * i] += __uint_as_float(r[i][0] ^ r[i][31]) * a_sc * bsc[i];
-#elif SGLB_FMA2
-    // two columns per instruction (packed float32 FMA): half the issue slots of the promotion
-#pragma unroll
-    for (int i = 0; i < Cfg::kPieces; ++i) {
-      const float sc = a_sc * bsc[i];
-#pragma unroll
-      for (int jj = 0; jj < 32; jj += 2)
-        ptx::fma2(acc[32 * i + jj], acc[32 * i + jj + 1], r[i][jj], r[i][jj + 1], sc);
-    }
-#else
-#pragma unroll
-    for (int i = 0; i < Cfg::kPieces; ++i) {
-      const float sc = a_sc * bsc[i];
-#pragma unroll
-      for (int jj = 0; jj < 32; ++jj) acc[32 * i + jj] = fmaf(__uint_as_float(r[i][jj]), sc, acc[32 * i + jj]);
-    }
-#endif
-    if (tn >= 0) SGLB_STAMP(2, tn, 3);
-  } else {
-    // a warp whose 32 rows all lie past M has nothing to add: it only keeps the buffer hand-off in step
-    ptx::tc_fence_before();
-    release_buffer<Cfg>(bar_tempty0 + B * 8, lane0);
-  }
-  return true;
-}
-
-template <bool kGrouped, int BN_, bool kPair>
-__global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
+template <bool kGrouped, int BN_>
+__global__ void __launch_bounds__(kGemmThreads, 1)
     fp8_blockscale_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
-  static_assert(!(kGrouped && kPair), "the rows of a pair tile share one weight matrix");
-  using Cfg = TileCfg<BN_, kPair>;
-  constexpr int kTileRows = kPair ? 2 * BM : BM;  // rows of a scheduling tile
-  constexpr int kEpiWarps = Cfg::kEpiWarps;
-  constexpr int BN = Cfg::BN, kStages = Cfg::kStages, kAccBufs = Cfg::kAccBufs, kEpiCols = Cfg::kEpiCols,
-                kPieces = Cfg::kPieces;
-  constexpr uint32_t kStageBytes = Cfg::kStageBytes, kGroupBytes = Cfg::kGroupBytes;
+  using Cfg = TileCfg<BN_>;
+  constexpr int BN = Cfg::BN, kStages = Cfg::kStages, kAccBufs = Cfg::kAccBufs, kAccStride = Cfg::kAccStride,
+                kEpiCols = Cfg::kEpiCols, kOutGroups = Cfg::kOutGroups;
+  constexpr uint32_t kStageBytes = Cfg::kStageBytes, kOutGroupBytes = Cfg::kOutGroupBytes, kOutBytes = Cfg::kOutBytes;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* out_stage = tiles + kStages * kStageBytes;
-  SharedCtl<Cfg>* ctl = reinterpret_cast<SharedCtl<Cfg>*>(out_stage + Cfg::kOutBytes);
+  SharedCtl<Cfg>* ctl = reinterpret_cast<SharedCtl<Cfg>*>(out_stage + kOutBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &ctl->abort_flag;
-  const uint32_t probes = p.wait_probes;
 
   int64_t rows = p.M;
   if (kGrouped) {
     const int64_t lim = *p.num_rows_dev;
     rows = lim < rows ? lim : rows;
   }
-  const int tiles_m = (int)((rows + kTileRows - 1) / kTileRows);
+  const int tiles_m = (int)((rows + BM - 1) / BM);
   const int tiles_n = p.tiles_n;
   const int num_tiles = tiles_m * tiles_n;
-  // a pair walks its units together: both CTAs see the same sequence
-  const uint32_t crank = kPair ? ptx::cluster_ctarank() : 0u;
-  const int unit0 = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-  const int unit_step = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int kb_total = p.kb_total;
   const int num_units = kGrouped         ? num_tiles
                         : p.sk_share > 0 ? p.sk_pieces * p.sk_ctas
@@ -356,8 +259,7 @@ __global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
     }
     for (int b = 0; b < kAccBufs; ++b) {
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[b]), 1);
-      // (a pair: the leader's barrier collects the promotion warps of both CTAs)
-      ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), kPair ? 2 * kEpiWarps : kEpiWarps);
+      ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), kEpiWarps);
     }
     ctl->abort_flag = 0;
     ptx::mbar_fence_init();
@@ -370,32 +272,22 @@ __global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if (kPair) ptx::cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   ptx::tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
-  auto raise_abort = [&]() {
-    *abort_flag = 1;
-    if (kPair) ptx::st_cluster_u32(ptx::mapa(ptx::smem_u32(&ctl->abort_flag), crank ^ 1u), 1u);  // the peer leaves too
-  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (ptx::elect_one()) {
       const uint32_t bar_empty0 = ptx::smem_u32(&ctl->empty[0]), bar_full0 = ptx::smem_u32(&ctl->full[0]);
-      // (a pair: the bytes of both CTAs are counted on the leader's barrier, which the leader arms for both)
-      const uint32_t bar_full_lead0 = kPair ? ptx::mapa(bar_full0, 0) : bar_full0;
       const uint32_t tiles0 = ptx::smem_u32(tiles);
       uint32_t s = 0, ph = 0;
       bool alive = true;
-      int tn = 0;
-      (void)tn;
-      for (int u = unit0; u < num_units && alive; u += unit_step) {
+      for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
         const Unit un = decode_unit<kGrouped>(p, u);
-        const int kb_begin = un.kb_begin, kb_stop = un.kb_stop;
-        if (kb_begin >= kb_stop) continue;
+        const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
+        if (kb_begin >= kb_stop) continue;  // (an empty piece of a stream-K run)
         int m_tile, n_tile;
-        tile_coord(un.tile, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
-        if (kPair) m_tile = 2 * m_tile + (int)crank;
+        tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
         int e = 0;
         if (kGrouped) {
           e = p.expert_ids[m_tile];
@@ -403,28 +295,14 @@ __global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
         }
         // this thread shares its scheduler with promotion warps that always have work: every instruction it
         // spends per slab delays the loads, so the loop keeps only 32-bit counters that step
-        const int row_a = m_tile * BM, row_b = n_tile * BN + (int)crank * Cfg::kBRows;
+        const int row_a = m_tile * BM, row_b = n_tile * BN;
         for (int k0 = kb_begin * BK; k0 < kb_stop * BK; k0 += BK) {
-          SGLB_STAMP(0, tn, 0);
-          if (!ptx::mbar_wait_bounded(bar_empty0 + s * 8, ph ^ 1u, abort_flag, probes)) {
-            raise_abort();
-            alive = false;
-            break;
-          }
-          SGLB_STAMP(0, tn, 1);
-          ++tn;
+          if (!SGLB_WAIT(bar_empty0 + s * 8, ph ^ 1u)) { *abort_flag = 1; alive = false; break; }
+          const uint32_t bar = bar_full0 + s * 8;
+          ptx::mbar_arrive_expect_tx(bar, kStageBytes);
           const uint32_t dst_a = tiles0 + s * kStageBytes;
-          if (kPair) {
-            if (crank == 0) ptx::mbar_arrive_expect_tx(bar_full0 + s * 8, 2 * kStageBytes);
-            const uint32_t bar = bar_full_lead0 + s * 8;
-            ptx::tma_load_2d_pair(dst_a, &map_a, bar, k0, row_a);
-            ptx::tma_load_3d_pair(dst_a + kTileBytesA, &map_b, bar, k0, row_b, e);
-          } else {
-            const uint32_t bar = bar_full0 + s * 8;
-            ptx::mbar_arrive_expect_tx(bar, kStageBytes);
-            ptx::tma_load_2d(dst_a, &map_a, bar, k0, row_a);
-            ptx::tma_load_3d(dst_a + kTileBytesA, &map_b, bar, k0, row_b, e);
-          }
+          ptx::tma_load_2d(dst_a, &map_a, bar, k0, row_a);
+          ptx::tma_load_3d(dst_a + kTileBytesA, &map_b, bar, k0, row_b, e);
           if (++s == (uint32_t)kStages) {
             s = 0;
             ph ^= 1u;
@@ -434,264 +312,187 @@ __global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (ptx::elect_one() && crank == 0) {  // (of a pair, the leader issues the MMAs for both CTAs)
-      constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(kTileRows, BN);
+    if (ptx::elect_one()) {
+      constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
       // Operand descriptor (K-major, 128-byte swizzle): low word = address/16 | LBO(1) << 16, high word =
       // SBO(1024/16) | version 1 (bit 46) | layout SWIZZLE_128B (2 at bit 61).  Only the low word changes.
       constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
       const uint32_t desc_lo0 = ((ptx::smem_u32(tiles) & 0x3ffffu) >> 4) | (1u << 16);
       const uint32_t bar_full0 = ptx::smem_u32(&ctl->full[0]), bar_empty0 = ptx::smem_u32(&ctl->empty[0]);
       const uint32_t bar_tfull0 = ptx::smem_u32(&ctl->tmem_full[0]), bar_tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
-      uint32_t s = 0, ph = 0;
-      uint32_t tpar = 0;  // bit b: parity of the last completed release of TMEM buffer b
+      uint32_t s = 0, ph = 0, buf = 0, aph = 0;
       bool alive = true;
-      for (int u = unit0; u < num_units && alive; u += unit_step) {
+      for (int u = blockIdx.x; u < num_units && alive; u += gridDim.x) {
         const Unit un = decode_unit<kGrouped>(p, u);
-        const int kb_begin = un.kb_begin, kb_stop = un.kb_stop;
+        const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
         if (kb_begin >= kb_stop) continue;
         if (kGrouped) {
           int m_tile, n_tile;
-          tile_coord(un.tile, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
+          tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
           if (p.expert_ids[m_tile] < 0) continue;
         }
-        uint32_t buf = 0;  // every unit starts at buffer 0 (the promotion warps count on it)
-        bool ok = true;
         for (int kb = kb_begin; kb < kb_stop; ++kb) {
-          // (Measured: doing the next slab's waits between this slab's MMAs instead gains nothing with four TMEM
-          // buffers and loses a quarter with two, where the next buffer is still being read.)
-          ok = ptx::mbar_wait_bounded(bar_tempty0 + buf * 8, ((tpar >> buf) & 1u) ^ 1u, abort_flag, probes) &&
-               ptx::mbar_wait_bounded(bar_full0 + s * 8, ph, abort_flag, probes);
-          if (!ok) break;
+          if (!SGLB_WAIT(bar_tempty0 + buf * 8, aph ^ 1u)) { *abort_flag = 1; alive = false; break; }
+          if (!SGLB_WAIT(bar_full0 + s * 8, ph)) { *abort_flag = 1; alive = false; break; }
           ptx::tc_fence_after();
           const uint32_t a_lo = desc_lo0 + s * (kStageBytes >> 4);
           const uint32_t b_lo = a_lo + (kTileBytesA >> 4);
-          const uint32_t d_tmem = tmem_base + buf * Cfg::kAccStride;
+          const uint32_t d_tmem = tmem_base + buf * kAccStride;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             // advancing 32 bytes along K inside the 128-byte swizzled row = +2 in the descriptor's 16-byte units
-            if (kPair)
-              ptx::mma_f8f6f4_pair(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi),
-                                   idesc, k > 0 ? 1u : 0u);
-            else
-              ptx::mma_f8f6f4(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi), idesc,
-                              k > 0 ? 1u : 0u);
+            ptx::mma_f8f6f4(d_tmem, ptx::pack_f32x2(a_lo + 2 * k, kDescHi), ptx::pack_f32x2(b_lo + 2 * k, kDescHi), idesc,
+                            k > 0 ? 1u : 0u);
           }
-          if (kPair) {  // (both CTAs' ring slots are free, both CTAs' promotion warps may read)
-            ptx::mma_commit_pair(bar_empty0 + s * 8);
-            ptx::mma_commit_pair(bar_tfull0 + buf * 8);
-          } else {
-            ptx::mma_commit(bar_empty0 + s * 8);
-            ptx::mma_commit(bar_tfull0 + buf * 8);
-          }
+          ptx::mma_commit(bar_empty0 + s * 8);
+          ptx::mma_commit(bar_tfull0 + buf * 8);
           if (++s == (uint32_t)kStages) {
             s = 0;
             ph ^= 1u;
           }
-          tpar ^= 1u << buf;
-          if (++buf == (uint32_t)kAccBufs) buf = 0;
-        }
-        if (!ok) {
-          raise_abort();
-          alive = false;
+          if (++buf == (uint32_t)kAccBufs) {
+            buf = 0;
+            aph ^= 1u;
+          }
         }
       }
     }
   } else if (warp >= kEpiWarp0) {
     // ------------------------------ promotion + epilogue ------------------------------
-    const int pw = warp - kEpiWarp0;
-    const int q = warp & 3;      // TMEM lane quadrant this warp may read
-    const int cgrp = pw >> 2;    // column group: columns cgrp*kEpiCols .. of the tile
+    // A thread that sees the abort flag keeps walking the same loops (without waiting or touching TMEM) so
+    // that the named barrier below always collects all kEpiThreads arrivals.
+    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
+    const int cgrp = (warp - kEpiWarp0) >> 2;   // column group: columns cgrp*kEpiCols .. of the tile
+    constexpr int kPiecesMax = kEpiCols / 32;
+    const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
     const int row_in_tile = q * 32 + lane;
-    const uint32_t lane0 = lane == 0 ? 1u : 0u;
     const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
                             (reinterpret_cast<uintptr_t>(p.a_s) & 15u) == 0;
-    // (a pair: buffers are handed back on the leader's barrier, through the cluster's shared-memory window)
-    const uint32_t bar_tfull0 = ptx::smem_u32(&ctl->tmem_full[0]);
-    const uint32_t bar_tempty0 = kPair ? ptx::mapa(ptx::smem_u32(&ctl->tmem_empty[0]), 0) : ptx::smem_u32(&ctl->tmem_empty[0]);
+    const uint32_t bar_tfull0 = ptx::smem_u32(&ctl->tmem_full[0]), bar_tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
     const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + cgrp * kEpiCols;
-    const uint32_t strip0 = ptx::smem_u32(&ctl->b_strip[pw][0][0][0]);
-    constexpr uint32_t kStripBytes = 2 * kBChunk * 4;  // one buffer of the strip: two weight blocks x kBChunk slabs
-    const uint32_t stage_q = ptx::smem_u32(out_stage) + q * Cfg::kOutGroups * kGroupBytes;  // this quadrant's staging
-    uint32_t par[kAccBufs];
-#pragma unroll
-    for (int b = 0; b < kAccBufs; ++b) par[b] = 0;
+    uint32_t buf = 0, aph = 0;
     bool alive = true;
-#ifdef SGLB_TRACE
-    int tslab = 0;  // slabs this warp has promoted (development trace, first promotion warp's lane 0 only)
-#define SGLB_TN ((pw == 0 && lane == 0) ? tslab++ : -1)
-#else
-#define SGLB_TN (-1)
-#endif
-
-    // what a promotion warp needs to know about a unit
-    struct Hdr {
-      int m_tile, n_tile, e, kb_begin, kb_stop, slot;
-      bool split, work;
-    };
-    auto header = [&](int u) {
-      Hdr h;
+    for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
       const Unit un = decode_unit<kGrouped>(p, u);
-      tile_coord(un.tile, tiles_m, tiles_n, p.group_m, h.m_tile, h.n_tile);
-      if (kPair) h.m_tile = 2 * h.m_tile + (int)crank;
-      h.kb_begin = un.kb_begin, h.kb_stop = un.kb_stop, h.slot = un.slot, h.split = un.split;
-      h.work = un.kb_begin < un.kb_stop;  // (an empty piece of a stream-K run: skipped by every role)
-      h.e = 0;
-      if (kGrouped) h.e = p.expert_ids[h.m_tile];
-      return h;
-    };
-    // activation scales of slabs kb .. kb+3 of one row (zero past the last slab)
-    auto load_a4 = [&](const float* a_row, int kb) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (vec_scales && kb + 3 < kb_total && (kb & 3) == 0) {
-        v = __ldg(reinterpret_cast<const float4*>(a_row + kb));
-      } else {
-        if (kb + 0 < kb_total) v.x = __ldg(a_row + (int64_t)(kb + 0) * p.as_stride_k);
-        if (kb + 1 < kb_total) v.y = __ldg(a_row + (int64_t)(kb + 1) * p.as_stride_k);
-        if (kb + 2 < kb_total) v.z = __ldg(a_row + (int64_t)(kb + 2) * p.as_stride_k);
-        if (kb + 3 < kb_total) v.w = __ldg(a_row + (int64_t)(kb + 3) * p.as_stride_k);
-      }
-      return v;
-    };
-    auto a_row_of = [&](const Hdr& h) {  // rows past M read a valid row; never stored
-      const int64_t row = (int64_t)h.m_tile * BM + row_in_tile;
-      return p.a_s + (row < rows ? row : rows - 1) * p.as_stride_m;
-    };
-    // weight-block scales (uniform across a warp: at most two 128-wide blocks per tile, one value per slab each)
-    auto b_rows_of = [&](const Hdr& h, const float*& r0, const float*& r1) {
-      const int nb_tile = min(h.n_tile * BN / kScaleBlockN, p.nb_total - 1);
-      r0 = p.b_s + ((int64_t)h.e * p.nb_total + nb_tile) * kb_total;
-      r1 = p.b_s + ((int64_t)h.e * p.nb_total + min(nb_tile + 1, p.nb_total - 1)) * kb_total;
-    };
-    // lane l fetches slabs kb0 + l and kb0 + 32 + l of both blocks (clamped: values past the last slab are unused)
-    auto fetch_b = [&](const float* r0, const float* r1, int kb0, float (&v)[4]) {
-      const int k0 = min(kb0 + lane, kb_total - 1), k1 = min(kb0 + 32 + lane, kb_total - 1);
-      v[0] = __ldg(r0 + k0), v[1] = __ldg(r0 + k1), v[2] = __ldg(r1 + k0), v[3] = __ldg(r1 + k1);
-    };
-    auto store_b = [&](uint32_t strip, const float (&v)[4]) {
-      __syncwarp();  // every lane is done reading what the buffer held
-      ptx::sts_f32(strip + lane * 4, v[0]);
-      ptx::sts_f32(strip + (32 + lane) * 4, v[1]);
-      ptx::sts_f32(strip + (kBChunk + lane) * 4, v[2]);
-      ptx::sts_f32(strip + (kBChunk + 32 + lane) * 4, v[3]);
-      __syncwarp();
-    };
-
-    // The scales a unit starts with (its first four activation scales, its first chunk of weight-block scales)
-    // are requested one unit ahead, before the previous unit's epilogue, and so arrive under it.
-    float4 a_first = make_float4(0.f, 0.f, 0.f, 0.f);
-    float bv[4] = {0.f, 0.f, 0.f, 0.f};
-    auto prefetch = [&](const Hdr& h) {
-      if (!h.work || h.e < 0) return;
-      const float *r0, *r1;
-      b_rows_of(h, r0, r1);
-      fetch_b(r0, r1, h.kb_begin, bv);
-      a_first = load_a4(a_row_of(h), h.kb_begin);
-    };
-
-    // (with the 192-wide tile the registers do not stretch to carrying them across the epilogue: its units fetch
-    // their first scales when they start, which their many slabs amortise)
-    constexpr bool kLookahead = SGLB_LOOKAHEAD_ALL || BN < 192;
-    int u = unit0;
-    bool have = u < num_units;
-    Hdr h{};
-    if (have) {
-      h = header(u);
-      if (kLookahead) prefetch(h);
-    }
-    uint32_t cb = 0;  // which half of the strip the next chunk of weight-block scales goes to
-    while (have) {
-      const int64_t row = (int64_t)h.m_tile * BM + row_in_tile;
-      const int n0 = h.n_tile * BN + cgrp * kEpiCols;                  // first of this warp's columns
-      const int n_end = (int)min((int64_t)h.n_tile * BN + BN, p.N);    // one past the tile's last valid column
+      const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
+      if (kb_begin >= kb_stop) continue;  // (an empty second piece of a stream-K run; uniform over the CTA)
+      int m_tile, n_tile;
+      tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
+      const int64_t row = (int64_t)m_tile * BM + row_in_tile;
+      const int n0 = n_tile * BN + cgrp * kEpiCols;            // first of this warp's columns
+      const int n_end = (int)min((int64_t)n_tile * BN + BN, p.N);  // one past the tile's last valid column
+      int e = 0;
+      if (kGrouped) e = p.expert_ids[m_tile];
       float acc[kEpiCols];
 #pragma unroll
       for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
-      if (h.work && h.e >= 0 && alive) {
-        if (!kLookahead) prefetch(h);
-        const float* a_row = a_row_of(h);
-        // A 32-column piece never straddle a weight block; a piece wholly past N is clamped to the last block.
-        const int nb_tile = min(h.n_tile * BN / kScaleBlockN, p.nb_total - 1);
-        uint32_t poff[kPieces];
+      if (e >= 0) {
+        // Activation scales live in registers: per group of four slabs a thread loads the four scales of its row,
+        // and the load for the next group is issued before the current group is promoted, a few thousand cycles
+        // ahead of its use.  The weight-block scales (uniform across a warp: at most two 128-wide blocks per
+        // tile, one value per slab each) are staged by every warp for itself, in its own strip of shared memory,
+        // once per unit: no barrier between warps.  (Staging both kinds for the whole CTA cost two CTA-wide
+        // barriers per group of slabs and kept the eight promotion warps in lock step.)
+        // A 32-column piece never straddles a weight block; a piece wholly past N is clamped to the last block.
+        const int nb_tile = min(n_tile * BN / kScaleBlockN, p.nb_total - 1);
+        bool piece_in_blk1[kPiecesMax];
 #pragma unroll
-        for (int i = 0; i < kPieces; ++i)
-          poff[i] = (BN != kScaleBlockN && min((n0 + 32 * i) / kScaleBlockN, p.nb_total - 1) != nb_tile) ? kBChunk * 4 : 0;
-        uint32_t b_base = strip0 + cb * kStripBytes;
-        store_b(b_base, bv);
-        float4 a_cur = a_first;
-        const int n_slabs = h.kb_stop - h.kb_begin;
-        const bool active = kGrouped || (int64_t)h.m_tile * BM + q * 32 < rows;
-        int g = 0;
-        while (g < n_slabs && alive) {
-          const int chunk_end = min(n_slabs, g + kBChunk);  // (g is a multiple of kBChunk here)
-          const bool more = chunk_end < n_slabs;
-          if (more) {  // (K beyond 8192: the next 64 slabs' weight-block scales, fetched a chunk ahead)
-            const float *b_row0, *b_row1;
-            b_rows_of(h, b_row0, b_row1);
-            fetch_b(b_row0, b_row1, h.kb_begin + chunk_end, bv);
+        for (int i = 0; i < kPiecesMax; ++i)
+          piece_in_blk1[i] = min((n0 + 32 * i) / kScaleBlockN, p.nb_total - 1) != nb_tile;
+        const float* a_row = p.a_s + min(row, rows - 1) * p.as_stride_m;  // rows past M read a valid row; never stored
+        const float* b_row0 = p.b_s + ((int64_t)e * p.nb_total + nb_tile) * kb_total;
+        const float* b_row1 = p.b_s + ((int64_t)e * p.nb_total + min(nb_tile + 1, p.nb_total - 1)) * kb_total;
+        float* b_strip = &ctl->b_stage[warp - kEpiWarp0][0][0];
+        auto stage_b = [&](int kb0) {  // weight-block scales of slabs kb0 .. kb0 + kBChunk - 1
+          __syncwarp();
+          for (int i = lane; i < kBChunk; i += 32) {
+            const int kb = kb0 + i;
+            b_strip[i] = kb < kb_stop ? __ldg(b_row0 + kb) : 0.f;
+            b_strip[kBChunk + i] = kb < kb_stop ? __ldg(b_row1 + kb) : 0.f;
           }
-          uint32_t b_addr = b_base;
-          for (; g + 4 <= chunk_end; g += 4, b_addr += 16) {
-            const float4 a_nxt = load_a4(a_row, h.kb_begin + g + 4);
-            // (the weight-block scales are read slab by slab: holding a group's worth in registers spills)
-            float bsc[kPieces];
-#define SGLB_SLAB(J, A_SC)                                                                                          \
-  {                                                                                                                 \
-    _Pragma("unroll") for (int i = 0; i < kPieces; ++i) bsc[i] = ptx::lds_f32(b_addr + poff[i] + 4 * (J));          \
-    alive = promote_slab<Cfg, (J) % kAccBufs>(bar_tfull0, bar_tempty0, taddr0, par, lane0, active, A_SC, bsc, acc,  \
-                                              abort_flag, probes, SGLB_TN);                                         \
-  }
-            SGLB_SLAB(0, a_cur.x)
-            if (alive) SGLB_SLAB(1, a_cur.y)
-            if (alive) SGLB_SLAB(2, a_cur.z)
-            if (alive) SGLB_SLAB(3, a_cur.w)
-            if (!alive) break;
-            a_cur = a_nxt;
+          __syncwarp();
+        };
+        auto load_a4 = [&](int kb) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (vec_scales && kb + 3 < kb_total && (kb & 3) == 0) {
+            v = __ldg(reinterpret_cast<const float4*>(a_row + kb));
+          } else {
+            if (kb + 0 < kb_total) v.x = __ldg(a_row + (int64_t)(kb + 0) * p.as_stride_k);
+            if (kb + 1 < kb_total) v.y = __ldg(a_row + (int64_t)(kb + 1) * p.as_stride_k);
+            if (kb + 2 < kb_total) v.z = __ldg(a_row + (int64_t)(kb + 2) * p.as_stride_k);
+            if (kb + 3 < kb_total) v.w = __ldg(a_row + (int64_t)(kb + 3) * p.as_stride_k);
           }
-          if (alive && g < chunk_end) {
-            // one to three trailing slabs (only a unit's last group can be short)
-            const int rem = chunk_end - g;
-            float bsc[kPieces];
-            SGLB_SLAB(0, a_cur.x)
-            if (alive && rem > 1) SGLB_SLAB(1, a_cur.y)
-            if (alive && rem > 2) SGLB_SLAB(2, a_cur.z)
-#undef SGLB_SLAB
-            g = chunk_end;
+          return v;
+        };
+        float4 a_cur = load_a4(kb_begin), a_nxt = a_cur;
+        const int n_slabs = kb_stop - kb_begin;
+        uint32_t b_addr = 0;
+        for (int g = 0; g < n_slabs; ++g) {
+          const int j = g & 3;
+          if ((g & (kBChunk - 1)) == 0) {
+            stage_b(kb_begin + g);
+            b_addr = ptx::smem_u32(b_strip);
           }
-          if (more && alive) {
-            cb ^= 1u;
-            b_base = strip0 + cb * kStripBytes;
-            store_b(b_base, bv);
+          if (j == 0) {
+            if (g > 0) a_cur = a_nxt;
+            if (g + 4 < n_slabs) a_nxt = load_a4(kb_begin + g + 4);
+          }
+          const float a_sc = j == 0 ? a_cur.x : j == 1 ? a_cur.y : j == 2 ? a_cur.z : a_cur.w;
+          const float sc0 = a_sc * ptx::lds_f32(b_addr), sc1 = a_sc * ptx::lds_f32(b_addr + kBChunk * 4);
+          b_addr += 4;
+          // (the 32 lanes probe the same word in the same instruction, so the outcome is uniform across the
+          // warp, as the warp-wide tcgen05.ld below requires)
+          if (alive && !SGLB_WAIT(bar_tfull0 + buf * 8, aph)) {
+            *abort_flag = 1;
+            alive = false;
+          }
+          if (alive) {
+            ptx::tc_fence_after();
+            const uint32_t taddr = taddr0 + buf * kAccStride;
+            // All 32-column pieces of the slab are requested before the one wait (tcgen05.wait::ld waits for
+            // every outstanding load of the thread): one TMEM round trip per slab sits on the hand-off chain
+            // MMA -> commit -> promotion -> release.  The buffer goes back to the MMA thread as soon as the
+            // pieces are in registers.
+            uint32_t r[kPiecesMax][32];
+#pragma unroll
+            for (int i = 0; i < kPiecesMax; ++i) ptx::tmem_ld_32x32(taddr + 32 * i, r[i]);
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before();
+            ptx::mbar_arrive_if(bar_tempty0 + buf * 8, lane == 0);
+#pragma unroll
+            for (int i = 0; i < kPiecesMax; ++i) {
+              const float sc = piece_in_blk1[i] ? sc1 : sc0;
+#if SGLB_FMA2
+              // two columns per instruction (packed float32 FMA: the same two IEEE operations): half the issue slots
+#pragma unroll
+              for (int jj = 0; jj < 32; jj += 2) ptx::fma2(acc[32 * i + jj], acc[32 * i + jj + 1], r[i][jj], r[i][jj + 1], sc);
+#else
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj) acc[32 * i + jj] = fmaf(__uint_as_float(r[i][jj]), sc, acc[32 * i + jj]);
+#endif
+            }
+          }
+          if (++buf == (uint32_t)kAccBufs) {
+            buf = 0;
+            aph ^= 1u;
           }
         }
-        if (!alive) raise_abort();
-        cb ^= 1u;
       }
-      // the next unit's header and first scales, requested before this unit's epilogue
-      const Hdr cur = h;
-      u += unit_step;
-      have = u < num_units;
-      if (have) {
-        h = header(u);
-        if (alive && kLookahead) prefetch(h);
-      }
-      if (!cur.work) continue;
       // ---- store ----
-      if (cur.split) {
+      if (un.split) {
         // this unit's float32 partial sums, tile-local layout; a second kernel adds the units of a tile in a
         // fixed order, adds the bias and rounds once
         if (alive && row < rows) {  // (rows past M are never read back)
-          // (a pair: the two CTAs' 128-row blocks of a unit follow each other)
           // Layout of a block: with full tiles [column / 4][row][4], so that the 32 lanes of a warp (32 consecutive
           // rows) write 512 contiguous bytes per store; with a handful of rows (weight streaming) [row][BN], where
           // a row's columns stay together.  The reduction kernel reads it the same way.
-          const int64_t blk = kPair ? (int64_t)cur.slot * 2 + crank : (int64_t)cur.slot;
           if (p.partial_rowmajor) {
-            float* dst = p.partial + blk * (BM * BN) + row_in_tile * BN + cgrp * kEpiCols;
+            float* dst = p.partial + (int64_t)un.slot * (BM * BN) + row_in_tile * BN + cgrp * kEpiCols;
 #pragma unroll
             for (int j = 0; j < kEpiCols / 4; ++j)
               *reinterpret_cast<float4*>(dst + j * 4) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
           } else {
-            float* dst = p.partial + blk * (BM * BN) + ((int64_t)(cgrp * kEpiCols / 4) * BM + row_in_tile) * 4;
+            float* dst = p.partial + (int64_t)un.slot * (BM * BN) + ((int64_t)(cgrp * kEpiCols / 4) * BM + row_in_tile) * 4;
 #pragma unroll
             for (int j = 0; j < kEpiCols / 4; ++j)
               *reinterpret_cast<float4*>(dst + (int64_t)j * BM * 4) =
@@ -701,18 +502,16 @@ __global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
         continue;
       }
       if (p.tma_out) {
-        // Rows of C are contiguous: round to the output type and park the 32 rows x BN columns of this TMEM lane
-        // quadrant in shared memory (per 64 columns a block of 128-byte rows, 16-byte chunks XOR-swizzled by the
-        // row so that the lanes of a store spread over all banks); the quadrant's two warps each write their half
-        // of the columns, meet at a barrier of their own (64 threads, same scheduler), and one lane hands the
-        // blocks to the TMA engine, which clips them to the tensor.  The stores drain while the next tile is being
-        // promoted; their source is reclaimed at the next epilogue.  No barrier spans the quadrants.
-        // (A warp whose wait expired still joins both barriers; only the data movement is skipped.)
-        const bool issuer = cgrp == 0 && lane == 0;
+        // Rows of C are contiguous: round to the output type, park the warp's 32 x 64 block in shared memory
+        // (128-byte rows, 16-byte chunks XOR-swizzled by the row so that the 32 lanes of a store spread over
+        // all banks) and let one thread of the column group hand the 128 x 64 block to the TMA engine, which
+        // clips it to the tensor.  The store drains while the next tile is being promoted; its source is
+        // reclaimed at the next epilogue.
+        const bool issuer = (ep_tid == 0);
         if (issuer) ptx::tma_store_wait_read();
-        ptx::bar_sync(2 + q, 32 * Cfg::kColGroups);
-        const bool rows_in = (int64_t)cur.m_tile * BM + q * 32 < rows;
-        if (alive && n0 < n_end && rows_in) {
+        // (a warp whose wait expired still joins both barriers; only the data movement is skipped)
+        asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+        if (alive && n0 < n_end) {
           if (p.bias != nullptr) {
             // (tile columns past N are clipped by the store; their bias reads are clamped to stay in bounds)
             const uint16_t* bsrc = static_cast<const uint16_t*>(p.bias);
@@ -727,39 +526,39 @@ __global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
           if (p.out_fp16) {
 #pragma unroll
             for (int j = 0; j < kEpiCols / 2; ++j) {
-              const __half2 hh = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
-              packed[j] = *reinterpret_cast<const uint32_t*>(&hh);
+              const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+              packed[j] = *reinterpret_cast<const uint32_t*>(&h);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < kEpiCols / 2; ++j) {
-              const __nv_bfloat162 hh = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-              packed[j] = *reinterpret_cast<const uint32_t*>(&hh);
+              const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+              packed[j] = *reinterpret_cast<const uint32_t*>(&h);
             }
           }
-          const uint32_t dst0 = stage_q + lane * 128;
-          const uint32_t swz = (uint32_t)(lane & 7);
+          const uint32_t stage0 = ptx::smem_u32(out_stage) + row_in_tile * 128;
+          const uint32_t swz = (uint32_t)(row_in_tile & 7);
 #pragma unroll
           for (int j = 0; j < kEpiCols / 8; ++j) {
             const int col = cgrp * kEpiCols + j * 8;  // within the tile: 64-column group col / 64, 16-byte chunk (col % 64) / 8
-            ptx::sts_128(dst0 + (col >> 6) * kGroupBytes + ((((uint32_t)(col & 63) >> 3) ^ swz) << 4),
+            ptx::sts_128(stage0 + (col >> 6) * kOutGroupBytes + ((((col & 63) >> 3) ^ swz) << 4),
                          make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]));
           }
           ptx::fence_async_smem();
         }
-        ptx::bar_sync(2 + q, 32 * Cfg::kColGroups);
-        if (issuer && alive && rows_in) {
+        asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+        if (issuer && alive) {
           const CUtensorMap* cmap = &map_c;
-          int out_row0 = cur.m_tile * BM;
+          int out_row0 = m_tile * BM;
           if (p.push_maps != nullptr) {
             const int owner = out_row0 / p.push_rows_per_owner;
             cmap = p.push_maps + owner;
             out_row0 += (p.push_rank - owner) * p.push_rows_per_owner;
           }
 #pragma unroll
-          for (int g = 0; g < Cfg::kOutGroups; ++g) {
-            if (cur.n_tile * BN + g * 64 < n_end)
-              ptx::tma_store_2d(cmap, stage_q + g * kGroupBytes, cur.n_tile * BN + g * 64, out_row0 + q * 32);
+          for (int g = 0; g < kOutGroups; ++g) {
+            if (n_tile * BN + g * 64 < n_end)
+              ptx::tma_store_2d(cmap, ptx::smem_u32(out_stage) + g * kOutGroupBytes, n_tile * BN + g * 64, out_row0);
           }
           ptx::tma_store_commit();
         }
@@ -787,21 +586,17 @@ __global__ void __launch_bounds__((TileCfg<BN_, kPair>::kThreads), 1)
         }
       }
     }
-    // this warp's tile stores: sources stay valid until read; tiles pushed to other GPUs have landed before the
-    // kernel counts as finished
-    if (cgrp == 0 && lane == 0) {
-      if (p.push_maps != nullptr)
-        ptx::tma_store_wait_all();
-      else
-        ptx::tma_store_wait_read();
-    }
   }
 
   // ------------------------------ teardown ------------------------------
+  if (threadIdx.x == kEpiWarp0 * 32) {
+    if (p.push_maps != nullptr)
+      ptx::tma_store_wait_all();  // tiles pushed to other GPUs have landed before the kernel counts as finished
+    else
+      ptx::tma_store_wait_read();  // sources stay valid until read
+  }
   ptx::tc_fence_before();
   __syncthreads();
-  // (a pair: neither CTA releases shared or tensor memory that its peer's instructions may still touch)
-  if (kPair) ptx::cluster_sync_all();
   if (ctl->abort_flag != 0 && threadIdx.x == 0) {
     atomicExch(&g_gemm_status, 1);
     // give TMA copies that may still be in flight time to land before the CTA's shared memory is released
@@ -908,9 +703,6 @@ __global__ void __launch_bounds__(256)
   for (int j = 0; j < 8; ++j) o[j] = ElemTraits<OutT>::from_f32(acc[j]);
   *reinterpret_cast<uint4*>(C + row * N + col) = raw;
 }
-
-// Tile width of a problem: the 128-wide tile (four accumulator buffers) where K is short.
-static int choose_bn(int64_t K) { return (K + BK - 1) / BK <= SGLB_SHORT_K ? 128 : 192; }
 
 // How a dense problem is cut into units.
 //  * Few tiles, long K, M <= 128 (weight streaming): stream-K over all SMs while the partial sums cost less than a
@@ -1063,7 +855,7 @@ static int get_tensor_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2
   return SGLB200_OK;
 }
 
-// Output tensor [rows][N] of 2-byte elements, box = 64 columns x 32 rows, 128-byte swizzle (matches the
+// Output tensor [rows][N] of 2-byte elements, box = 64 columns x 128 rows, 128-byte swizzle (matches the
 // staging layout written by the epilogue).
 static int get_out_map(const void* ptr, uint64_t N, uint64_t rows, int out_fp16, CUtensorMap* out) {
   static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
@@ -1077,7 +869,7 @@ static int get_out_map(const void* ptr, uint64_t N, uint64_t rows, int out_fp16,
   if (enc == nullptr) return fail(SGLB200_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {N, rows};
   cuuint64_t strides[1] = {N * 2};
-  cuuint32_t box[2] = {64u, 32u};
+  cuuint32_t box[2] = {64u, (cuuint32_t)BM};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, out_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1101,27 +893,40 @@ static int choose_group_m(int64_t rows, int64_t K, int tile_rows = BM) {
   return (int)((tiles_m + groups - 1) / groups);
 }
 
-// How a dense problem runs: tile width, single CTAs or CTA pairs, and the cut into units.
-#ifndef SGLB_PAIR_MIN_M
-#define SGLB_PAIR_MIN_M 0    // from this many rows on, pairs of CTAs share 256-row tiles (0 = never)
+// Tile width of a dense problem (TileCfg).  Where the 192-wide tiling streams weights (stream-K, split tiles) or
+// makes several waves, it wins: fewer tiles, fewer bytes per FLOP, and at large M the 128-wide tile runs at about
+// 0.85 of its rate.  Where one wave of 192-wide tiles leaves SMs idle and K is not split, the 128-wide tile's
+// extra tiles fill them.  Compared as waves x tile width, the 128-wide tile charged 150 instead of 128.
+#ifndef SGLB_FORCE_BN
+#define SGLB_FORCE_BN 0  // 128 or 192: one tile width for everything (measurements)
 #endif
-#ifndef SGLB_PAIR_BN
-#define SGLB_PAIR_BN 128     // tile width of a pair whatever K is (0 = as a single CTA would choose)
-#endif
+static int choose_bn(int64_t M, int64_t N, int64_t K) {
+  if (SGLB_FORCE_BN) return SGLB_FORCE_BN;
+  const int sms = sm_count();
+  const UnitPlan p192 = plan_units(M, N, K, 192, BM, sms);
+  if (p192.scratch_blocks() > 0) return 192;
+  const int64_t tiles_m = (M + BM - 1) / BM;
+  const int64_t waves192 = (tiles_m * ((N + 191) / 192) + sms - 1) / sms;
+  const int64_t waves128 = (tiles_m * ((N + 127) / 128) + sms - 1) / sms;
+  return waves128 * 150 < waves192 * 192 ? 128 : 192;
+}
+// The expert-grouped form: rows per expert are not known on the host; with a handful of routed rows (decode) the
+// 128-wide tile spreads the few row blocks over more SMs, otherwise the 192-wide tile is ahead by 5-10 %.
+static int choose_bn_grouped(int64_t numel) {
+  if (SGLB_FORCE_BN) return SGLB_FORCE_BN;
+  return numel <= 64 ? 128 : 192;
+}
+
+// How a dense problem runs: tile width and the cut into units.
 struct DensePlan {
   int bn;
-  bool pair;
-  int tile_rows, workers;
   UnitPlan units;
-  int64_t scratch_bytes() const { return units.scratch_blocks() * (int64_t)tile_rows * bn * (int64_t)sizeof(float); }
+  int64_t scratch_bytes() const { return units.scratch_blocks() * (int64_t)BM * bn * (int64_t)sizeof(float); }
 };
 static DensePlan plan_dense(int64_t M, int64_t N, int64_t K) {
   DensePlan d;
-  d.pair = SGLB_PAIR_MIN_M > 0 && M >= SGLB_PAIR_MIN_M;
-  d.bn = d.pair && SGLB_PAIR_BN > 0 ? SGLB_PAIR_BN : choose_bn(K);
-  d.tile_rows = d.pair ? 2 * BM : BM;
-  d.workers = d.pair ? sm_count() / 2 : sm_count();
-  d.units = plan_units(M, N, K, d.bn, d.tile_rows, d.workers);
+  d.bn = choose_bn(M, N, K);
+  d.units = plan_units(M, N, K, d.bn, BM, sm_count());
   return d;
 }
 
@@ -1132,56 +937,36 @@ static size_t gemm_smem_bytes() {
   return (size_t)Cfg::kStages * Cfg::kStageBytes + Cfg::kOutBytes + sizeof(SharedCtl<Cfg>) + 1024;
 }
 
-template <bool kGrouped, int BN, bool kPair = false>
+template <bool kGrouped, int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const GemmParams& p,
                        int64_t max_units, cudaStream_t st, int sm_margin = 0) {
-  const size_t smem = gemm_smem_bytes<TileCfg<BN, kPair>>();
+  const size_t smem = gemm_smem_bytes<TileCfg<BN>>();
   static thread_local bool attr_set[64] = {false};  // the opt-in is per function and per device
   int dev = 0;
   SGLB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    SGLB_CUDA(cudaFuncSetAttribute(fp8_blockscale_gemm_kernel<kGrouped, BN, kPair>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SGLB_CUDA(cudaFuncSetAttribute(fp8_blockscale_gemm_kernel<kGrouped, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   int sms = sm_count() - sm_margin;  // SMs left free run a concurrent kernel (the reduce-and-gather of an earlier chunk)
   if (sms < 1) sms = 1;
-  if (!kPair) {
-    const unsigned grid = (unsigned)(max_units < sms ? max_units : sms);
-    fp8_blockscale_gemm_kernel<kGrouped, BN, kPair><<<grid, TileCfg<BN, kPair>::kThreads, smem, st>>>(ma, mb, mc, p);
-    SGLB_CUDA(cudaGetLastError());
-    return SGLB200_OK;
-  }
-  // pairs: a cluster of two CTAs per unit in flight (one cluster per two SMs)
-  int64_t clusters = sms / 2;
-  if (clusters < 1) clusters = 1;
-  if (max_units < clusters) clusters = max_units;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-  cfg.blockDim = dim3(TileCfg<BN, kPair>::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  SGLB_CUDA(cudaLaunchKernelEx(&cfg, fp8_blockscale_gemm_kernel<kGrouped, BN, kPair>, ma, mb, mc, p));
+  const unsigned grid = (unsigned)(max_units < sms ? max_units : sms);
+  fp8_blockscale_gemm_kernel<kGrouped, BN><<<grid, kGemmThreads, smem, st>>>(ma, mb, mc, p);
+  SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
 }
 
-template <int BN, bool kPair>
+template <int BN>
 static int dense_mm(const DensePlan& dp, const void* A, const void* B, const float* a_s, const float* b_s, void* C,
                     const void* bias, int64_t M, int64_t N, int64_t K, int64_t as_stride_m, int64_t as_stride_k,
                     int out_dtype, void* workspace, int64_t workspace_bytes, cudaStream_t st) {
-  constexpr int kTileRows = kPair ? 2 * BM : BM;
+  constexpr int kTileRows = BM;
   CUtensorMap ma, mb;
   int rc = get_tensor_map(A, (uint64_t)K, (uint64_t)M, 1, BM, 2, &ma);
   if (rc) return rc;
   // B is addressed as [1][N][K] so that dense and grouped kernels share the 3-D load
-  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, TileCfg<BN, kPair>::kBRows, 3, &mb);
+  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, BN, 3, &mb);
   if (rc) return rc;
   GemmParams p{};
   p.a_s = a_s, p.b_s = b_s, p.C = C, p.bias = bias;
@@ -1207,8 +992,7 @@ static int dense_mm(const DensePlan& dp, const void* A, const void* B, const flo
     rc = get_out_map(C, (uint64_t)N, (uint64_t)M, out_dtype, &mc);
     if (rc) return rc;
   }
-  rc = launch_gemm<false, BN, kPair>(ma, mb, mc, p,
-                                     pl.sk_share > 0 ? pl.sk_ctas : pl.full_units + pl.split_tiles * pl.splits, st);
+  rc = launch_gemm<false, BN>(ma, mb, mc, p, pl.sk_share > 0 ? pl.sk_ctas : pl.full_units + pl.split_tiles * pl.splits, st);
   if (rc != SGLB200_OK || pl.scratch_blocks() == 0) return rc;
   const int tiles_m = (int)((M + kTileRows - 1) / kTileRows);
   const unsigned ygrid = (unsigned)((kTileRows * BN / 8 + 255) / 256);
@@ -1270,7 +1054,7 @@ static int grouped_mm(const void* A, const float* a_s, const void* B, const floa
     if (rc) return rc;
   }
   const int64_t tiles = ((max_rows + BM - 1) / BM) * p.tiles_n;
-  return launch_gemm<true, BN, false>(ma, mb, mc, p, tiles, st);
+  return launch_gemm<true, BN>(ma, mb, mc, p, tiles, st);
 }
 
 }  // namespace sglb200
@@ -1288,15 +1072,6 @@ extern "C" int sglb200_gemm_status(void) {
   if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
   return v;
 }
-
-#ifdef SGLB_TRACE
-extern "C" int sglb200_debug_trace(void* out, int64_t bytes) {
-  if (bytes > (int64_t)sizeof(long long) * 2 * kTraceRoles * kTraceSlabs * kTraceEvents)
-    bytes = (int64_t)sizeof(long long) * 2 * kTraceRoles * kTraceSlabs * kTraceEvents;
-  SGLB_CUDA(cudaMemcpyFromSymbol(out, g_trace, (size_t)bytes));
-  return SGLB200_OK;
-}
-#endif
 
 extern "C" void sglb200_gemm_set_wait_probes(uint32_t probes) { g_wait_probes = probes == 0 ? ptx::kProbeLimit : probes; }
 
@@ -1321,17 +1096,11 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   SGLB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "fp8_blockwise_scaled_mm: dimension too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const DensePlan dp = plan_dense(M, N, K);
-  if (dp.bn == 128 && dp.pair)
-    return dense_mm<128, true>(dp, A, B, a_s, b_s, C, bias, M, N, K, as_stride_m, as_stride_k, out_dtype, workspace,
-                               workspace_bytes, st);
   if (dp.bn == 128)
-    return dense_mm<128, false>(dp, A, B, a_s, b_s, C, bias, M, N, K, as_stride_m, as_stride_k, out_dtype, workspace,
-                                workspace_bytes, st);
-  if (dp.pair)
-    return dense_mm<192, true>(dp, A, B, a_s, b_s, C, bias, M, N, K, as_stride_m, as_stride_k, out_dtype, workspace,
-                               workspace_bytes, st);
-  return dense_mm<192, false>(dp, A, B, a_s, b_s, C, bias, M, N, K, as_stride_m, as_stride_k, out_dtype, workspace,
-                              workspace_bytes, st);
+    return dense_mm<128>(dp, A, B, a_s, b_s, C, bias, M, N, K, as_stride_m, as_stride_k, out_dtype, workspace,
+                         workspace_bytes, st);
+  return dense_mm<192>(dp, A, B, a_s, b_s, C, bias, M, N, K, as_stride_m, as_stride_k, out_dtype, workspace,
+                       workspace_bytes, st);
 }
 
 extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s, const void* B, const float* b_s,
@@ -1348,7 +1117,7 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   SGLB_REQUIRE(!scatter || sorted_token_ids, "grouped_mm: scatter mode needs sorted_token_ids");
   SGLB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C), "grouped_mm: A, B and C must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (choose_bn(K) == 128)
+  if (choose_bn_grouped(numel) == 128)
     return grouped_mm<128>(A, a_s, B, b_s, C, sorted_token_ids, expert_ids, num_rows_dev, row_weights, max_rows, numel,
                            num_experts, N, K, scatter, out_dtype, st);
   return grouped_mm<192>(A, a_s, B, b_s, C, sorted_token_ids, expert_ids, num_rows_dev, row_weights, max_rows, numel,
@@ -1404,15 +1173,15 @@ static int get_push_maps(void* const* stage_ptrs, int world, uint64_t N, uint64_
   return SGLB200_OK;
 }
 
-template <int BN, bool kPair>
+template <int BN>
 static int push_mm(const void* A, const void* B, const float* a_s, const float* b_s, void* const* stage_ptrs, int world,
                    int rank, int64_t M, int64_t N, int64_t K, int64_t as_stride_m, int64_t as_stride_k, int out_dtype,
                    int sm_margin, cudaStream_t st) {
-  constexpr int kTileRows = kPair ? 2 * BM : BM;
+  constexpr int kTileRows = BM;
   CUtensorMap ma, mb;
   int rc = get_tensor_map(A, (uint64_t)K, (uint64_t)M, 1, BM, 2, &ma);
   if (rc) return rc;
-  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, TileCfg<BN, kPair>::kBRows, 3, &mb);
+  rc = get_tensor_map(B, (uint64_t)K, (uint64_t)N, 1, BN, 3, &mb);
   if (rc) return rc;
   GemmParams p{};
   p.a_s = a_s, p.b_s = b_s, p.C = nullptr, p.bias = nullptr;
@@ -1436,7 +1205,7 @@ static int push_mm(const void* A, const void* B, const float* a_s, const float* 
   CUtensorMap mc = {};
   rc = get_out_map(stage_ptrs[rank], (uint64_t)N, (uint64_t)(rpo * world), out_dtype, &mc);  // unused by the stores; keeps map_c valid
   if (rc) return rc;
-  return launch_gemm<false, BN, kPair>(ma, mb, mc, p, tiles, st, sm_margin);
+  return launch_gemm<false, BN>(ma, mb, mc, p, tiles, st, sm_margin);
 }
 
 }  // namespace sglb200
@@ -1474,13 +1243,7 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B
   SGLB_REQUIRE(aligned16(A) && aligned16(B), "mm_push: A and B must be 16-byte aligned");
   SGLB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "mm_push: dimension too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const DensePlan dp = plan_dense(M, N, K);  // (tile shape only: a pushed tile is never split along K)
-#define SGLB_PUSH(BN_, PAIR_)                                                                                        \
-  return push_mm<BN_, PAIR_>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, \
-                             sm_margin, st)
-  if (dp.bn == 128 && dp.pair) SGLB_PUSH(128, true);
-  if (dp.bn == 128) SGLB_PUSH(128, false);
-  if (dp.pair) SGLB_PUSH(192, true);
-  SGLB_PUSH(192, false);
-#undef SGLB_PUSH
+  if (choose_bn(M, N, K) == 128)
+    return push_mm<128>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, sm_margin, st);
+  return push_mm<192>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, sm_margin, st);
 }

@@ -35,10 +35,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 // Bounded waits.  Each probe (mbarrier.try_wait with a time hint) may suspend the thread for up to `kProbeHintNs`
 // and resumes at once when the phase completes, so a waiting warp spends a couple of instructions per microsecond
 // instead of competing for issue slots with the warps that have work.
-#ifndef SGLB_PROBE_HINT_NS
-#define SGLB_PROBE_HINT_NS 4000
-#endif
-constexpr uint32_t kProbeHintNs = SGLB_PROBE_HINT_NS;
+constexpr uint32_t kProbeHintNs = 4000;
 constexpr uint32_t kProbeLimit = 1u << 22;  // default number of probes after which a wait gives up (seconds)
 constexpr uint32_t kProbesFast = 8, kProbesSlow = 64;
 constexpr uint32_t kProbesNone = 0xffffffffu;  // as a limit: give up without probing (exercises the give-up paths)
@@ -50,13 +47,7 @@ __device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity, uint32
       "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
       "mov.u32 n, 0;\n"
       "QUIET_LOOP:\n\t"
-#if defined(SGLB_PROBE_POLL)
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#elif SGLB_PROBE_HINT_NS > 0
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-#else
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
       "@p bra QUIET_DONE;\n\t"
       "add.u32 n, n, 1;\n\t"
       "setp.lt.u32 p, n, %4;\n\t"
@@ -88,11 +79,7 @@ __device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.u32 p, %1, 0;\n\t"
-#ifdef SGLB_RELAXED_ARRIVE
-      "@p mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar),
-#else
       "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar),
-#endif
       "r"(pred)
       : "memory");
 }
@@ -200,74 +187,6 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-
-// ---- CTA pairs (a cluster of two CTAs that share one tcgen05.mma.cta_group::2) ---------------------------
-// Each CTA fetches its own tiles; nothing here uses a cluster-wide (multicast) load.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// All threads of both CTAs (the hardware barrier of the cluster; every thread reaches it unconditionally).
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-}
-// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
-__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-// Arrive on an mbarrier of a CTA of the cluster (address from mapa) from the threads whose `pred` is set.
-__device__ __forceinline__ void mbar_arrive_cluster_if(uint32_t bar_cluster, uint32_t pred) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.u32 p, %1, 0;\n\t"
-      // (relaxed: the arrival only says "my tensor-memory reads are done", which tcgen05.wait::ld has already made
-      // true; a release at cluster scope would first wait for every earlier store of the thread, over a thousand
-      // clocks per slab)
-      "@p mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n\t}" ::"r"(bar_cluster),
-      "r"(pred)
-      : "memory");
-}
-__device__ __forceinline__ void st_cluster_u32(uint32_t addr_cluster, uint32_t v) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr_cluster), "r"(v) : "memory");
-}
-// TMA tile loads of a CTA pair: the data lands in THIS CTA's shared memory, the bytes are counted on the mbarrier
-// `bar_cluster` of the pair's leader (shared::cluster address).
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int c0, int c1,
-                                                 int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-// D[tmem of both CTAs] (+)= A[each CTA's own rows] * B[half of the columns from each CTA], issued by ONE thread of
-// the leader CTA; M = 256 over the pair.
-__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// One arrival on the mbarrier at this offset in BOTH CTAs of the pair when every tcgen05.mma issued so far by this
-// thread has finished (a signal, not a load).
-__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
-  const uint16_t mask = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
-               "h"(mask)
-               : "memory");
-}
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base_lane + i).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
