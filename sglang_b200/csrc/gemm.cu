@@ -59,9 +59,6 @@ constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 // (Measured: also polling the CTA's abort flag between runs of probes, so that one role's expiry ends the others'
 // waits early, cost 5 % of the large-M rate; each role sits out its own limit instead.)
 #define SGLB_WAIT(bar, parity) (p.wait_probes != ptx::kProbesNone && ptx::mbar_wait_quiet(bar, parity))
-#ifndef SGLB_LOOKAHEAD
-#define SGLB_LOOKAHEAD 0                   // first scales of a short unit requested before the previous unit's epilogue
-#endif
 #ifndef SGLB_FMA2
 #define SGLB_FMA2 1                        // promotion with packed float32 FMAs (two columns per instruction)
 #endif
@@ -388,11 +385,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       return v;
     };
-    // Units of at most 32 slabs (K up to 4096: the tiles whose epilogue weighs as much as their MMAs) get their first
-    // scales requested one unit ahead, before the previous unit's epilogue, so that the loads fly under it.
-    int pre_u = -1;
-    float4 a_pre = make_float4(0.f, 0.f, 0.f, 0.f);
-    float b_pre0 = 0.f, b_pre1 = 0.f;
+    // (Measured: requesting a short unit's first scales one unit ahead, before the previous unit's epilogue, moves
+    // dense shapes by -2..+6 % and costs the grouped form 4-8 %; not kept.)
     for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
       const Unit un = decode_unit<kGrouped>(p, u);
       const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
@@ -434,21 +428,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           __syncwarp();
         };
         auto load_a4 = [&](int kb) { return load_a4_row(a_row, kb); };
-        const bool have_pre = SGLB_LOOKAHEAD && pre_u == u;
-        float4 a_cur = have_pre ? a_pre : load_a4(kb_begin), a_nxt = a_cur;
+        float4 a_cur = load_a4(kb_begin), a_nxt = a_cur;
         const int n_slabs = kb_stop - kb_begin;
         uint32_t b_addr = 0;
         for (int g = 0; g < n_slabs; ++g) {
           const int j = g & 3;
           if ((g & (kBChunk - 1)) == 0) {
-            if (g == 0 && have_pre) {  // (all of this unit's slabs: lane l holds slab kb_begin + l)
-              __syncwarp();
-              b_strip[lane] = b_pre0;
-              b_strip[kBChunk + lane] = b_pre1;
-              __syncwarp();
-            } else {
-              stage_b(kb_begin + g);
-            }
+            stage_b(kb_begin + g);
             b_addr = ptx::smem_u32(b_strip);
           }
           if (j == 0) {
@@ -496,30 +482,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
-#if SGLB_LOOKAHEAD
-      pre_u = -1;
-      if (alive && u + (int)gridDim.x < num_units) {
-        const Unit un2 = decode_unit<kGrouped>(p, u + (int)gridDim.x);
-        const int ns2 = un2.kb_stop - un2.kb_begin;
-        if (ns2 > 0 && ns2 <= 32) {
-          int m2, n2;
-          tile_coord(un2.tile, tiles_m, tiles_n, p.group_m, m2, n2);
-          int e2 = 0;
-          if (kGrouped) e2 = p.expert_ids[m2];
-          if (e2 >= 0) {
-            const int64_t row2 = (int64_t)m2 * BM + row_in_tile;
-            const int nb2 = min(n2 * BN / kScaleBlockN, p.nb_total - 1);
-            const float* r0 = p.b_s + ((int64_t)e2 * p.nb_total + nb2) * kb_total;
-            const float* r1 = p.b_s + ((int64_t)e2 * p.nb_total + min(nb2 + 1, p.nb_total - 1)) * kb_total;
-            const int kbl = un2.kb_begin + lane;
-            b_pre0 = kbl < un2.kb_stop ? __ldg(r0 + kbl) : 0.f;
-            b_pre1 = kbl < un2.kb_stop ? __ldg(r1 + kbl) : 0.f;
-            a_pre = load_a4_row(p.a_s + min(row2, rows - 1) * p.as_stride_m, un2.kb_begin);
-            pre_u = u + (int)gridDim.x;
-          }
-        }
-      }
-#endif
       // ---- store ----
       if (un.split) {
         // this unit's float32 partial sums, tile-local layout; a second kernel adds the units of a tile in a
