@@ -518,7 +518,7 @@ def run_main(args, dist_ctx):
 
 # DRAM bytes (read + write) of the GEMM launches of one step of the default workload, from one ncu capture of
 # `bench.py --steps 1 --warmup 1 --sections main --cpu-baseline 0` (dram__bytes_read.sum + dram__bytes_write.sum
-# of the first six fp8_blockscale_gemm_kernel launches; profiles/gemm_dram_traffic_M4096.md).  Algorithmic bytes
+# of the first six fp8_blockscale_gemm_kernel launches).  Algorithmic bytes
 # of the same six launches: 1 706 MB (weights 583, activations 210, outputs 906, scales 7).
 _GEMM_DRAM_BYTES_PER_STEP_M4096 = {"fused_qkv_a": 49.2e6, "q_b": 187.5e6, "kv_b": 226.1e6, "o_proj": 503.1e6,
                                    "gate_up": 577.2e6, "down": 689.9e6}
@@ -554,7 +554,8 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--sections", default="main,moe,tp,sweep,hbm")
+    ap.add_argument("--sections", default="main,moe,tp,sweep,hbm",
+                    help="main is always run; moe = moe3 (config 3) + moe4 (config 4, skewed), tp, sweep, hbm")
     ap.add_argument("--cpu-baseline", type=int, default=1)
     ap.add_argument("--layers", default="", help="comma-separated subset of layer names (profiler captures only)")
     ap.add_argument("--m-tokens", type=int, default=M_TOKENS, help="smaller values are for profiler captures only")

@@ -352,8 +352,13 @@ def moe_layer_skewed(args, ctx, peaks):
     """128 experts, hidden 2048, moe_intermediate 768, top-8 softmax routing; the logits carry log(p_e) with
     p_e ~ rank^-1.2 over a seeded permutation of the experts.  Reports the layer time (max over ranks), this
     rank's own time and the spread of tokens per local expert, i.e. the load-imbalance tail.  With more than one
-    rank the whole layer (all experts) is first timed on every GPU by itself (`ms_1gpu_eager`)."""
+    rank the whole layer (all experts) is first timed on every GPU by itself (`ms_1gpu_eager`), then the
+    expert-parallel layer with the static block placement (`ms`), then with redundant copies of the hottest experts on
+    every rank and the other experts packed onto the ranks by load (`ms_redundant`: `srt/eplb`, eight copies per
+    rank, chosen from the routed-row counts of the batch itself summed over the ranks; a hot expert's rows are served
+    by the sender's own copy and never cross NVLink)."""
     from sglang_b200.srt.distributed import initialize_model_parallel
+    from sglang_b200.srt.eplb import ExpertLocationMetadata
     from sglang_b200.srt.layers.moe.fused_moe_triton.layer import FusedMoE
     from sglang_b200.srt.layers.moe.token_dispatcher import StandardTopKOutput
     from sglang_b200.srt.layers.moe.topk import fused_topk
@@ -361,39 +366,44 @@ def moe_layer_skewed(args, ctx, peaks):
     rank, world, dev = ctx
     E, H, I, topk = 128, 2048, 768, 8
     sizes = (32, 1024, 16384)
+    redundant_per_rank = 8
     perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))  # the same popularity order on every rank
     logp = torch.empty(E)
     logp[perm] = -1.2 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))
     logp = logp.to(dev)
     res = {str(T): {} for T in sizes}
 
-    def build(ep):
+    def routing(T, gen):
+        x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
+        logits = torch.randn(T, E, device=dev, generator=gen) + logp
+        w, ids = fused_topk(logits, topk, True)
+        counts = torch.bincount(ids.flatten().long(), minlength=E).float()
+        return x, StandardTopKOutput(w, ids, None), counts
+
+    def build(ep, location=None):
         initialize_model_parallel(1, ep)
         gen = torch.Generator(device=dev).manual_seed(41 + rank)
         moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="nccl", device=dev,
-                       equal_tokens_gather_below=2048)
+                       equal_tokens_gather_below=2048, expert_location=location)
         _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
         _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
+        return moe
 
-        def layer_for(T):
-            x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
-            logits = torch.randn(T, E, device=dev, generator=gen) + logp
-            w, ids = fused_topk(logits, topk, True)
-            top = StandardTopKOutput(w, ids, None)
-            counts = torch.bincount(ids.flatten().long(), minlength=E).float()
-            return (lambda: moe(x, top)), counts
-
-        return layer_for
-
-    if world > 1:
-        layer_for = build(1)
-        for T in sizes:
-            res[str(T)]["ms_1gpu_eager"] = _time(layer_for(T)[0], 10, 3, world, dev)
-        del layer_for
-        torch.cuda.empty_cache()
-    layer_for = build(world)
+    batches = {}
+    gen_in = torch.Generator(device=dev).manual_seed(4100 + rank)
     for T in sizes:
-        layer, counts = layer_for(T)
+        batches[T] = routing(T, gen_in)
+    if world > 1:
+        moe = build(1)
+        for T in sizes:
+            x, top, _ = batches[T]
+            res[str(T)]["ms_1gpu_eager"] = _time(lambda: moe(x, top), 10, 3, world, dev)
+        del moe
+        torch.cuda.empty_cache()
+    moe = build(world)
+    for T in sizes:
+        x, top, counts = batches[T]
+        layer = lambda: moe(x, top)
         ms = _time(layer, 10, 3, world, dev)
         r = res[str(T)]
         r["ms_eager"] = r["ms"] = ms
@@ -414,10 +424,31 @@ def moe_layer_skewed(args, ctx, peaks):
                   "tflops_per_gpu": 6.0 * T * topk * H * I / r["ms"] / 1e9,
                   "routed_per_expert_max_over_mean": float(counts.max() / counts.mean()),
                   "experts_hit": int((counts > 0).sum())})
+    del moe
+    torch.cuda.empty_cache()
+    if world > 1:
+        import torch.distributed as dist
+        for T in sizes:
+            x, top, counts = batches[T]
+            total = counts.clone()
+            dist.all_reduce(total)
+            loc = ExpertLocationMetadata.init_by_load(total, world, rank, redundant_per_rank)
+            moe = build(world, loc)
+            ms = _time(lambda: moe(x, top), 10, 3, world, dev)
+            r = res[str(T)]
+            r["ms_redundant"] = ms
+            r["efficiency_vs_1gpu_redundant"] = r["ms_1gpu_eager"] / ms
+            # share of this rank's routed rows that its own copies serve
+            hot = loc.physical_to_logical_map[loc.num_local_physical_experts - redundant_per_rank: loc.num_local_physical_experts]
+            r["rows_served_by_own_copies"] = float(counts[hot.long()].sum() / counts.sum())
+            del moe
+            torch.cuda.empty_cache()
     return {"moe_layer_skewed": {"config": "BASELINE config 4: Qwen3-30B-A3B MoE, 128 experts, hidden 2048, "
                                            "moe_intermediate 768, top-8 softmax routing, Zipf(1.2) expert popularity, "
-                                           "tokens per GPU as keyed",
-                                 "ep": world, "scaling": "weak", "results": res}}
+                                           "tokens per GPU as keyed; ms = static block placement, ms_redundant = eight "
+                                           "redundant copies of the hottest experts on every rank",
+                                 "ep": world, "scaling": "weak", "redundant_experts_per_rank": redundant_per_rank,
+                                 "results": res}}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -588,12 +619,19 @@ def ep_parity(ctx):
     w2q, w2s = make_block_fp8_weight(H, I, dev, gen, std=0.05, experts=E)
     gen_r = torch.Generator(device=dev).manual_seed(1000 + rank)  # this rank's own tokens
     cos = 1.0
-    for form, T in (("a2a", 33 + rank), ("gather", 32), ("allreduce", 32)):
+    import torch.distributed as dist
+    from sglang_b200.srt.eplb import ExpertLocationMetadata
+    for form, T in (("a2a", 33 + rank), ("gather", 32), ("allreduce", 32), ("a2a + redundant hot experts", 33 + rank)):
         g = gen if form == "allreduce" else gen_r  # the replicate form holds the same tokens on every rank
         x = torch.randn(T, H, device=dev, generator=g).bfloat16()
         w, ids = fused_topk(torch.randn(T, E, device=dev, generator=g), topk, True)
+        loc = None
+        if "redundant" in form:  # the eight most-routed experts on every rank, the other eight packed by load
+            count = torch.bincount(ids.flatten().long(), minlength=E).float()
+            dist.all_reduce(count)
+            loc = ExpertLocationMetadata.init_by_load(count, world, rank, E // 2)
         moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="none" if form == "allreduce" else "nccl",
-                       device=dev, equal_tokens_gather_below=1024 if form == "gather" else None)
+                       device=dev, equal_tokens_gather_below=1024 if form == "gather" else None, expert_location=loc)
         moe.load_full_weights(w13q, w13s, w2q, w2s)
         out = moe(x, StandardTopKOutput(w, ids, None))
         ref = fused_experts_impl(x, w13q, w2q, w, ids, use_fp8_w8a8=True, w1_scale=w13s, w2_scale=w2s,
@@ -627,6 +665,9 @@ def sharded_summary(out, world):
                 d = {"ms": round(r["ms_eager"], 4)}
                 if "ms_1gpu_eager" in r:
                     d["eff"] = round(r["ms_1gpu_eager"] / r["ms_eager"], 3)
+                if "ms_redundant" in r:  # with redundant copies of the hot experts (srt/eplb)
+                    d["ms_red"] = round(r["ms_redundant"], 4)
+                    d["eff_red"] = round(r["ms_1gpu_eager"] / r["ms_redundant"], 3)
                 s[f"{name}_T{T}"] = d
     par = [out.get(k, {}).get("parity") for k in ("tp_layer", "moe_layer")]
     par = [p for p in par if p is not None]
@@ -649,12 +690,13 @@ def run(sections, args, ctx, peaks):
     if "tp" in sections:
         out.update(tp_layer(args, ctx, peaks))
         torch.cuda.empty_cache()
-    if "moe" in sections:
+    if "moe" in sections or "moe3" in sections:
         out.update(moe_layer(args, ctx, peaks))
         torch.cuda.empty_cache()
-        if not (getattr(args, "moe_experts", 0) or getattr(args, "moe_tokens", 0)):  # (not in a profiler's reduced case)
-            out.update(moe_layer_skewed(args, ctx, peaks))
-            torch.cuda.empty_cache()
-    if "tp" in sections or "moe" in sections:
+    reduced = getattr(args, "moe_experts", 0) or getattr(args, "moe_tokens", 0)  # (a profiler's reduced case)
+    if ("moe" in sections and not reduced) or "moe4" in sections:
+        out.update(moe_layer_skewed(args, ctx, peaks))
+        torch.cuda.empty_cache()
+    if sections & {"tp", "moe", "moe3", "moe4"}:
         out["sharded"] = sharded_summary(out, world)  # last key of the JSON line
     return out

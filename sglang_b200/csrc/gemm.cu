@@ -252,6 +252,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         : p.sk_share > 0 ? p.sk_pieces * p.sk_ctas
                                          : p.full_units + (num_tiles - p.full_units) * p.splits;
 
+  // (the reduction kernel that follows a split launch is launched programmatically: letting it be scheduled now
+  // hides its launch latency; it waits for this grid to complete before it reads a partial sum)
+  ptx::launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
@@ -642,6 +645,7 @@ __global__ void __launch_bounds__(256)
     split_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
                         int64_t M, int64_t N, int BN, int tile_rows, int tiles_m, int tiles_n, int group_m,
                         int full_units, int splits, int rowmajor) {
+  ptx::grid_dependency_wait();  // the GEMM's partial sums are complete and visible
   const int tile = full_units + blockIdx.x;
   int m_tile, n_tile;
   tile_coord(tile, tiles_m, tiles_n, group_m, m_tile, n_tile);
@@ -679,6 +683,7 @@ __global__ void __launch_bounds__(256)
     streamk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C, const OutT* __restrict__ bias,
                           int64_t M, int64_t N, int BN, int tile_rows, int tiles_m, int tiles_n, int group_m,
                           int kb_total, int share, int ctas, int rowmajor) {
+  ptx::grid_dependency_wait();  // the GEMM's partial sums are complete and visible
   const int tile = blockIdx.x;
   int m_tile, n_tile;
   tile_coord(tile, tiles_m, tiles_n, group_m, m_tile, n_tile);
@@ -1000,31 +1005,38 @@ static int dense_mm(const DensePlan& dp, const void* A, const void* B, const flo
   if (rc != SGLB200_OK || pl.scratch_blocks() == 0) return rc;
   const int tiles_m = (int)((M + kTileRows - 1) / kTileRows);
   const unsigned ygrid = (unsigned)((kTileRows * BN / 8 + 255) / 256);
+  // The reduction is launched programmatically (it may be scheduled while the GEMM's last CTAs drain).
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int rowmajor = p.partial_rowmajor, bn = BN, tile_rows = kTileRows;
   if (pl.sk_share > 0) {
-    const dim3 sgrid((unsigned)tiles, ygrid);
+    cfg.gridDim = dim3((unsigned)tiles, ygrid, 1);
     if (out_dtype == 0)
-      streamk_reduce_kernel<__nv_bfloat16><<<sgrid, 256, 0, st>>>(
-          p.partial, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, BN, kTileRows, tiles_m,
-          p.tiles_n, p.group_m, p.kb_total, pl.sk_share, pl.sk_ctas, p.partial_rowmajor);
+      SGLB_CUDA(cudaLaunchKernelEx(&cfg, streamk_reduce_kernel<__nv_bfloat16>, (const float*)p.partial,
+                                   static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, bn,
+                                   tile_rows, tiles_m, p.tiles_n, p.group_m, p.kb_total, pl.sk_share, pl.sk_ctas, rowmajor));
     else
-      streamk_reduce_kernel<__half><<<sgrid, 256, 0, st>>>(p.partial, static_cast<__half*>(C),
-                                                           static_cast<const __half*>(bias), M, N, BN, kTileRows,
-                                                           tiles_m, p.tiles_n, p.group_m, p.kb_total, pl.sk_share,
-                                                           pl.sk_ctas, p.partial_rowmajor);
-    SGLB_CUDA(cudaGetLastError());
+      SGLB_CUDA(cudaLaunchKernelEx(&cfg, streamk_reduce_kernel<__half>, (const float*)p.partial, static_cast<__half*>(C),
+                                   static_cast<const __half*>(bias), M, N, bn, tile_rows, tiles_m, p.tiles_n, p.group_m,
+                                   p.kb_total, pl.sk_share, pl.sk_ctas, rowmajor));
     return SGLB200_OK;
   }
-  const dim3 grid((unsigned)pl.split_tiles, ygrid);
+  cfg.gridDim = dim3((unsigned)pl.split_tiles, ygrid, 1);
   if (out_dtype == 0)
-    split_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p.partial, static_cast<__nv_bfloat16*>(C),
-                                                             static_cast<const __nv_bfloat16*>(bias), M, N, BN, kTileRows,
-                                                             tiles_m, p.tiles_n, p.group_m, pl.full_units, pl.splits,
-                                                             p.partial_rowmajor);
+    SGLB_CUDA(cudaLaunchKernelEx(&cfg, split_reduce_kernel<__nv_bfloat16>, (const float*)p.partial,
+                                 static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, bn, tile_rows,
+                                 tiles_m, p.tiles_n, p.group_m, pl.full_units, pl.splits, rowmajor));
   else
-    split_reduce_kernel<__half><<<grid, 256, 0, st>>>(p.partial, static_cast<__half*>(C),
-                                                      static_cast<const __half*>(bias), M, N, BN, kTileRows, tiles_m,
-                                                      p.tiles_n, p.group_m, pl.full_units, pl.splits, p.partial_rowmajor);
-  SGLB_CUDA(cudaGetLastError());
+    SGLB_CUDA(cudaLaunchKernelEx(&cfg, split_reduce_kernel<__half>, (const float*)p.partial, static_cast<__half*>(C),
+                                 static_cast<const __half*>(bias), M, N, bn, tile_rows, tiles_m, p.tiles_n, p.group_m,
+                                 pl.full_units, pl.splits, rowmajor));
   return SGLB200_OK;
 }
 

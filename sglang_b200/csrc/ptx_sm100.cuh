@@ -20,6 +20,14 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may be scheduled while its predecessor in
+// the stream is still running (once every CTA of the predecessor has called launch_dependents or exited);
+// grid_dependency_wait() then blocks until the predecessor has completed and its writes are visible.  Both are
+// no-ops in launches without the attribute.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- mbarrier ------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -24,6 +24,7 @@ import torch
 from torch import nn
 
 from ....distributed import get_moe_ep_group
+from ....eplb import ExpertLocationMetadata, topk_ids_logical_to_physical
 from ..moe_runner.base import MoeRunnerConfig
 from ..token_dispatcher import StandardDispatcher, StandardTopKOutput
 from .ep_a2a import ep_all_to_all_forward
@@ -33,12 +34,21 @@ class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, hidden_size: int, intermediate_size: int, top_k: int,
                  params_dtype: torch.dtype = torch.bfloat16, quant_config=None, prefix: str = "",
                  routed_scaling_factor: Optional[float] = None, a2a_backend: str = "none", inplace: bool = False,
-                 device=None, equal_tokens_gather_below: Optional[int] = None):
+                 device=None, equal_tokens_gather_below: Optional[int] = None,
+                 expert_location: Optional[ExpertLocationMetadata] = None):
+        """`expert_location`: a placement with redundant copies of hot experts (`srt/eplb`); `num_experts` stays the
+        number of LOGICAL experts the router names, the layer holds `num_local_physical_experts` of them and maps the
+        routed ids to physical slots before dispatching."""
         super().__init__()
         ep = get_moe_ep_group()
         self.moe_ep_size = ep.world_size
         self.moe_ep_rank = max(ep.rank_in_group, 0)
         assert num_experts % self.moe_ep_size == 0
+        self.num_logical_experts = num_experts
+        self.expert_location = expert_location
+        if expert_location is not None:
+            assert expert_location.ep_size == self.moe_ep_size and expert_location.num_logical_experts == num_experts
+            num_experts = expert_location.num_physical_experts
         self.num_experts = num_experts
         self.num_local_experts = num_experts // self.moe_ep_size
         self.hidden_size = hidden_size
@@ -58,6 +68,16 @@ class FusedMoE(nn.Module):
         self.dispatcher = StandardDispatcher(num_experts, self.moe_ep_size, self.moe_ep_rank)
 
     def load_full_weights(self, w13, w13_s, w2, w2_s) -> None:
+        """Takes this rank's experts out of tensors that hold ALL logical experts."""
+        if self.expert_location is not None:
+            idx = self.expert_location.local_logical_experts(self.moe_ep_rank).long().to(w13.device)
+            pick = lambda t: t.view(torch.uint8).index_select(0, idx).view(t.dtype) if t.dtype == torch.float8_e4m3fn \
+                else t.index_select(0, idx)
+            self.w13_weight.data.copy_(pick(w13))
+            self.w13_weight_scale_inv.data.copy_(pick(w13_s))
+            self.w2_weight.data.copy_(pick(w2))
+            self.w2_weight_scale_inv.data.copy_(pick(w2_s))
+            return
         lo = self.moe_ep_rank * self.num_local_experts
         hi = lo + self.num_local_experts
         self.w13_weight.data.copy_(w13[lo:hi])
@@ -66,6 +86,9 @@ class FusedMoE(nn.Module):
         self.w2_weight_scale_inv.data.copy_(w2_s[lo:hi])
 
     def forward(self, hidden_states: torch.Tensor, topk_output: StandardTopKOutput) -> torch.Tensor:
+        if self.expert_location is not None:  # logical ids -> this rank's choice of physical slots
+            topk_output = StandardTopKOutput(topk_output[0], topk_ids_logical_to_physical(topk_output[1], self.expert_location),
+                                             topk_output[2])
         if self.a2a_backend == "nccl" and self.moe_ep_size > 1:
             n = self.equal_tokens_gather_below
             if n is not None and hidden_states.shape[0] * self.moe_ep_size <= n:

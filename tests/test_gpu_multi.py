@@ -76,9 +76,20 @@ def _worker(rank, world, port, ret):
         moe.load_full_weights(codes_to_fp8(w13q, dev), torch.from_numpy(w13s).to(dev), codes_to_fp8(wdq, dev),
                               torch.from_numpy(wds).to(dev))
         outs["gather"] = moe(xt[:33].to(dev), StandardTopKOutput(tw[:33].to(dev), ti[:33].to(dev), None)).float().cpu().numpy()
+        # redundant copies of the two hottest experts on every rank (srt/eplb): hot rows are served by the sender's own copy
+        from sglang_b200.srt.eplb import ExpertLocationMetadata
+        count = torch.bincount(ti.flatten().long(), minlength=E).float().to(dev)
+        dist.all_reduce(count)
+        for key, make in (("replicas", ExpertLocationMetadata.init_by_hot_replication),
+                          ("packed", ExpertLocationMetadata.init_by_load)):  # (hot copies; hot copies + cold experts by load)
+            loc = make(count, world, rank, 2)
+            moe = FusedMoE(E, Hm, Im, topk, quant_config=cfg, a2a_backend="nccl", device=dev, expert_location=loc)
+            moe.load_full_weights(codes_to_fp8(w13q, dev), torch.from_numpy(w13s).to(dev), codes_to_fp8(wdq, dev),
+                                  torch.from_numpy(wds).to(dev))
+            outs[key] = moe(xt.to(dev), StandardTopKOutput(tw.to(dev), ti.to(dev), None)).float().cpu().numpy()
         torch.cuda.synchronize()
         from sglang_b200 import ops
-        ret[rank] = dict(moe_gather=outs["gather"], y=y.float().cpu().numpy(), gu=gu.float().cpu().numpy(), moe_a2a=outs["nccl"],
+        ret[rank] = dict(moe_rep=outs["replicas"], moe_packed=outs["packed"], moe_gather=outs["gather"], y=y.float().cpu().numpy(), gu=gu.float().cpu().numpy(), moe_a2a=outs["nccl"],
                          moe_std=outs["none"], x=to_f32_np(xt), tw=tw.numpy(), ti=ti.numpy(), status=ops.gemm_status())
     finally:
         dist.destroy_process_group()
@@ -110,6 +121,8 @@ def test_tp_and_ep_on_two_gpus():
         assert_close_fp(d["y"], y_ref, rtol=2e-2, atol=2e-2, min_cos=0.9995)
         ref = O.fused_experts_block_fp8(d["x"], w13q, w13s, wdq, wds, d["tw"], d["ti"], 1.0)
         assert_close_fp(d["moe_a2a"], ref, rtol=2e-2, atol=2e-2)
+        assert_close_fp(d["moe_rep"], ref, rtol=2e-2, atol=2e-2)
+        assert_close_fp(d["moe_packed"], ref, rtol=2e-2, atol=2e-2)
         assert d["moe_gather"].shape == (33, Hm)
         assert_close_fp(d["moe_gather"], ref[:33], rtol=2e-2, atol=2e-2)
     ref0 = O.fused_experts_block_fp8(ret[0]["x"], w13q, w13s, wdq, wds, ret[0]["tw"], ret[0]["ti"], 1.0)

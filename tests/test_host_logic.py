@@ -131,6 +131,56 @@ def test_dispatch_mask_mixed_filtered_and_valid_ids():
     assert (plan.slot[2] == S).all() and (plan.slot[4] == S).all()  # tokens that go nowhere point at the zero row
 
 
+def test_expert_location_hot_replication():
+    """Placement with redundant copies of the hottest experts: every rank keeps its block of logical experts plus a copy
+    of the same hot ones, sends a hot expert's rows to its own copy (to the original where it is the owner), and the
+    physical-to-logical map tells each slot which weights to load."""
+    from sglang_b200.srt.eplb import ExpertLocationMetadata, topk_ids_logical_to_physical
+    count = torch.tensor([5.0, 1, 9, 2, 7, 7, 0, 3])  # experts 2 and 4 are the hottest (4 wins the tie with 5)
+    metas = [ExpertLocationMetadata.init_by_hot_replication(count, 2, r, 2) for r in range(2)]
+    for m in metas:
+        assert m.num_physical_experts == 12 and m.num_local_physical_experts == 6
+        assert m.physical_to_logical_map.tolist() == [0, 1, 2, 3, 2, 4, 4, 5, 6, 7, 2, 4]
+    assert metas[0].logical_to_rank_dispatch_physical_map.tolist() == [0, 1, 2, 3, 5, 7, 8, 9]
+    assert metas[1].logical_to_rank_dispatch_physical_map.tolist() == [0, 1, 10, 3, 6, 7, 8, 9]
+    ids = torch.tensor([[2, 4, -1], [0, 7, 5]], dtype=torch.int32)
+    for r, m in enumerate(metas):
+        phys = topk_ids_logical_to_physical(ids, m)
+        assert phys.dtype == torch.int32 and int(phys[0, 2]) == -1
+        # every physical slot a rank names holds the logical expert that was routed, and hot rows stay on the rank
+        ok = phys >= 0
+        assert torch.equal(m.physical_to_logical_map[phys[ok].long()], ids[ok])
+        assert all(int(phys[0, j]) // 6 == r for j in (0, 1))
+    assert metas[0].local_logical_experts(1).tolist() == [4, 5, 6, 7, 2, 4]
+    assert topk_ids_logical_to_physical(ids, None) is ids
+
+
+def test_expert_location_by_load():
+    """Hot experts on every rank only, cold experts packed by routed rows: every logical expert has a slot, every rank
+    the same number of slots, the cold load is spread evenly, and all ranks agree on the cold experts' places."""
+    from sglang_b200.srt.eplb import ExpertLocationMetadata, topk_ids_logical_to_physical
+    g = torch.Generator().manual_seed(5)
+    E, p, R = 20, 4, 4
+    count = (torch.arange(1, E + 1, dtype=torch.float64) ** -1.2)[torch.randperm(E, generator=g)] * 1e6
+    metas = [ExpertLocationMetadata.init_by_load(count, p, r, R) for r in range(p)]
+    hot = set(torch.topk(count, R).indices.tolist())
+    local = (E - R) // p + R
+    for r, m in enumerate(metas):
+        assert m.num_local_physical_experts == local and m.num_physical_experts == p * local
+        assert torch.equal(m.physical_to_logical_map, metas[0].physical_to_logical_map)
+        l2p = m.logical_to_rank_dispatch_physical_map
+        assert torch.equal(m.physical_to_logical_map[l2p.long()], torch.arange(E, dtype=torch.int32))
+        for e in range(E):
+            owner = int(l2p[e]) // local
+            assert (owner == r) if e in hot else (int(l2p[e]) == int(metas[0].logical_to_rank_dispatch_physical_map[e]))
+        assert set(m.local_logical_experts(r)[-R:].tolist()) == hot
+    # cold rows per rank: within 15 % of their mean (they are 16 experts with a 1 : 9 spread of loads)
+    cold_load = [sum(float(count[e]) for e in metas[0].local_logical_experts(r)[:-R].tolist()) for r in range(p)]
+    assert max(cold_load) <= 1.15 * (sum(cold_load) / p)
+    ids = torch.tensor([[0, 5, -1]], dtype=torch.int32)
+    assert int(topk_ids_logical_to_physical(ids, metas[2])[0, 2]) == -1
+
+
 def _tp_worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
