@@ -207,6 +207,13 @@ def tp_layer(args, ctx, peaks):
 
             return layer
 
+        def compare(T):
+            x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
+            w, ids = biased_grouped_topk(torch.randn(T, E, device=dev, generator=gen), None, topk, True, 8, 4)
+            return grouped_vs_reference(moe.w13_weight.data, moe.w13_weight_scale_inv.data, moe.w2_weight.data,
+                                        moe.w2_weight_scale_inv.data, x, ids, w, dev)
+
+        layer_for.compare = compare
         return layer_for
 
     def time_all(layer_for, key, ranks):
@@ -309,6 +316,13 @@ def moe_layer(args, ctx, peaks):
 
             return layer
 
+        def compare(T):
+            x = torch.randn(T, H, device=dev, generator=gen).bfloat16()
+            w, ids = biased_grouped_topk(torch.randn(T, E, device=dev, generator=gen), None, topk, True, 8, 4)
+            return grouped_vs_reference(moe.w13_weight.data, moe.w13_weight_scale_inv.data, moe.w2_weight.data,
+                                        moe.w2_weight_scale_inv.data, x, ids, w, dev)
+
+        layer_for.compare = compare
         return layer_for
 
     if world > 1:
@@ -330,6 +344,10 @@ def moe_layer(args, ctx, peaks):
             r["efficiency_vs_1gpu"] = r["ms_1gpu_eager"] / ms
         flops = 6.0 * T * topk * H * I + 6.0 * T * H * I
         r.update({"tokens_per_s": world * T / r["ms"] * 1e3, "tflops_per_gpu": flops / r["ms"] / 1e9})
+    if world == 1 and not reduced:
+        cmp_ = layer_for.compare(max(sizes))
+        if cmp_ is not None:
+            res[str(max(sizes))]["grouped_gemms_vs_reference_kernel"] = cmp_
     out = {"config": "BASELINE config 3: DeepSeek-V3 MoE, 256 routed experts + 1 shared, hidden 7168, "
                      "moe_intermediate 2048, top-8 grouped sigmoid routing (8 groups, top-4), "
                      "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine (batches of at "
@@ -341,6 +359,98 @@ def moe_layer(args, ctx, peaks):
     if parity is not None:
         out["parity"] = parity
     return {"moe_layer": out}
+
+
+# ------------------------------------------------------------------------------------------------
+# the two expert-grouped GEMMs of a MoE layer call against the reference's own CUDA kernel (one GPU only)
+# ------------------------------------------------------------------------------------------------
+def grouped_vs_reference(w13, w13_s, w2, w2_s, x, ids, wts, dev, iters=5):
+    """This library's grouped kernel and the reference's `fp8_blockwise_scaled_grouped_mm` (its
+    sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu compiled here with its one-CTA tile configurations, `make -C oracle
+    ref_gpu_moe`) on the same quantised rows and the same expert weights, each in the row order its own pipeline
+    uses: 128-row padded expert blocks here, compact expert-major rows there (python/sglang/srt/layers/moe/
+    cutlass_moe.py:140-232).  Returns None where the comparator library is not built; not part of any `value`."""
+    import os
+    lib = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libsgl_gpu_ref_moe.so")
+    if not os.path.exists(lib):
+        return None
+    try:
+        import sglang_b200.sgl_kernel as sk
+        from sglang_b200 import ops
+        from sglang_b200.srt.layers.moe.fused_moe_triton.fused_moe import _max_padded_rows
+        T, H = x.shape
+        E, N1, _ = w13.shape
+        I, topk = N1 // 2, ids.shape[1]
+        R = T * topk
+        if R <= 2048 and (H >= 2048 or I >= 2048):
+            return {"unavailable": "at most 2048 rows with K >= 2048: the reference routes this shape to its two-CTA "
+                                   "cluster configuration, which is left out of the comparator build"}
+        torch.ops.load_library(lib)
+        ref = torch.ops.sgl_gpu_ref.fp8_blockwise_scaled_grouped_mm
+        i32, i64 = dict(dtype=torch.int32, device=dev), dict(dtype=torch.int64, device=dev)
+        offs, ps1, ps2 = torch.empty(E + 1, **i32), torch.empty(E, 3, **i32), torch.empty(E, 3, **i32)
+        a_map, c_map = torch.empty(R, **i32), torch.empty(R, **i32)
+        sk.prepare_moe_input(ids, offs, ps1, ps2, a_map, c_map, E, I, H)
+        if int(ps1[:, 0].min()) == 0:
+            return {"unavailable": "an expert without rows in this batch; the comparator is only run on batches that "
+                                   "give every expert at least one row"}
+        xq, xs = ops.per_token_group_quant_fp8(x, 128)
+        rep_a, rep_s = sk.shuffle_rows(xq, a_map, (R, H)), sk.shuffle_rows(xs, a_map, (R, H // 128))
+        c1 = torch.empty(R, 2 * I, device=dev, dtype=torch.bfloat16)
+        c2 = torch.empty(R, H, device=dev, dtype=torch.bfloat16)
+        ptrs = [torch.empty(E, **i64) for _ in range(5)]
+        ab1, cs1 = torch.full((E,), H, **i64), torch.full((E,), 2 * I, **i64)
+        ab2, cs2 = torch.full((E,), I, **i64), torch.full((E,), H, **i64)
+        lay_a, lay_b = torch.empty(E, 5, **i32), torch.empty(E, 5, **i32)
+        work = torch.empty(90000, device=dev, dtype=torch.uint8)
+        w13_t, w13_st, w2_t, w2_st = w13.transpose(1, 2), w13_s.transpose(1, 2), w2.transpose(1, 2), w2_s.transpose(1, 2)
+
+        def ref1():
+            ref(c1, *ptrs, rep_a, w13_t, rep_s, w13_st, ab1, ab1, cs1, lay_a, lay_b, ps1, offs[:-1], work)
+
+        ref1()
+        inter_q, inter_s = ops.per_token_group_quant_fp8(sk.silu_and_mul(c1), 128)
+
+        def ref2():
+            ref(c2, *ptrs, inter_q, w2_t, inter_s, w2_st, ab2, ab2, cs2, lay_a, lay_b, ps2, offs[:-1], work)
+
+        sorted_ids, expert_ids, post = ops.moe_align_block_size(ids, ops.ALIGN_BLOCK, E)
+        a1, a1s = ops.gather_rows_fp8(xq, xs, sorted_ids, post, R, topk, _max_padded_rows(R, E, ops.ALIGN_BLOCK))
+        ic1 = torch.empty(a1.shape[0], 2 * I, device=dev, dtype=torch.bfloat16)
+
+        def mine1():
+            ops.grouped_block_fp8_matmul(a1, a1s, w13, w13_s, sorted_ids, expert_ids, post, numel=R, scatter=False,
+                                         out=ic1)
+
+        mine1()
+        a2, a2s = ops.silu_and_mul_quant_fp8(ic1, 128, num_rows=post)
+        o2 = torch.empty(R, H, device=dev, dtype=torch.bfloat16)
+
+        def mine2(weights=wts):
+            ops.grouped_block_fp8_matmul(a2, a2s, w2, w2_s, sorted_ids, expert_ids, post, numel=R, scatter=True,
+                                         row_weights=weights, out=o2)
+
+        # parity of the two kernels on these inputs: row p of the padded order is flat slot sorted_ids[p], which the
+        # reference's order holds at row c_map[slot]
+        ref2()
+        mine2(None)
+        n_pad = int(post.item())
+        slot = sorted_ids[:n_pad].long()
+        valid = slot < R
+        same1 = bool(torch.equal(ic1[:n_pad][valid].view(torch.int16), c1[c_map[slot[valid]].long()].view(torch.int16)))
+        same2 = bool(torch.equal(o2.view(torch.int16), c2[c_map.long()].view(torch.int16)))
+        close2 = bool(torch.allclose(o2.float(), c2[c_map.long()].float(), rtol=2 ** -6, atol=1e-2))
+        fl1, fl2 = 2.0 * R * 2 * I * H, 2.0 * R * H * I
+        out = {"rows": R, "experts": E,
+               "reference_kernel": "sgl-kernel fp8_blockwise_scaled_grouped_mm, one-CTA configurations "
+                                   "(128x128x128 tiles for K >= 2048, 64x128x128 below)",
+               "bit_identical": {"gemm1": same1, "gemm2": same2}, "gemm2_close": close2}
+        for name, mine, theirs, fl in (("gemm1", mine1, ref1, fl1), ("gemm2", mine2, ref2, fl2)):
+            ms, ms_ref = _time(mine, iters, 3, 1, dev), _time(theirs, iters, 3, 1, dev)
+            out[name] = {"ms": ms, "ref_ms": ms_ref, "tflops": fl / ms / 1e9, "ref_tflops": fl / ms_ref / 1e9}
+        return out
+    except Exception as e:  # the comparator is optional: never let it break the section
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -424,6 +534,12 @@ def moe_layer_skewed(args, ctx, peaks):
                   "tflops_per_gpu": 6.0 * T * topk * H * I / r["ms"] / 1e9,
                   "routed_per_expert_max_over_mean": float(counts.max() / counts.mean()),
                   "experts_hit": int((counts > 0).sum())})
+    if world == 1:
+        x, top, _ = batches[max(sizes)]
+        cmp_ = grouped_vs_reference(moe.w13_weight.data, moe.w13_weight_scale_inv.data, moe.w2_weight.data,
+                                    moe.w2_weight_scale_inv.data, x, top[1], top[0], dev)
+        if cmp_ is not None:
+            res[str(max(sizes))]["grouped_gemms_vs_reference_kernel"] = cmp_
     del moe
     torch.cuda.empty_cache()
     if world > 1:

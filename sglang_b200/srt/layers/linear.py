@@ -6,6 +6,12 @@ After python/sglang/srt/layers/linear.py: `LinearBase` (:160-228), `ColumnParall
 checkpoint tensor and of its 128x128 block scales (:737-746, :917-973: a shard of n output rows owns
 n/128 scale rows, a shard of k input columns owns k/128 scale columns), and the all-reduce after a
 row-parallel layer (:1384-1385).
+
+Checkpoint loading: every layer gives its `weight` and `weight_scale_inv` parameters a `weight_loader` attribute with
+the calling convention of the reference's loaders (`param.weight_loader(param, loaded_weight[, shard_id])`,
+:381-436, :575-763, :1035-1195, :1314-1352) so that a model's `load_weights` loop can drive them
+(`srt/model_loader/weight_utils.py`).  `loaded_weight` is the FULL checkpoint tensor of one logical matrix; the
+loader keeps this rank's rows or columns, and 1/128 of them (rounded up) for a block-scale parameter.
 """
 from __future__ import annotations
 
@@ -28,6 +34,22 @@ def divide(a: int, b: int) -> int:
     return a // b
 
 
+def _ceil_div(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
+def _copy_checked(dst: torch.Tensor, src: torch.Tensor, what: str) -> None:
+    if tuple(dst.shape) != tuple(src.shape):
+        raise ValueError(f"{what}: checkpoint shard of shape {tuple(src.shape)} does not fit the parameter slice "
+                         f"of shape {tuple(dst.shape)}")
+    if dst.dtype == torch.float8_e4m3fn:  # copy codes as bytes (no float8 copy kernels are needed on any device)
+        if src.dtype != torch.float8_e4m3fn:
+            raise ValueError(f"{what}: the checkpoint holds {src.dtype}, the layer wants serialized float8_e4m3fn")
+        dst.view(torch.uint8).copy_(src.view(torch.uint8))
+    else:
+        dst.copy_(src)
+
+
 class LinearBase(nn.Module):
     def __init__(self, input_size: int, output_size: int, params_dtype: torch.dtype = torch.bfloat16,
                  quant_config=None, prefix: str = ""):
@@ -41,6 +63,42 @@ class LinearBase(nn.Module):
             raise NotImplementedError("this package implements the block-FP8 quantised linears only")
         self.tp_size = get_tensor_model_parallel_world_size()
         self.tp_rank = get_tensor_model_parallel_rank()
+        self.prefix = prefix
+
+    def _attach_loaders(self) -> None:
+        for name in ("weight", "weight_scale_inv"):
+            param = getattr(self, name)
+            param.weight_loader = self.weight_loader
+            param.is_block_scale = name == "weight_scale_inv"
+
+    def _block(self, param) -> tuple:
+        """(rows, columns) of the weight that one element of `param` stands for."""
+        if getattr(param, "is_block_scale", False):
+            bn, bk = self.quant_method.quant_config.weight_block_size
+            return bn, bk
+        return 1, 1
+
+
+class ReplicatedLinear(LinearBase):
+    """Y = X W^T with the whole W on every rank (linear.py:231-262); DeepSeek's fused_qkv_a_proj_with_mqa is one."""
+
+    def __init__(self, input_size: int, output_size: int, bias: bool = False, params_dtype: torch.dtype = torch.bfloat16,
+                 quant_config=None, prefix: str = "", device=None):
+        super().__init__(input_size, output_size, params_dtype, quant_config, prefix)
+        # (partition sizes equal to the full sizes: none of create_weights' tensor-parallel divisibility rules
+        # applies, so an output size like 2112 = 16.5 blocks is accepted, as by the reference's replicated layer)
+        self.tp_size, self.tp_rank = 1, 0
+        self.quant_method.create_weights(self, input_size, [output_size], input_size, output_size, params_dtype,
+                                         device=device)
+        self.bias = nn.Parameter(torch.zeros(output_size, dtype=params_dtype, device=device),
+                                 requires_grad=False) if bias else None
+        self._attach_loaders()
+
+    def weight_loader(self, param, loaded_weight: torch.Tensor) -> None:
+        _copy_checked(param.data, loaded_weight, self.prefix or "ReplicatedLinear")
+
+    def forward(self, x):
+        return self.quant_method.apply(self, x, self.bias), None
 
 
 class ColumnParallelLinear(LinearBase):
@@ -58,6 +116,35 @@ class ColumnParallelLinear(LinearBase):
             self, input_size, self.output_partition_sizes, input_size, output_size, params_dtype, device=device)
         self.bias = nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=params_dtype, device=device),
                                  requires_grad=False) if bias else None
+        self._attach_loaders()
+
+    def _load_part(self, param, loaded_weight: torch.Tensor, part: int, src_block: Optional[int] = None) -> None:
+        """Logical part `part` of a (merged) column-parallel parameter from the full tensor of that part:
+        destination rows [sum of the earlier parts, + this part) of this rank's shard, source rows
+        [src_block x this part, + this part); rows counted in 128-row blocks, rounded up, for a scale parameter
+        (linear.py:737-746).  `src_block` defaults to this rank (a replicated KV head passes its own index)."""
+        bn, _ = self._block(param)
+        size = _ceil_div(self.output_partition_sizes[part], bn)
+        dst_off = _ceil_div(sum(self.output_partition_sizes[:part]), bn)
+        src_off = (self.tp_rank if src_block is None else src_block) * size
+        if src_off + size > loaded_weight.shape[0]:
+            raise ValueError(f"{self.prefix}: rows {src_off}..{src_off + size} of a checkpoint tensor with "
+                             f"{loaded_weight.shape[0]} rows")
+        _copy_checked(param.data.narrow(0, dst_off, size), loaded_weight.narrow(0, src_off, size), self.prefix)
+
+    def weight_loader(self, param, loaded_weight: torch.Tensor, loaded_shard_id: Optional[int] = None) -> None:
+        """`loaded_shard_id` None: the checkpoint tensor holds all logical parts one after the other (a plain
+        column-parallel layer, or a merged one stored fused on disk: linear.py:651-707); an int: it holds that part."""
+        if loaded_shard_id is not None:
+            assert 0 <= loaded_shard_id < len(self.output_sizes)
+            self._load_part(param, loaded_weight, loaded_shard_id)
+            return
+        bn, _ = self._block(param)
+        off = 0
+        for part, full in enumerate(self.output_sizes):
+            rows = _ceil_div(full, bn)
+            self._load_part(param, loaded_weight.narrow(0, off, rows), part)
+            off += rows
 
     def load_full_weight(self, weight: torch.Tensor, weight_scale_inv: torch.Tensor, block: int = 128) -> None:
         """Shards a full [N,K] e4m3 weight and its [N/128,K/128] scales; merged layers shard each logical
@@ -85,9 +172,35 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
 
 
 class QKVParallelLinear(ColumnParallelLinear):
+    """Query heads are split over the ranks; so are the key/value heads while there are at least as many of them as
+    ranks, beyond that every KV head is held by tp_size / total_num_kv_heads consecutive ranks (linear.py:846-870)."""
+
     def __init__(self, hidden_size: int, head_size: int, total_num_heads: int, total_num_kv_heads: int, **kw):
-        sizes = [total_num_heads * head_size, total_num_kv_heads * head_size, total_num_kv_heads * head_size]
+        from ..distributed import get_tensor_model_parallel_world_size as tp_world
+        tp = tp_world()
+        self.head_size = head_size
+        self.num_kv_head_replicas = 1 if tp <= total_num_kv_heads else divide(tp, total_num_kv_heads)
+        # (sizes as ColumnParallelLinear divides them: a replicated KV head counts once per rank that holds it)
+        kv = max(total_num_kv_heads, tp) * head_size
+        sizes = [total_num_heads * head_size, kv, kv]
         super().__init__(hidden_size, sum(sizes), output_sizes=sizes, **kw)
+
+    def weight_loader(self, param, loaded_weight: torch.Tensor, loaded_shard_id: Optional[str] = None) -> None:
+        """`loaded_shard_id` "q" / "k" / "v" (linear.py:1035-1195): the checkpoint's q_proj, k_proj or v_proj."""
+        if loaded_shard_id is None:
+            raise NotImplementedError("QKV weights stored fused on disk are not on this path; pass \"q\", \"k\" or \"v\"")
+        part = {"q": 0, "k": 1, "v": 2}[loaded_shard_id]
+        src = self.tp_rank if part == 0 else self.tp_rank // self.num_kv_head_replicas
+        self._load_part(param, loaded_weight, part, src_block=src)
+
+    def load_full_weight(self, weight: torch.Tensor, weight_scale_inv: torch.Tensor, block: int = 128) -> None:
+        """A full [q; k; v] weight (rows of the checkpoint's three projections one after the other) and its scales."""
+        q = self.output_sizes[0]
+        kv = self.output_sizes[1] // self.num_kv_head_replicas
+        assert weight.shape[0] == q + 2 * kv and q % block == 0 and kv % block == 0
+        for name, lo, n in (("q", 0, q), ("k", q, kv), ("v", q + kv, kv)):
+            self.weight_loader(self.weight, weight[lo : lo + n], name)
+            self.weight_loader(self.weight_scale_inv, weight_scale_inv[lo // block : (lo + n) // block], name)
 
 
 class RowParallelLinear(LinearBase):
@@ -104,6 +217,14 @@ class RowParallelLinear(LinearBase):
             self, self.input_size_per_partition, [output_size], input_size, output_size, params_dtype, device=device)
         self.bias = nn.Parameter(torch.zeros(output_size, dtype=params_dtype, device=device),
                                  requires_grad=False) if bias else None
+        self._attach_loaders()
+
+    def weight_loader(self, param, loaded_weight: torch.Tensor) -> None:
+        """This rank's input columns of the full tensor (linear.py:1314-1352); K/128 columns for a scale parameter."""
+        _, bk = self._block(param)
+        size = _ceil_div(self.input_size_per_partition, bk)
+        src = loaded_weight.narrow(1, self.tp_rank * size, size) if self.tp_size > 1 else loaded_weight
+        _copy_checked(param.data, src, self.prefix)
 
     def load_full_weight(self, weight: torch.Tensor, weight_scale_inv: torch.Tensor, block: int = 128) -> None:
         k = self.input_size_per_partition

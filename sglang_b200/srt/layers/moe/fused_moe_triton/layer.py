@@ -18,7 +18,7 @@ rank r of an EP group of size p owns experts [r*E/p, (r+1)*E/p) (:182-185).
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import List, Optional, Tuple
 
 import torch
 from torch import nn
@@ -66,6 +66,56 @@ class FusedMoE(nn.Module):
             inplace=inplace, routed_scaling_factor=routed_scaling_factor)
         self.quant_method.create_moe_runner(self, self.moe_runner_config)
         self.dispatcher = StandardDispatcher(num_experts, self.moe_ep_size, self.moe_ep_rank)
+        self.prefix = prefix
+        for name in ("w13_weight", "w2_weight", "w13_weight_scale_inv", "w2_weight_scale_inv"):
+            getattr(self, name).weight_loader = self.weight_loader
+
+    # ---- checkpoint loading (layer.py:575-918) -------------------------------------------------------------------
+    @classmethod
+    def make_expert_params_mapping(cls, ckpt_gate_proj_name: str, ckpt_down_proj_name: str, ckpt_up_proj_name: str,
+                                   num_experts: int) -> List[Tuple[str, str, int, str]]:
+        """(parameter-name prefix, checkpoint-name fragment, expert id, shard id) for every expert and projection, in
+        the form a model's `load_weights` loop matches names with (layer.py:921-947): the checkpoint's
+        `experts.<e>.<gate|up>_proj.` tensors are shards "w1" / "w3" of `experts.w13_*`, `down_proj.` is "w2" of
+        `experts.w2_*`."""
+        out = []
+        for e in range(num_experts):
+            for shard_id, ckpt in (("w1", ckpt_gate_proj_name), ("w2", ckpt_down_proj_name), ("w3", ckpt_up_proj_name)):
+                target = "experts.w2_" if ckpt == ckpt_down_proj_name else "experts.w13_"
+                out.append((target, f"experts.{e}.{ckpt}.", e, shard_id))
+        return out
+
+    def local_slots_of(self, expert_id: int) -> List[int]:
+        """This rank's slots that hold logical expert `expert_id` (none if another rank owns it; more than one only
+        under a placement with redundant copies)."""
+        if self.expert_location is not None:
+            mine = self.expert_location.local_logical_experts(self.moe_ep_rank).tolist()
+            return [j for j, e in enumerate(mine) if e == expert_id]
+        j = expert_id - self.moe_ep_rank * self.num_local_experts
+        return [j] if 0 <= j < self.num_local_experts else []
+
+    def weight_loader(self, param, loaded_weight: torch.Tensor, weight_name: str, shard_id: str, expert_id: int) -> None:
+        """One projection of one expert from the checkpoint into its place (layer.py:575-918, block-FP8 branch):
+        gate_proj ("w1") fills rows [0, I) of w13, up_proj ("w3") rows [I, 2I), down_proj ("w2") all of w2; a
+        `*_scale_inv` parameter takes the rows counted in 128-row blocks.  Experts of other ranks are skipped."""
+        if shard_id not in ("w1", "w2", "w3"):
+            raise ValueError(f"shard_id must be ['w1','w2','w3'] but got {shard_id}.")
+        is_scale = param is self.w13_weight_scale_inv or param is self.w2_weight_scale_inv
+        bn = self.quant_config.weight_block_size[0] if is_scale else 1
+        half = (self.intermediate_size_per_partition + bn - 1) // bn
+        for slot in self.local_slots_of(expert_id):
+            dst = param.data[slot]
+            if shard_id != "w2":
+                dst = dst.narrow(0, 0 if shard_id == "w1" else half, half)
+            if tuple(dst.shape) != tuple(loaded_weight.shape):
+                raise ValueError(f"{weight_name}: checkpoint tensor of shape {tuple(loaded_weight.shape)} for a "
+                                 f"parameter slice of shape {tuple(dst.shape)}")
+            if dst.dtype == torch.float8_e4m3fn:
+                if loaded_weight.dtype != torch.float8_e4m3fn:
+                    raise ValueError(f"{weight_name}: the layer wants serialized float8_e4m3fn, got {loaded_weight.dtype}")
+                dst.view(torch.uint8).copy_(loaded_weight.view(torch.uint8))
+            else:
+                dst.copy_(loaded_weight)
 
     def load_full_weights(self, w13, w13_s, w2, w2_s) -> None:
         """Takes this rank's experts out of tensors that hold ALL logical experts."""

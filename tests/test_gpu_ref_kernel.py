@@ -80,3 +80,58 @@ def test_op_surface_matches_reference_call(ref_mm):
     mine = torch.ops.sgl_kernel.fp8_blockwise_scaled_mm.default(xq, wq.t(), a_s, ws.t(), torch.bfloat16)
     ref = ref_mm(xq, wq.t(), a_s, ws.t(), torch.bfloat16)
     assert torch.equal(mine.view(torch.int16), ref.view(torch.int16))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# the expert-grouped kernel
+# ------------------------------------------------------------------------------------------------------------------
+LIB_MOE = os.path.join(os.path.dirname(LIB), "libsgl_gpu_ref_moe.so")
+
+
+@pytest.fixture(scope="module")
+def ref_grouped():
+    """sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu compiled with its one-CTA tile configurations (oracle/Makefile,
+    target `ref_gpu_moe`): more than 2048 rows with K >= 2048 run its 128x128x128 tiles, K < 2048 its 64x128x128
+    tiles; at most 2048 rows with K >= 2048 would take the two-CTA cluster configuration, which is not built."""
+    if not os.path.exists(LIB_MOE):
+        pytest.skip("oracle/_ref/libsgl_gpu_ref_moe.so not built (make -C oracle ref_gpu_moe)")
+    torch.ops.load_library(LIB_MOE)
+    return torch.ops.sgl_gpu_ref.fp8_blockwise_scaled_grouped_mm
+
+
+@pytest.mark.parametrize("E,R,N,K", [(8, 2600, 512, 2048), (16, 4096, 1024, 768), (8, 300, 256, 512),
+                                     (32, 6000, 1536, 2048), (4, 2100, 4096, 7168)])
+def test_grouped_bitwise_equal_to_reference_kernel(ref_grouped, E, R, N, K):
+    """Same arguments to both (the call of python/sglang/srt/layers/moe/cutlass_moe.py:179-198): per expert the rows
+    off_e .. off_e + M_e of `a` times that expert's [N, K] weights.  Neither kernel splits K, both add the per-slab
+    float32 partial products in ascending K order, so the outputs must agree bit for bit."""
+    import sglang_b200.sgl_kernel as sk
+    from sglang_b200 import ops
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(E * 1000 + R)
+    cuts = torch.sort(torch.randperm(R - 1, device=dev, generator=g)[: E - 1] + 1).values
+    offs = torch.cat([torch.zeros(1, device=dev, dtype=torch.int64), cuts, torch.tensor([R], device=dev)]).to(torch.int32)
+    counts = (offs[1:] - offs[:-1]).to(torch.int32)
+    assert int(counts.min()) >= 1 and int(counts.sum()) == R
+    x = torch.randn(R, K, device=dev, generator=g).bfloat16()
+    aq, a_s = ops.per_token_group_quant_fp8(x, 128)
+    w = torch.randn(E, N, K, device=dev, generator=g) * 0.02
+    blk = w.view(E, N // 128, 128, K // 128, 128)
+    ws = (blk.abs().amax(dim=(2, 4)) / 448.0).contiguous()
+    wq = (blk / ws[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(E, N, K).contiguous()
+    ps = torch.stack([counts, torch.full_like(counts, N), torch.full_like(counts, K)], dim=1).contiguous()
+    i64 = dict(dtype=torch.int64, device=dev)
+    ptrs = [torch.empty(E, **i64) for _ in range(5)]
+    ab, cs = torch.full((E,), K, **i64), torch.full((E,), N, **i64)
+    lay_a, lay_b = (torch.empty(E, 5, dtype=torch.int32, device=dev) for _ in range(2))
+    work = torch.empty(90000, device=dev, dtype=torch.uint8)
+    out_ref = torch.zeros(R, N, device=dev, dtype=torch.bfloat16)
+    out = torch.zeros(R, N, device=dev, dtype=torch.bfloat16)
+    args = (*ptrs, aq, wq.transpose(1, 2), a_s, ws.transpose(1, 2), ab, ab, cs, lay_a, lay_b, ps, offs[:-1].contiguous(), work)
+    ref_grouped(out_ref, *args)
+    sk.fp8_blockwise_scaled_grouped_mm(out, *args)
+    torch.cuda.synchronize()
+    assert ops.gemm_status() == 0
+    assert torch.allclose(out.float(), out_ref.float(), rtol=2 ** -7, atol=2e-3)
+    differ = (out.view(torch.int16) != out_ref.view(torch.int16)).float().mean().item()
+    assert differ == 0.0, f"{differ:.2e} of the outputs differ in their bf16 bits"
