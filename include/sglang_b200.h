@@ -78,6 +78,22 @@ int sglb200_silu_and_mul_quant_fp8(const void* input, int dtype, void* output_q,
                                    int64_t d, int group_size, float eps, const int32_t* num_rows_dev, void* stream);
 
 /*
+ * The same fusion over the masked expert layout: input [num_experts, rows_per_expert, 2d] (bf16/fp16), of which only
+ * the first masked_m[e] rows of expert e hold data (masked_m: device int32 [num_experts], values clamped to
+ * [0, rows_per_expert]); output_q [num_experts, rows_per_expert, d], output_s [num_experts, rows_per_expert,
+ * d/group_size] float32, both contiguous.  Rows beyond masked_m[e] are neither read nor written.
+ * Replaces: silu_and_mul_masked_post_quant_fwd with scale_ue8m0=False
+ *   (python/sglang/srt/layers/moe/ep_moe/kernels.py:287-420), the float32-scale form of the layout that
+ *   sgl_per_token_group_quant_8bit_v2's MaskedLayoutScheduler walks
+ *   (sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:194-238; that CUDA kernel is instantiated for UE8M0 scales
+ *   only, :463-471, which this library does not produce).
+ * At most 1024 experts per call.
+ */
+int sglb200_silu_and_mul_masked_quant_fp8(const void* input, int dtype, void* output_q, float* output_s,
+                                          int num_experts, int64_t rows_per_expert, int64_t d, int group_size,
+                                          float eps, const int32_t* masked_m, void* stream);
+
+/*
  * Counting sort of flat topk_ids into block-padded expert segments; deterministic: within an expert,
  * entries keep ascending flat index.  Ids are shifted by +1 so that id -1 lands in bucket 0 and is
  * reported as expert -1; `num_experts` here is the bucket count, i.e. (model experts + 1), exactly
@@ -232,7 +248,7 @@ int sglb200_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, 
  *   w8a8_block_fp8_matmul (python/sglang/srt/layers/quantization/fp8_kernel.py:1072-1168, Triton kernel :695-777).
  * A [M,K] e4m3 row-major; B [N,K] e4m3 row-major (the checkpoint layout of `weight`);
  * a_s element (m,kb) at a_s[m*as_stride_m + kb*as_stride_k]; b_s [ceil(N/128), ceil(K/128)] row-major;
- * C [M,N] row-major, out_dtype 0 = bf16, 1 = fp16.  K % 16 == 0, N % 8 == 0; A, B, C 16-byte aligned.
+ * C [M,N] row-major, out_dtype 0 = bf16, 1 = fp16.  K % 16 == 0, K <= 65536, N % 8 == 0; A, B, C 16-byte aligned.
  * bias (optional, may be NULL): [N] of out_dtype, added in float32 before the final rounding.
  * workspace: only used for the split-K path chosen for small M; at least
  * sglb200_gemm_workspace_bytes(M,N,K) bytes (0 means none needed).

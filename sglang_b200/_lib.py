@@ -29,6 +29,7 @@ SIGNATURES = {
     "sglb200_per_token_group_quant_fp8": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _i32, _f32, _f32, _f32, _i64, _i64, _vp]),
     "sglb200_silu_and_mul": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp]),
     "sglb200_silu_and_mul_quant_fp8": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp]),
+    "sglb200_silu_and_mul_masked_quant_fp8": (_i32, [_vp, _i32, _vp, _vp, _i32, _i64, _i64, _i32, _f32, _vp, _vp]),
     "sglb200_moe_align_workspace_bytes": (_i64, [_i64, _i32]),
     "sglb200_moe_align_block_size": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp]),
     "sglb200_moe_align_set_cooperative": (None, [_i32]),

@@ -16,15 +16,20 @@
 //     accumulators with the slab's scale a_s[m,kb]*b_s[nb,kb] (DeepSeek-style 128-block float scales cannot be
 //     folded into the hardware's power-of-two MX scaling, so promotion runs on the CUDA cores, overlapped with
 //     the next slabs' MMAs through the TMEM buffers), two columns per instruction (packed float32 FMA).  A
-//     thread's activation scales are prefetched into registers four slabs at a time; the weight-block scales of
-//     the tile are staged by each warp for itself in its own strip of shared memory, so the slab loop has no
-//     barrier between warps.
+//     thread's activation scales are prefetched into registers four slabs at a time; the slab loop has no
+//     barrier between warps;
+//   * warp 3 (the scout) runs one unit ahead of the promotion warps and leaves, in one of two descriptor slots in
+//     shared memory, the next unit's tile coordinates, K range, weight-block scales and the activation scales of its
+//     first four slabs, so that a promotion warp starts a unit with shared-memory reads instead of integer divisions
+//     and exposed global loads (per tile that start cost as much as a slab and a half of MMAs);
+//   * warp 2 (one elected lane) hands finished tiles to the TMA engine: the promotion threads park their rounded
+//     part of a tile in shared memory and arrive on an mbarrier, never waiting for each other or for a store.
 // The kernel runs latency-, power- and issue-limited rather than tensor-limited (the tensor pipe is busy 40-50 %
 // of the cycles): every instruction a promotion warp executes or a waiting warp spends polling costs time,
 // so the per-slab loops are kept short, waits suspend in hardware (mbarrier.try_wait with a time hint) and
 // each promotion warp owns as many columns as the register file allows (fewer warps = less per-slab overhead).
-// The epilogue rounds to bf16/fp16, parks the tile in swizzled shared memory and writes it with TMA
-// stores that drain during the next tile; in grouped "scatter" mode it multiplies by the routing
+// The epilogue rounds to bf16/fp16, parks the tile in swizzled shared memory, from where TMA stores drain it
+// during the next tile; in grouped "scatter" mode it multiplies by the routing
 // weight and writes 16 bytes at a time to the token-major row named by sorted_token_ids.
 // Scheduling: with fewer than two waves of tiles and a long K the tiles x slabs space is cut into one equal run
 // of slabs per SM (stream-K; a run covers the end of one tile, possibly a whole tile, and the start of the next);
@@ -33,8 +38,9 @@
 // stored through the tensor map of the staging buffer of the GPU that owns its rows, which folds the
 // reduce-scatter of the all-reduce into the epilogue.
 //
-// Every mbarrier wait is bounded; on expiry the role raises a flag in shared memory that the other waiters poll,
-// the CTA sets a status word, drains, frees its TMEM and returns (sglb200_gemm_status() reports it).
+// Every mbarrier wait is bounded; on expiry the role raises a flag in shared memory and leaves its loops, the other
+// roles sit out their own limits, the CTA sets a status word, drains, frees its TMEM and returns
+// (sglb200_gemm_status() reports it).
 #include <cuda.h>
 
 #include <mutex>
@@ -58,6 +64,23 @@ constexpr uint32_t kTileBytesA = BM * BK;  // fp8
 // diagnostic setting) makes every wait give up at once, which exercises the give-up path on a healthy GPU.
 // (Measured: also polling the CTA's abort flag between runs of probes, so that one role's expiry ends the others'
 // waits early, cost 5 % of the large-M rate; each role sits out its own limit instead.)
+// Measurement builds (-DSGLB_TRACE): clock stamps of one promotion warp per column group of CTA 0, per unit.
+#ifdef SGLB_TRACE
+constexpr int kTraceUnits = 64, kTraceStamps = 8;
+__device__ long long g_trace[3][kTraceUnits][kTraceStamps];  // [2] = the scout warp
+#define SGLB_SCOUT_STAMP(i)                                                                             \
+  do {                                                                                                  \
+    if (blockIdx.x == 0 && lane == 0 && scout_unit < kTraceUnits) g_trace[2][scout_unit][i] = clock64(); \
+  } while (0)
+#define SGLB_STAMP(i)                                                                                  \
+  do {                                                                                                 \
+    if (blockIdx.x == 0 && q == 0 && lane == 0 && trace_unit < kTraceUnits) g_trace[cgrp][trace_unit][i] = clock64(); \
+  } while (0)
+#else
+#define SGLB_STAMP(i)
+#define SGLB_SCOUT_STAMP(i)
+#endif
+
 #define SGLB_WAIT(bar, parity) (p.wait_probes != ptx::kProbesNone && ptx::mbar_wait_quiet(bar, parity))
 #ifndef SGLB_FMA2
 #define SGLB_FMA2 1                        // promotion with packed float32 FMAs (two columns per instruction)
@@ -126,15 +149,29 @@ struct GemmParams {
   uint32_t wait_probes;          // probes after which a pipeline wait gives up
 };
 
-constexpr int kBChunk = 256;  // slabs of weight-block scales a promotion warp stages at a time
+constexpr int kDescSlabs = 512;  // K slabs of one unit whose weight-block scales a unit descriptor holds (K <= 65536)
+
+// What the scout warp prepares for the promotion warps while they work on the previous unit: where the unit lies and
+// the scales its first slabs need, so that a promotion warp starts a unit with a few shared-memory reads instead of
+// integer divisions and global loads whose latency nothing hides.
+struct UnitDesc {
+  float a4[BM][4];          // activation scales of the unit's first four slabs, per tile row
+  float b[2][kDescSlabs];   // weight-block scales of the unit's slabs for the (at most two) 128-column blocks of the tile
+  int m_tile, n_tile, expert, kb_begin;
+  int kb_stop, split, slot, pad;
+};
 
 template <class Cfg>
 struct SharedCtl {
-  float b_stage[kEpiWarps][2][kBChunk];  // per promotion warp: [weight block within the tile][slab]
+  UnitDesc desc[2];
+  uint64_t desc_full[2];   // the descriptor is written (every scout lane arrives)
+  uint64_t desc_empty[2];  // every promotion thread has read what it needs from it
   uint64_t full[Cfg::kStages];
   uint64_t empty[Cfg::kStages];
   uint64_t tmem_full[Cfg::kAccBufs];
   uint64_t tmem_empty[Cfg::kAccBufs];
+  uint64_t out_full;  // the output staging holds a rounded tile (every promotion thread arrives)
+  uint64_t out_free;  // the TMA stores of the previous tile have read the staging (the storing thread arrives)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -264,6 +301,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[b]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), kEpiWarps);
     }
+    for (int d = 0; d < 2; ++d) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->desc_full[d]), 32);
+      ptx::mbar_init(ptx::smem_u32(&ctl->desc_empty[d]), kEpiThreads);
+    }
+    ptx::mbar_init(ptx::smem_u32(&ctl->out_full), kEpiThreads);
+    ptx::mbar_init(ptx::smem_u32(&ctl->out_free), 1);
     ctl->abort_flag = 0;
     ptx::mbar_fence_init();
     ptx::tma_prefetch_desc(&map_a);
@@ -277,6 +320,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+  const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
+                          (reinterpret_cast<uintptr_t>(p.a_s) & 15u) == 0;
+  // activation scales of slabs kb .. kb+3 of the row `a_row` points at (zero past the last slab)
+  auto load_a4_row = [&](const float* a_row, int kb) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (vec_scales && kb + 3 < kb_total && (kb & 3) == 0) {
+      v = __ldg(reinterpret_cast<const float4*>(a_row + kb));
+    } else {
+      if (kb + 0 < kb_total) v.x = __ldg(a_row + (int64_t)(kb + 0) * p.as_stride_k);
+      if (kb + 1 < kb_total) v.y = __ldg(a_row + (int64_t)(kb + 1) * p.as_stride_k);
+      if (kb + 2 < kb_total) v.z = __ldg(a_row + (int64_t)(kb + 2) * p.as_stride_k);
+      if (kb + 3 < kb_total) v.w = __ldg(a_row + (int64_t)(kb + 3) * p.as_stride_k);
+    }
+    return v;
+  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -360,57 +418,184 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
     }
+  } else if (warp == 2) {
+    // ------------------------------ output stores ------------------------------
+    // One thread hands every finished tile to the TMA engine: it waits until all promotion threads have parked their
+    // part of the tile in the staging area, issues the stores, waits until they have read the staging and gives it
+    // back.  The promotion warps never wait for each other or for a store to be issued: each goes on to its next
+    // unit as soon as its own part is parked.
+    if (p.tma_out && ptx::elect_one()) {
+      const uint32_t bar_out_full = ptx::smem_u32(&ctl->out_full), bar_out_free = ptx::smem_u32(&ctl->out_free);
+      uint32_t oph = 0;
+      for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+        const Unit un = decode_unit<kGrouped>(p, u);
+        if (un.kb_begin >= un.kb_stop || un.split) continue;
+        if (!SGLB_WAIT(bar_out_full, oph)) {
+          *abort_flag = 1;
+          break;
+        }
+        oph ^= 1u;
+        if (*abort_flag == 0) {  // (after a give-up the tile is incomplete: nothing is stored)
+          int m_tile, n_tile;
+          tile_coord(un.tile, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
+          const int n_end = (int)min((int64_t)n_tile * BN + BN, p.N);
+          const CUtensorMap* cmap = &map_c;
+          int out_row0 = m_tile * BM;
+          if (p.push_maps != nullptr) {
+            const int owner = out_row0 / p.push_rows_per_owner;
+            cmap = p.push_maps + owner;
+            out_row0 += (p.push_rank - owner) * p.push_rows_per_owner;
+          }
+#pragma unroll
+          for (int g = 0; g < kOutGroups; ++g) {
+            if (n_tile * BN + g * 64 < n_end)
+              ptx::tma_store_2d(cmap, ptx::smem_u32(out_stage) + g * kOutGroupBytes, n_tile * BN + g * 64, out_row0);
+          }
+          ptx::tma_store_commit();
+        }
+        ptx::tma_store_wait_read();
+        ptx::mbar_arrive(bar_out_free);
+      }
+      // tiles pushed to other GPUs have landed before the kernel counts as finished
+      if (p.push_maps != nullptr) ptx::tma_store_wait_all();
+    }
+  } else if (warp == 3) {
+    // ------------------------------ unit scout ------------------------------
+    // Walks the CTA's units one ahead of the promotion warps and leaves a descriptor of each in one of two slots:
+    // tile coordinates and K range (every unit, empty stream-K pieces included, so that the two sides count alike),
+    // and for units with work the activation scales of the first four slabs of all 128 rows and the unit's
+    // weight-block scales.  All 32 lanes probe the same barrier word, so the outcome of a wait is uniform.
+    const uint32_t bar_dfull0 = ptx::smem_u32(&ctl->desc_full[0]), bar_dempty0 = ptx::smem_u32(&ctl->desc_empty[0]);
+    uint32_t ds = 0, dph = 0;
+#ifdef SGLB_TRACE
+    int scout_unit = -1;
+#endif
+    for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+#ifdef SGLB_TRACE
+      ++scout_unit;
+#endif
+      SGLB_SCOUT_STAMP(0);
+      if (!SGLB_WAIT(bar_dempty0 + ds * 8, dph ^ 1u)) {
+        *abort_flag = 1;
+        break;
+      }
+      SGLB_SCOUT_STAMP(1);
+      const Unit un = decode_unit<kGrouped>(p, u);
+      UnitDesc* d = &ctl->desc[ds];
+      int m_tile = 0, n_tile = 0, e = 0;
+      const bool work = un.kb_begin < un.kb_stop;
+      if (work) {
+        tile_coord(un.tile, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
+        if (kGrouped) e = p.expert_ids[m_tile];
+      }
+      if (lane == 0) {
+        d->m_tile = m_tile, d->n_tile = n_tile, d->expert = e, d->kb_begin = un.kb_begin;
+        d->kb_stop = un.kb_stop, d->split = un.split ? 1 : 0, d->slot = un.slot, d->pad = 0;
+      }
+      SGLB_SCOUT_STAMP(2);
+      if (work && e >= 0) {
+        // every load of the descriptor is requested before the first value is stored: one round trip to L2, not one
+        // per row
+        const int nb_tile = min(n_tile * BN / kScaleBlockN, p.nb_total - 1);
+        const float* b_row0 = p.b_s + ((int64_t)e * p.nb_total + nb_tile) * kb_total + un.kb_begin;
+        const float* b_row1 = p.b_s + ((int64_t)e * p.nb_total + min(nb_tile + 1, p.nb_total - 1)) * kb_total + un.kb_begin;
+        const int n = min(un.kb_stop - un.kb_begin, kDescSlabs);
+        float4 av[BM / 32];
+        float bv0[4], bv1[4];
+#pragma unroll
+        for (int k = 0; k < BM / 32; ++k) {
+          const int64_t row = (int64_t)m_tile * BM + lane + 32 * k;  // rows past M read a valid row; never stored
+          av[k] = load_a4_row(p.a_s + min(row, rows - 1) * p.as_stride_m, un.kb_begin);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i = lane + 32 * k;
+          bv0[k] = i < n ? __ldg(b_row0 + i) : 0.f;
+          bv1[k] = i < n ? __ldg(b_row1 + i) : 0.f;
+        }
+        const uint32_t d_addr = ptx::smem_u32(d);
+#pragma unroll
+        for (int k = 0; k < BM / 32; ++k)
+          ptx::sts_128(d_addr + (uint32_t)offsetof(UnitDesc, a4) + (uint32_t)(lane + 32 * k) * 16u,
+                       make_uint4(__float_as_uint(av[k].x), __float_as_uint(av[k].y), __float_as_uint(av[k].z),
+                                  __float_as_uint(av[k].w)));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i = lane + 32 * k;
+          if (i < n) {
+            d->b[0][i] = bv0[k];
+            d->b[1][i] = bv1[k];
+          }
+        }
+        for (int i = lane + 128; i < n; i += 32) {  // (K beyond 16384)
+          d->b[0][i] = __ldg(b_row0 + i);
+          d->b[1][i] = __ldg(b_row1 + i);
+        }
+      }
+      ptx::mbar_arrive(bar_dfull0 + ds * 8);  // every lane: its own writes are released with its arrival
+      SGLB_SCOUT_STAMP(3);
+      if (++ds == 2u) {
+        ds = 0;
+        dph ^= 1u;
+      }
+    }
   } else if (warp >= kEpiWarp0) {
     // ------------------------------ promotion + epilogue ------------------------------
     // A thread that sees the abort flag keeps walking the same loops (without waiting or touching TMEM) so
-    // that the named barrier below always collects all kEpiThreads arrivals.
+    // that the storing thread always collects all kEpiThreads arrivals per tile.
     const int q = warp & 3;                     // TMEM lane quadrant this warp may read
     const int cgrp = (warp - kEpiWarp0) >> 2;   // column group: columns cgrp*kEpiCols .. of the tile
     constexpr int kPiecesMax = kEpiCols / 32;
-    const int ep_tid = threadIdx.x - kEpiWarp0 * 32;
     const int row_in_tile = q * 32 + lane;
-    const bool vec_scales = p.as_stride_k == 1 && (p.as_stride_m & 3) == 0 &&
-                            (reinterpret_cast<uintptr_t>(p.a_s) & 15u) == 0;
     const uint32_t bar_tfull0 = ptx::smem_u32(&ctl->tmem_full[0]), bar_tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
     const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + cgrp * kEpiCols;
-    uint32_t buf = 0, aph = 0;
+    const uint32_t bar_out_full = ptx::smem_u32(&ctl->out_full), bar_out_free = ptx::smem_u32(&ctl->out_free);
+    const uint32_t bar_dfull0 = ptx::smem_u32(&ctl->desc_full[0]), bar_dempty0 = ptx::smem_u32(&ctl->desc_empty[0]);
+    const uint32_t desc_addr0 = ptx::smem_u32(&ctl->desc[0]);
+    uint32_t buf = 0, aph = 0, oph = 0, ds = 0, dph = 0;
     bool alive = true;
-    // activation scales of slabs kb .. kb+3 of the row `a_row` points at (zero past the last slab)
-    auto load_a4_row = [&](const float* a_row, int kb) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (vec_scales && kb + 3 < kb_total && (kb & 3) == 0) {
-        v = __ldg(reinterpret_cast<const float4*>(a_row + kb));
-      } else {
-        if (kb + 0 < kb_total) v.x = __ldg(a_row + (int64_t)(kb + 0) * p.as_stride_k);
-        if (kb + 1 < kb_total) v.y = __ldg(a_row + (int64_t)(kb + 1) * p.as_stride_k);
-        if (kb + 2 < kb_total) v.z = __ldg(a_row + (int64_t)(kb + 2) * p.as_stride_k);
-        if (kb + 3 < kb_total) v.w = __ldg(a_row + (int64_t)(kb + 3) * p.as_stride_k);
-      }
-      return v;
-    };
-    // (Measured: requesting a short unit's first scales one unit ahead, before the previous unit's epilogue, moves
-    // dense shapes by -2..+6 % and costs the grouped form 4-8 %; not kept.)
+#ifdef SGLB_TRACE
+    int trace_unit = -1;
+#endif
     for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
-      const Unit un = decode_unit<kGrouped>(p, u);
-      const int t = un.tile, kb_begin = un.kb_begin, kb_stop = un.kb_stop;
-      if (kb_begin >= kb_stop) continue;  // (an empty second piece of a stream-K run; uniform over the CTA)
-      int m_tile, n_tile;
-      tile_coord(t, tiles_m, tiles_n, p.group_m, m_tile, n_tile);
+#ifdef SGLB_TRACE
+      ++trace_unit;
+#endif
+      SGLB_STAMP(0);
+      // the unit as the scout warp described it (without a descriptor there is nothing to walk: leave)
+      if (!SGLB_WAIT(bar_dfull0 + ds * 8, dph)) {
+        *abort_flag = 1;
+        break;
+      }
+      const uint32_t desc_addr = desc_addr0 + ds * (uint32_t)sizeof(UnitDesc);
+      // the descriptor is handed back (by every thread) once nothing more is read from it
+      auto release_desc = [&]() {
+        ptx::mbar_arrive(bar_dempty0 + ds * 8);
+        if (++ds == 2u) {
+          ds = 0;
+          dph ^= 1u;
+        }
+      };
+      const float4 h0 = ptx::lds_f32x4(desc_addr + (uint32_t)offsetof(UnitDesc, m_tile));
+      const int m_tile = __float_as_int(h0.x), n_tile = __float_as_int(h0.y), kb_begin = __float_as_int(h0.w);
+      const int kb_stop = __float_as_int(ptx::lds_f32(desc_addr + (uint32_t)offsetof(UnitDesc, kb_stop)));
+      if (kb_begin >= kb_stop) {  // (an empty piece of a stream-K run; uniform over the CTA)
+        release_desc();
+        continue;
+      }
       const int64_t row = (int64_t)m_tile * BM + row_in_tile;
       const int n0 = n_tile * BN + cgrp * kEpiCols;            // first of this warp's columns
       const int n_end = (int)min((int64_t)n_tile * BN + BN, p.N);  // one past the tile's last valid column
-      int e = 0;
-      if (kGrouped) e = p.expert_ids[m_tile];
+      const int e = kGrouped ? __float_as_int(h0.z) : 0;
       float acc[kEpiCols];
 #pragma unroll
       for (int j = 0; j < kEpiCols; ++j) acc[j] = 0.f;
       if (e >= 0) {
-        // Activation scales live in registers: per group of four slabs a thread loads the four scales of its row,
-        // and the load for the next group is issued before the current group is promoted, a few thousand cycles
-        // ahead of its use.  The weight-block scales (uniform across a warp: at most two 128-wide blocks per
-        // tile, one value per slab each) are staged by every warp for itself, in its own strip of shared memory,
-        // once per unit: no barrier between warps.  (Staging both kinds for the whole CTA cost two CTA-wide
-        // barriers per group of slabs and kept the eight promotion warps in lock step.)
+        // Activation scales live in registers: the four scales of a thread's row for the unit's first four slabs come
+        // from the descriptor; per later group of four slabs the thread loads them itself, the load for the next
+        // group issued before the current group is promoted, a few thousand cycles ahead of its use.  The
+        // weight-block scales (uniform across a warp: at most two 128-wide blocks per tile, one value per slab each)
+        // are read from the descriptor slab by slab.  No barrier between the promotion warps.
         // A 32-column piece never straddles a weight block; a piece wholly past N is clamped to the last block.
         const int nb_tile = min(n_tile * BN / kScaleBlockN, p.nb_total - 1);
         bool piece_in_blk1[kPiecesMax];
@@ -418,34 +603,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int i = 0; i < kPiecesMax; ++i)
           piece_in_blk1[i] = min((n0 + 32 * i) / kScaleBlockN, p.nb_total - 1) != nb_tile;
         const float* a_row = p.a_s + min(row, rows - 1) * p.as_stride_m;  // rows past M read a valid row; never stored
-        const float* b_row0 = p.b_s + ((int64_t)e * p.nb_total + nb_tile) * kb_total;
-        const float* b_row1 = p.b_s + ((int64_t)e * p.nb_total + min(nb_tile + 1, p.nb_total - 1)) * kb_total;
-        float* b_strip = &ctl->b_stage[warp - kEpiWarp0][0][0];
-        auto stage_b = [&](int kb0) {  // weight-block scales of slabs kb0 .. kb0 + kBChunk - 1
-          __syncwarp();
-          for (int i = lane; i < kBChunk; i += 32) {
-            const int kb = kb0 + i;
-            b_strip[i] = kb < kb_stop ? __ldg(b_row0 + kb) : 0.f;
-            b_strip[kBChunk + i] = kb < kb_stop ? __ldg(b_row1 + kb) : 0.f;
-          }
-          __syncwarp();
-        };
         auto load_a4 = [&](int kb) { return load_a4_row(a_row, kb); };
-        float4 a_cur = load_a4(kb_begin), a_nxt = a_cur;
+        float4 a_cur = ptx::lds_f32x4(desc_addr + (uint32_t)offsetof(UnitDesc, a4) + (uint32_t)row_in_tile * 16u);
+        float4 a_nxt = a_cur;
         const int n_slabs = kb_stop - kb_begin;
-        uint32_t b_addr = 0;
+        uint32_t b_addr = desc_addr + (uint32_t)offsetof(UnitDesc, b);
+        SGLB_STAMP(1);
         for (int g = 0; g < n_slabs; ++g) {
           const int j = g & 3;
-          if ((g & (kBChunk - 1)) == 0) {
-            stage_b(kb_begin + g);
-            b_addr = ptx::smem_u32(b_strip);
-          }
           if (j == 0) {
             if (g > 0) a_cur = a_nxt;
             if (g + 4 < n_slabs) a_nxt = load_a4(kb_begin + g + 4);
           }
           const float a_sc = j == 0 ? a_cur.x : j == 1 ? a_cur.y : j == 2 ? a_cur.z : a_cur.w;
-          const float sc0 = a_sc * ptx::lds_f32(b_addr), sc1 = a_sc * ptx::lds_f32(b_addr + kBChunk * 4);
+          const float sc0 = a_sc * ptx::lds_f32(b_addr), sc1 = a_sc * ptx::lds_f32(b_addr + kDescSlabs * 4);
           b_addr += 4;
           // (the 32 lanes probe the same word in the same instruction, so the outcome is uniform across the
           // warp, as the warp-wide tcgen05.ld below requires)
@@ -485,7 +656,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
+      // (whether the unit is a piece of a split tile, and its slot among the partial sums, are read only now: two
+      // registers fewer across the slab loop)
+      Unit un;
+      {
+        const float4 h1 = ptx::lds_f32x4(desc_addr + (uint32_t)offsetof(UnitDesc, kb_stop));
+        un.tile = 0, un.kb_begin = kb_begin, un.kb_stop = kb_stop;
+        un.split = __float_as_int(h1.y) != 0, un.slot = __float_as_int(h1.z);
+      }
+      release_desc();
       // ---- store ----
+      SGLB_STAMP(2);
       if (un.split) {
         // this unit's float32 partial sums, tile-local layout; a second kernel adds the units of a tile in a
         // fixed order, adds the bias and rounds once
@@ -511,13 +692,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (p.tma_out) {
         // Rows of C are contiguous: round to the output type, park the warp's 32 x 64 block in shared memory
         // (128-byte rows, 16-byte chunks XOR-swizzled by the row so that the 32 lanes of a store spread over
-        // all banks) and let one thread of the column group hand the 128 x 64 block to the TMA engine, which
-        // clips it to the tensor.  The store drains while the next tile is being promoted; its source is
-        // reclaimed at the next epilogue.
-        const bool issuer = (ep_tid == 0);
-        if (issuer) ptx::tma_store_wait_read();
-        // (a warp whose wait expired still joins both barriers; only the data movement is skipped)
-        asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+        // all banks); the storing thread (warp 2) hands the 128 x 64 blocks to the TMA engine, which clips them to
+        // the tensor.  The store drains while the next tile is being promoted.
+        // The staging area is free once the stores of the previous tile have read it (a thread whose wait expired
+        // skips the data movement and still arrives, so that the storing thread is released).
+        if (alive && !SGLB_WAIT(bar_out_free, oph ^ 1u)) {
+          *abort_flag = 1;
+          alive = false;
+        }
+        oph ^= 1u;
+        SGLB_STAMP(3);
         if (alive && n0 < n_end) {
           if (p.bias != nullptr) {
             // (tile columns past N are clipped by the store; their bias reads are clamped to stay in bounds)
@@ -551,24 +735,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             ptx::sts_128(stage0 + (col >> 6) * kOutGroupBytes + ((((col & 63) >> 3) ^ swz) << 4),
                          make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]));
           }
-          ptx::fence_async_smem();
+          ptx::fence_async_smem();  // this thread's part is visible to the TMA engine before it arrives
         }
-        asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
-        if (issuer && alive) {
-          const CUtensorMap* cmap = &map_c;
-          int out_row0 = m_tile * BM;
-          if (p.push_maps != nullptr) {
-            const int owner = out_row0 / p.push_rows_per_owner;
-            cmap = p.push_maps + owner;
-            out_row0 += (p.push_rank - owner) * p.push_rows_per_owner;
-          }
-#pragma unroll
-          for (int g = 0; g < kOutGroups; ++g) {
-            if (n_tile * BN + g * 64 < n_end)
-              ptx::tma_store_2d(cmap, ptx::smem_u32(out_stage) + g * kOutGroupBytes, n_tile * BN + g * 64, out_row0);
-          }
-          ptx::tma_store_commit();
-        }
+        SGLB_STAMP(4);
+        ptx::mbar_arrive(bar_out_full);
+        SGLB_STAMP(5);
+        SGLB_STAMP(6);
         continue;
       }
       if (!alive) continue;
@@ -596,12 +768,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 
   // ------------------------------ teardown ------------------------------
-  if (threadIdx.x == kEpiWarp0 * 32) {
-    if (p.push_maps != nullptr)
-      ptx::tma_store_wait_all();  // tiles pushed to other GPUs have landed before the kernel counts as finished
-    else
-      ptx::tma_store_wait_read();  // sources stay valid until read
-  }
+  // (the storing thread has waited for its last stores to read their source, in push mode to land, before it
+  // reaches the barrier below)
   ptx::tc_fence_before();
   __syncthreads();
   if (ctl->abort_flag != 0 && threadIdx.x == 0) {
@@ -1103,6 +1271,7 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, con
   SGLB_REQUIRE(M >= 0 && N > 0 && K > 0, "fp8_blockwise_scaled_mm: bad shape M=%lld N=%lld K=%lld", (long long)M,
                (long long)N, (long long)K);
   SGLB_REQUIRE(K % 16 == 0, "fp8_blockwise_scaled_mm: K=%lld must be a multiple of 16", (long long)K);
+  SGLB_REQUIRE(K <= (int64_t)kDescSlabs * BK, "fp8_blockwise_scaled_mm: K=%lld exceeds %d", (long long)K, kDescSlabs * BK);
   SGLB_REQUIRE(N % 8 == 0, "fp8_blockwise_scaled_mm: N=%lld must be a multiple of 8", (long long)N);
   SGLB_REQUIRE(out_dtype == 0 || out_dtype == 1, "fp8_blockwise_scaled_mm: out_dtype %d (0 bf16, 1 fp16)", out_dtype);
   if (M == 0) return SGLB200_OK;
@@ -1127,6 +1296,7 @@ extern "C" int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s,
   SGLB_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && num_experts >= 1, "grouped_mm: bad shape rows=%lld N=%lld K=%lld E=%d",
                (long long)max_rows, (long long)N, (long long)K, num_experts);
   SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, "grouped_mm: K must be a multiple of 16 and N of 8");
+  SGLB_REQUIRE(K <= (int64_t)kDescSlabs * BK, "grouped_mm: K=%lld exceeds %d", (long long)K, kDescSlabs * BK);
   SGLB_REQUIRE(out_dtype == 0 || out_dtype == 1, "grouped_mm: out_dtype %d (0 bf16, 1 fp16)", out_dtype);
   if (max_rows == 0) return SGLB200_OK;
   SGLB_REQUIRE(A && a_s && B && b_s && C && expert_ids && num_rows_dev, "grouped_mm: null pointer");
@@ -1252,6 +1422,7 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B
                (long long)K);
   SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, "mm_push: K=%lld must be a multiple of 16 and N=%lld of 8", (long long)K,
                (long long)N);
+  SGLB_REQUIRE(K <= (int64_t)kDescSlabs * BK, "mm_push: K=%lld exceeds %d", (long long)K, kDescSlabs * BK);
   SGLB_REQUIRE(out_dtype == 0 || out_dtype == 1, "mm_push: out_dtype %d (0 bf16, 1 fp16)", out_dtype);
   SGLB_REQUIRE(A && B && a_s && b_s && stage_ptrs, "mm_push: null pointer");
   for (int i = 0; i < world; ++i)
@@ -1263,3 +1434,10 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* A, const void* B
     return push_mm<128>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, sm_margin, st);
   return push_mm<192>(A, B, a_s, b_s, stage_ptrs, world, rank, M, N, K, as_stride_m, as_stride_k, out_dtype, sm_margin, st);
 }
+
+#ifdef SGLB_TRACE
+extern "C" int sglb200_debug_trace(void* host_buf, int64_t bytes) {
+  if (bytes != (int64_t)sizeof(long long) * 3 * kTraceUnits * kTraceStamps) return -1;
+  return cudaMemcpyFromSymbol(host_buf, g_trace, (size_t)bytes) == cudaSuccess ? 0 : -2;
+}
+#endif

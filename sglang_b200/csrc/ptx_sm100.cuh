@@ -82,6 +82,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
   return false;
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 // Arrive from the threads whose `pred` is set, without a branch around the instruction.
 __device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
   asm volatile(

@@ -336,38 +336,101 @@ struct Packed2<__half> {
 
 constexpr int kSiluStages = 2;  // 2 x (16 KB gate + 16 KB up) per CTA, three CTAs per SM (80 registers)
 
-template <typename T, int LPG>
+constexpr int kMaskedMaxExperts = 1024;  // experts of one masked call (four per thread in the tile count scan)
+
+// kMasked: the input is [experts, rows_per_expert, 2d] and only the first masked_m[e] rows of expert e are valid
+// (the layout of python/sglang/srt/layers/moe/ep_moe/kernels.py:287-361).  The valid rows of every expert are cut
+// into tiles of their own, numbered one expert after the other; rows beyond masked_m[e] are neither read nor written.
+template <typename T, int LPG, bool kMasked>
 __global__ void __launch_bounds__(kStreamThreads, 3)
     silu_mul_quant_stream_kernel(const T* __restrict__ x, uint8_t* __restrict__ out_q, float* __restrict__ out_s,
                                  int64_t rows, int d, const int32_t* __restrict__ num_rows_dev, float eps, float qmin,
-                                 float qmax, uint32_t probes) {
+                                 float qmax, uint32_t probes, const int32_t* __restrict__ masked_m, int num_experts,
+                                 int64_t rows_per_expert) {
   static_assert(sizeof(T) == 2, "16-bit inputs only");
   constexpr int CE = 8, NCH = 4, GC = LPG * NCH, G = LPG * kThreadElems;
   constexpr uint32_t kHalfBytes = kTileElems * 2;  // gate part of a stage; the up part follows it
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[kSiluStages];
   __shared__ int s_abort;
+  __shared__ int s_tiles_before[kMasked ? kMaskedMaxExperts + 1 : 1];  // tiles of the experts before e
+  __shared__ int s_warp_sum[kStreamThreads / 32];
   if (num_rows_dev != nullptr) {
     const int64_t lim = *num_rows_dev;
     rows = lim < rows ? lim : rows;
   }
   const uint32_t smem_base = ptx::smem_u32(smem_raw);
   const int tid = threadIdx.x;
-  const int64_t total_elems = rows * d;
-  const int64_t tiles = (total_elems + kTileElems - 1) / kTileElems;
+  int64_t total_elems = rows * d;
+  int64_t tiles = (total_elems + kTileElems - 1) / kTileElems;
+  auto valid_rows = [&](int e) -> int64_t {
+    const int64_t m = masked_m[e];
+    return m < 0 ? 0 : (m > rows_per_expert ? rows_per_expert : m);
+  };
+  if constexpr (kMasked) {
+    // exclusive scan of the experts' tile counts: four experts per thread, then the warps' sums
+    int cnt[4], mine = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int e = tid * 4 + k;
+      cnt[k] = e < num_experts ? (int)((valid_rows(e) * d + kTileElems - 1) / kTileElems) : 0;
+      mine += cnt[k];
+    }
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if ((tid & 31) >= o) incl += up;
+    }
+    if ((tid & 31) == 31) s_warp_sum[tid >> 5] = incl;
+    __syncthreads();
+    int before = incl - mine;
+    for (int w = 0; w < (tid >> 5); ++w) before += s_warp_sum[w];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int e = tid * 4 + k;
+      if (e < num_experts) s_tiles_before[e] = before;
+      before += cnt[k];
+    }
+    if (tid == kStreamThreads - 1) s_tiles_before[num_experts] = before;  // (experts beyond num_experts count 0)
+    __syncthreads();
+    tiles = s_tiles_before[num_experts];
+  }
   if ((int64_t)blockIdx.x >= tiles) return;  // the grid is sized from the host-side bound on rows
   const int64_t my_tiles = (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
+  // tile i of this CTA: first element within its expert (or within the whole input), that range's element count, and
+  // the range's first row
+  auto locate = [&](int64_t i, int64_t& e0, int64_t& lim, int64_t& row_base) {
+    const int64_t gt = blockIdx.x + i * gridDim.x;
+    if constexpr (kMasked) {
+      int lo = 0, hi = num_experts;  // the expert with s_tiles_before[e] <= gt < s_tiles_before[e + 1]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((int64_t)s_tiles_before[mid] <= gt) lo = mid; else hi = mid;
+      }
+      e0 = (gt - s_tiles_before[lo]) * (int64_t)kTileElems;
+      lim = valid_rows(lo) * d;
+      row_base = (int64_t)lo * rows_per_expert;
+    } else {
+      e0 = gt * (int64_t)kTileElems;
+      lim = total_elems;
+      row_base = 0;
+    }
+  };
+
   auto issue = [&](int64_t i) {  // thread 0 only
     const int slot = (int)(i % kSiluStages);
-    const int64_t e0 = (blockIdx.x + i * gridDim.x) * (int64_t)kTileElems;
-    const int64_t left = total_elems - e0;
+    int64_t e0, lim, row_base;
+    locate(i, e0, lim, row_base);
+    const int64_t left = lim - e0;
     const int n = left >= kTileElems ? kTileElems : (int)left;
     const uint32_t bar = ptx::smem_u32(&bars[slot]);
     const uint32_t dst = smem_base + slot * (2 * kHalfBytes);
     ptx::mbar_arrive_expect_tx(bar, (uint32_t)n * 4u);
     int64_t r = e0 / d;
     int c = (int)(e0 - r * d);
+    r += row_base;
     for (int off = 0; off < n;) {
       const int seg = (d - c) < (n - off) ? (d - c) : (n - off);
       const T* row = x + r * 2 * (int64_t)d + c;
@@ -428,9 +491,11 @@ __global__ void __launch_bounds__(kStreamThreads, 3)
     uint32_t codes[NCH][CE / 4];
     const float scale = quant_group<T, LPG, true>(hraw, v, eps, qmin, qmax, codes);
 
-    const int64_t e0 = (blockIdx.x + i * gridDim.x) * (int64_t)kTileElems;
-    const int64_t ge = e0 + (int64_t)g_local * G;
-    if (ge < total_elems) {
+    int64_t e0, lim, row_base;
+    locate(i, e0, lim, row_base);
+    const int64_t ge_in = e0 + (int64_t)g_local * G;
+    if (ge_in < lim) {
+      const int64_t ge = row_base * d + ge_in;
 #pragma unroll
       for (int j = 0; j < NCH; ++j)
         *reinterpret_cast<uint2*>(out_q + ge + cj[j] * CE) = make_uint2(codes[j][0], codes[j][1]);
@@ -483,19 +548,35 @@ static int launch_quant(const void* input, void* output_q, float* output_s, int6
 #undef SGLB_LAUNCH_Q
 }
 
-template <typename T, int LPG>
-static int launch_silu_mul_quant_inst(const void* input, void* output_q, float* output_s, int64_t rows, int64_t d,
-                                      float eps, const int32_t* num_rows_dev, cudaStream_t stream) {
+template <typename T, int LPG, bool kMasked>
+static int launch_silu_mul_quant_kernel(const void* input, void* output_q, float* output_s, int64_t rows, int64_t d,
+                                        float eps, const int32_t* num_rows_dev, const int32_t* masked_m,
+                                        int num_experts, int64_t rows_per_expert, cudaStream_t stream) {
   constexpr size_t smem = (size_t)kSiluStages * 2 * kTileElems * sizeof(T);
-  auto kern = silu_mul_quant_stream_kernel<T, LPG>;
+  auto kern = silu_mul_quant_stream_kernel<T, LPG, kMasked>;
   SGLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int64_t tiles = (rows * d + kTileElems - 1) / kTileElems;
+  // (masked: every expert's last tile may be partial, so the bound counts the experts' tiles one by one)
+  const int64_t tiles = kMasked ? (int64_t)num_experts * ((rows_per_expert * d + kTileElems - 1) / kTileElems)
+                                : (rows * d + kTileElems - 1) / kTileElems;
   const int64_t resident = (int64_t)sm_count() * 3;
   const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
   kern<<<grid, kStreamThreads, smem, stream>>>(static_cast<const T*>(input), static_cast<uint8_t*>(output_q), output_s,
-                                               rows, (int)d, num_rows_dev, eps, -448.0f, 448.0f, g_stream_wait_probes);
+                                               rows, (int)d, num_rows_dev, eps, -448.0f, 448.0f, g_stream_wait_probes,
+                                               masked_m, num_experts, rows_per_expert);
   SGLB_CUDA(cudaGetLastError());
   return SGLB200_OK;
+}
+
+template <typename T, int LPG>
+static int launch_silu_mul_quant_inst(const void* input, void* output_q, float* output_s, int64_t rows, int64_t d,
+                                      float eps, const int32_t* num_rows_dev, cudaStream_t stream,
+                                      const int32_t* masked_m = nullptr, int num_experts = 0,
+                                      int64_t rows_per_expert = 0) {
+  if (masked_m != nullptr)
+    return launch_silu_mul_quant_kernel<T, LPG, true>(input, output_q, output_s, rows, d, eps, nullptr, masked_m,
+                                                      num_experts, rows_per_expert, stream);
+  return launch_silu_mul_quant_kernel<T, LPG, false>(input, output_q, output_s, rows, d, eps, num_rows_dev, nullptr, 0, 0,
+                                                     stream);
 }
 
 template <typename T>
@@ -512,9 +593,54 @@ static int launch_silu_mul_quant(const void* input, void* output_q, float* outpu
   }
 }
 
+template <typename T>
+static int launch_silu_mul_quant_masked(const void* input, void* output_q, float* output_s, int num_experts,
+                                        int64_t rows_per_expert, int64_t d, int group_size, float eps,
+                                        const int32_t* masked_m, cudaStream_t stream) {
+  const int64_t rows = (int64_t)num_experts * rows_per_expert;
+#define SGLB_MASKED(LPG)                                                                                         \
+  return launch_silu_mul_quant_inst<T, LPG>(input, output_q, output_s, rows, d, eps, nullptr, stream, masked_m, \
+                                            num_experts, rows_per_expert)
+  switch (group_size) {
+    case 32: SGLB_MASKED(1);
+    case 64: SGLB_MASKED(2);
+    case 128: SGLB_MASKED(4);
+    case 256: SGLB_MASKED(8);
+    default: return fail(SGLB200_E_INVALID, "silu_mul_quant: group_size %d not in {32,64,128,256}", group_size);
+  }
+#undef SGLB_MASKED
+}
+
 }  // namespace sglb200
 
 using namespace sglb200;
+
+extern "C" int sglb200_silu_and_mul_masked_quant_fp8(const void* input, int dtype, void* output_q, float* output_s,
+                                                     int num_experts, int64_t rows_per_expert, int64_t d,
+                                                     int group_size, float eps, const int32_t* masked_m,
+                                                     void* stream) {
+  SGLB_REQUIRE(num_experts >= 0 && num_experts <= kMaskedMaxExperts && rows_per_expert >= 0 && d > 0 &&
+                   group_size > 0 && d % group_size == 0 && d < (1ll << 30),
+               "silu_mul_masked_quant: bad shape experts=%d (at most %d) rows_per_expert=%lld d=%lld group=%d",
+               num_experts, kMaskedMaxExperts, (long long)rows_per_expert, (long long)d, group_size);
+  if (num_experts == 0 || rows_per_expert == 0) return SGLB200_OK;
+  SGLB_REQUIRE(rows_per_expert * d < (1ll << 40), "silu_mul_masked_quant: expert of %lld x %lld elements too large",
+               (long long)rows_per_expert, (long long)d);
+  SGLB_REQUIRE(input && output_q && output_s && masked_m, "silu_mul_masked_quant: null pointer");
+  SGLB_REQUIRE(aligned16(input) && (reinterpret_cast<uintptr_t>(output_q) & 7u) == 0,
+               "silu_mul_masked_quant: input must be 16-byte and output_q 8-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case 0:
+      return launch_silu_mul_quant_masked<__nv_bfloat16>(input, output_q, output_s, num_experts, rows_per_expert, d,
+                                                         group_size, eps, masked_m, st);
+    case 1:
+      return launch_silu_mul_quant_masked<__half>(input, output_q, output_s, num_experts, rows_per_expert, d,
+                                                  group_size, eps, masked_m, st);
+    default:
+      return fail(SGLB200_E_UNSUPPORTED, "silu_mul_masked_quant: dtype code %d (0 bf16, 1 fp16)", dtype);
+  }
+}
 
 extern "C" int sglb200_per_token_group_quant_fp8(const void* input, int in_dtype, void* output_q, float* output_s,
                                                  int64_t num_tokens, int64_t hidden, int group_size, float eps,

@@ -129,6 +129,26 @@ def silu_and_mul_quant_fp8(
     return q, s
 
 
+def silu_and_mul_masked_quant_fp8_out(x: torch.Tensor, out_q: torch.Tensor, out_s: torch.Tensor, masked_m: torch.Tensor,
+                                      group_size: int = 128, eps: float = 1e-10) -> None:
+    """Masked expert layout: x [E, T_pad, 2d]; rows t < masked_m[e] of expert e are activated and quantised into
+    out_q [E, T_pad, d] / out_s [E, T_pad, d/group] (float32), every other row of the outputs is left untouched."""
+    for t, n in ((x, "input"), (out_q, "output"), (out_s, "output_scale"), (masked_m, "masked_m")):
+        _cuda_contig(t, n)
+    if x.dim() != 3 or x.shape[-1] % 2:
+        raise RuntimeError("silu_and_mul_masked_quant: input must be [experts, padded tokens, 2d]")
+    E, T, d2 = x.shape
+    d = d2 // 2
+    if out_q.dtype != FP8 or tuple(out_q.shape) != (E, T, d):
+        raise RuntimeError("silu_and_mul_masked_quant: output must be float8_e4m3fn [experts, padded tokens, d]")
+    if out_s.dtype != torch.float32 or tuple(out_s.shape) != (E, T, d // group_size):
+        raise RuntimeError("silu_and_mul_masked_quant: output_scale must be float32 [experts, padded tokens, d/group]")
+    if masked_m.dtype != torch.int32 or tuple(masked_m.shape) != (E,):
+        raise RuntimeError("silu_and_mul_masked_quant: masked_m must be int32 [experts]")
+    check(lib.sglb200_silu_and_mul_masked_quant_fp8(x.data_ptr(), _dt(x), out_q.data_ptr(), out_s.data_ptr(), E, T, d,
+                                                    int(group_size), float(eps), masked_m.data_ptr(), _stream(x)))
+
+
 def moe_sum_reduce_out(x: torch.Tensor, out: torch.Tensor, routed_scaling_factor: float) -> None:
     _cuda_contig(x, "input")
     _cuda_contig(out, "output")

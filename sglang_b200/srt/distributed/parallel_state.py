@@ -37,6 +37,10 @@ class GroupCoordinator:
     def all_gather(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
         if self.world_size == 1:
             return x
+        if x.is_cuda and dim % x.dim() == 0:  # rows: one collective straight into the result
+            out = torch.empty((self.world_size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(out, x.contiguous(), group=self.device_group)
+            return out
         parts = [torch.empty_like(x) for _ in range(self.world_size)]
         dist.all_gather(parts, x.contiguous(), group=self.device_group)
         return torch.cat(parts, dim=dim)

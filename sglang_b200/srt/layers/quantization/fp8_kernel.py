@@ -75,7 +75,12 @@ def sglang_per_token_group_quant_fp8(
     assert x.shape[-1] % group_size == 0, "the last dimension of `x` cannot be divisible by `group_size`"
     assert x.is_contiguous(), "`x` is not contiguous"
     if masked_m is not None:
-        raise NotImplementedError("masked (DeepEP low-latency) layout is not on this path")
+        # fp8_kernel.py:329-403: the reference serves this combination only with UE8M0 scales in DeepGEMM's packed
+        # layout (it asserts column_major_scales, scale_tma_aligned and scale_ue8m0), which this library does not
+        # produce.  The masked layout with float32 scales is `silu_and_mul_masked_post_quant_fwd`
+        # (srt/layers/moe/ep_moe/kernels.py), as in the reference.
+        raise NotImplementedError("masked_m goes with UE8M0 scales in the reference's per_token_group_quant_8bit; "
+                                  "for float32 scales call ep_moe.kernels.silu_and_mul_masked_post_quant_fwd")
     if fuse_silu_and_mul:
         if column_major_scales or scale_ue8m0:
             raise NotImplementedError("fused silu_and_mul quantisation writes row-major float32 scales")

@@ -147,6 +147,51 @@ def test_silu_mul_quant_equals_unfused_pipeline(ops, rows, d):
     assert ops.stream_status() == 0
 
 
+@pytest.mark.parametrize("E,T_pad,d,group", [(4, 64, 2048, 128), (32, 128, 768, 128), (3, 40, 256, 64), (1, 5, 128, 128),
+                                             (256, 16, 512, 128), (8, 200, 7168, 128), (1000, 8, 128, 32)])
+def test_silu_mul_masked_quant(ops, E, T_pad, d, group):
+    """`silu_and_mul_masked_post_quant_fwd` (python/sglang/srt/layers/moe/ep_moe/kernels.py:287-420, float32 scales):
+    the first masked_m[e] rows of every expert equal the unfused pair silu_and_mul + quantizer bit for bit, and the
+    quantizer half equals the oracle on the same h; rows at or beyond masked_m[e] keep what the outputs held."""
+    from sglang_b200.srt.layers.moe.ep_moe.kernels import silu_and_mul_masked_post_quant_fwd
+    g = torch.Generator().manual_seed(E * 7 + T_pad)
+    masked_m = torch.randint(0, T_pad + 1, (E,), generator=g, dtype=torch.int32)
+    masked_m[0] = T_pad                      # a full expert
+    if E > 2:
+        masked_m[1], masked_m[E - 1] = 0, 1  # an empty one; a single row in the last
+    x = (make_act(E * T_pad, 2 * d, 5 + E, outliers=False) * 3).cuda().view(E, T_pad, 2 * d)
+    q = torch.full((E, T_pad, d), 0x55, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    s = torch.full((E, T_pad, d // group), -7.0, device="cuda")
+    silu_and_mul_masked_post_quant_fwd(x, q, s, group, masked_m.cuda())
+    h = torch.empty(E * T_pad, d, device="cuda", dtype=torch.bfloat16)
+    ops.silu_and_mul_out(h, x.view(E * T_pad, 2 * d))
+    q_ref, s_ref = ops.per_token_group_quant_fp8(h, group)
+    rq, rs = CO.quant(bf16_bits(h), 0, group)
+    valid = (torch.arange(T_pad)[None, :] < masked_m[:, None]).cuda()          # [E, T_pad]
+    qb, sb = q.view(torch.uint8), s
+    assert torch.equal(qb[valid], q_ref.view(torch.uint8).view(E, T_pad, d)[valid])
+    assert torch.equal(sb[valid], s_ref.view(E, T_pad, -1)[valid])
+    v = valid.cpu().numpy().reshape(-1)
+    assert np.array_equal(fp8_codes(q).reshape(E * T_pad, d)[v], rq[v])
+    assert np.array_equal(s.cpu().numpy().reshape(E * T_pad, -1)[v], rs[v])
+    assert bool((qb[~valid] == 0x55).all()) and bool((sb[~valid] == -7.0).all())
+    assert ops.stream_status() == 0
+
+
+def test_silu_mul_masked_quant_rejects(ops):
+    from sglang_b200.srt.layers.moe.ep_moe.kernels import silu_and_mul_masked_post_quant_fwd
+    x = torch.zeros(2, 4, 256, device="cuda", dtype=torch.bfloat16)
+    q = torch.zeros(2, 4, 128, device="cuda", dtype=torch.float8_e4m3fn)
+    s = torch.zeros(2, 4, 1, device="cuda")
+    m = torch.zeros(2, device="cuda", dtype=torch.int32)
+    with pytest.raises(NotImplementedError):
+        silu_and_mul_masked_post_quant_fwd(x, q, s, 128, m, scale_ue8m0=True)
+    with pytest.raises(RuntimeError):
+        ops.silu_and_mul_masked_quant_fp8_out(x, q, torch.zeros(2, 4, 2, device="cuda"), m, 128)
+    with pytest.raises(RuntimeError):
+        ops.silu_and_mul_masked_quant_fp8_out(x, q, s, torch.zeros(3, device="cuda", dtype=torch.int32), 128)
+
+
 @pytest.mark.parametrize("tokens,topk,hidden", [(1, 8, 7168), (33, 8, 2048), (512, 6, 1024), (5, 1, 128)])
 def test_moe_sum_reduce_bit_exact(ops, tokens, topk, hidden):
     x = make_act(tokens * topk, hidden, 99 + tokens, outliers=False).view(tokens, topk, hidden).cuda()

@@ -124,7 +124,9 @@ def test_grouped_bitwise_equal_to_reference_kernel(ref_grouped, E, R, N, K):
     ptrs = [torch.empty(E, **i64) for _ in range(5)]
     ab, cs = torch.full((E,), K, **i64), torch.full((E,), N, **i64)
     lay_a, lay_b = (torch.empty(E, 5, dtype=torch.int32, device=dev) for _ in range(2))
-    work = torch.empty(90000, device=dev, dtype=torch.uint8)
+    # (the reference's 90 000 bytes, fp8.py:1196, fit the CUTLASS it pins; the CUTLASS this comparator is built with
+    # keeps about 0.3 MB of tensor-map copies per grouped launch and does not check the size it is given)
+    work = torch.empty(4 << 20, device=dev, dtype=torch.uint8)
     out_ref = torch.zeros(R, N, device=dev, dtype=torch.bfloat16)
     out = torch.zeros(R, N, device=dev, dtype=torch.bfloat16)
     args = (*ptrs, aq, wq.transpose(1, 2), a_s, ws.transpose(1, 2), ab, ab, cs, lay_a, lay_b, ps, offs[:-1].contiguous(), work)
@@ -135,3 +137,71 @@ def test_grouped_bitwise_equal_to_reference_kernel(ref_grouped, E, R, N, K):
     assert torch.allclose(out.float(), out_ref.float(), rtol=2 ** -7, atol=2e-3)
     differ = (out.view(torch.int16) != out_ref.view(torch.int16)).float().mean().item()
     assert differ == 0.0, f"{differ:.2e} of the outputs differ in their bf16 bits"
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# the reference's CUDA quantizer and moe_align kernel
+# ------------------------------------------------------------------------------------------------------------------
+LIB_AUX = os.path.join(os.path.dirname(LIB), "libsgl_gpu_ref_aux.so")
+
+
+@pytest.fixture(scope="module")
+def ref_aux():
+    """sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu and sgl-kernel/csrc/moe/moe_align_kernel.cu compiled
+    unmodified (oracle/Makefile, target `ref_gpu_aux`; without the reference build's fast-math flag, so its
+    `val / y_s` is an IEEE division like the torch-native form the oracle restates)."""
+    if not os.path.exists(LIB_AUX):
+        pytest.skip("oracle/_ref/libsgl_gpu_ref_aux.so not built (make -C oracle ref_gpu_aux)")
+    torch.ops.load_library(LIB_AUX)
+    return torch.ops.sgl_gpu_ref
+
+
+@pytest.mark.parametrize("tokens,hidden,dtype", [(83, 7168, torch.bfloat16), (2048, 4096, torch.bfloat16),
+                                                 (7, 512, torch.float16), (300, 2048, torch.float32),
+                                                 (4096, 7168, torch.bfloat16)])
+def test_quantizer_bitwise_equal_to_reference_kernel(ref_aux, tokens, hidden, dtype):
+    """The division form (`y_s = absmax / 448`, `q = clamp(x / y_s)`, per_token_group_quant_8bit.cu:86-111): codes and
+    scales must agree bit for bit."""
+    from sglang_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(tokens + hidden)
+    x = torch.randn(tokens, hidden, device="cuda", generator=g)
+    x[torch.rand(tokens, hidden, device="cuda", generator=g) < 0.001] *= 30
+    x[0, :128] = 0                                   # a group below eps
+    x = x.to(dtype)
+    q_ref = torch.empty(tokens, hidden, device="cuda", dtype=torch.float8_e4m3fn)
+    s_ref = torch.empty(tokens, hidden // 128, device="cuda", dtype=torch.float32)
+    ref_aux.sgl_per_token_group_quant_8bit(x, q_ref, s_ref, 128, 1e-10, -448.0, 448.0, False)
+    q, s = ops.per_token_group_quant_fp8(x, 128)
+    torch.cuda.synchronize()
+    assert torch.equal(s, s_ref)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("T,topk,E,filtered", [(1, 8, 256, False), (64, 8, 256, False), (4096, 8, 256, False),
+                                                (16384, 8, 128, False), (300, 2, 8, True), (4096, 8, 32, True)])
+def test_moe_align_agrees_with_reference_kernel(ref_aux, T, topk, E, filtered):
+    """Same padded total, same expert of every block, and the same set of flat indices in every expert's segment (the
+    reference kernel orders a segment by atomics, this library by ascending flat index)."""
+    from sglang_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(T * 31 + E)
+    ids = torch.randint(0, E, (T, topk), device="cuda", generator=g, dtype=torch.int32)
+    if filtered:
+        ids[torch.rand(T, topk, device="cuda", generator=g) < 0.15] = -1
+    block, numel = 128, T * topk
+    mine_sorted, mine_experts, mine_post = ops.moe_align_block_size(ids, block, E)
+    max_padded = numel + (E + 1) * (block - 1)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    ref_sorted = torch.empty(max_padded, **i32)
+    ref_experts = torch.empty((max_padded + block - 1) // block, **i32)
+    ref_post, cumsum = torch.empty(1, **i32), torch.empty(E + 2, **i32)
+    ref_aux.moe_align_block_size(ids, E + 1, block, ref_sorted, ref_experts, ref_post, cumsum, True)
+    torch.cuda.synchronize()
+    n = int(ref_post.item())
+    assert int(mine_post.item()) == n and n % block == 0
+    assert torch.equal(mine_experts[: n // block], ref_experts[: n // block])
+
+    def keys(sorted_ids, experts):
+        e = experts[: n // block].long().repeat_interleave(block) + 1
+        return torch.sort(e * (numel + 1) + sorted_ids[:n].long()).values
+
+    assert torch.equal(keys(mine_sorted, mine_experts), keys(ref_sorted, ref_experts))
