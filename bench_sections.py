@@ -8,6 +8,10 @@ import torch
 
 SWEEP_M = [1, 16, 64, 256, 1024, 4096, 8192]
 L2_BYTES = 126 * 1024 * 1024
+# Expert-parallel batches of at most this many tokens over all ranks (the same count on every rank) take the gather
+# form (quantise, all-gather the codes, local experts, reduce-scatter: no host synchronisation); larger ones the
+# all-to-all form, whose fixed host-side cost (about a millisecond of split-size exchange and index kernels) they amortise.
+GATHER_BELOW = 16384
 
 
 def _barrier(world):
@@ -97,6 +101,17 @@ def gemm_sweep(args, ctx, peaks):
     rank, world, dev = ctx
     gen = torch.Generator(device=dev).manual_seed(7)
     out = {}
+    # the reference's own CUDA kernel, where its comparator library is built (one GPU only): timed right after this
+    # library's kernel, same inputs, same graph-replay protocol, same clocks
+    import os
+    ref_mm = None
+    ref_lib = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libsgl_gpu_ref.so")
+    if world == 1 and os.path.exists(ref_lib):
+        try:
+            torch.ops.load_library(ref_lib)
+            ref_mm = torch.ops.sgl_gpu_ref.fp8_blockwise_scaled_mm
+        except Exception:  # noqa: BLE001  (the comparator is optional)
+            ref_mm = None
     for name, N, K in DSV3_LAYERS:
         wq, ws = make_block_fp8_weight(N, K, dev, gen)
         # rotate over enough copies of the weight that successive launches cannot hit L2
@@ -128,6 +143,28 @@ def gemm_sweep(args, ctx, peaks):
             flops = 2.0 * M * N * K
             nbytes = M * K + N * K + 2 * M * N + 4 * M * (K // 128) + 4 * ((N + 127) // 128) * (K // 128)
             res[str(M)] = {"us": ms * 1e3, "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6}
+            if ref_mm is not None and N % 128 == 0 and M >= 256:  # (it wants whole 128-column blocks)
+                xs_m = xs.t().contiguous().t()  # M-major activation scales, as the reference kernel wants them
+                ws_t = ws.t()
+
+                def run_ref():
+                    w = wqs[state["i"] % copies]
+                    state["i"] += 1
+                    ref_mm(xq, w.t(), xs_m, ws_t, torch.bfloat16)
+
+                try:
+                    for _ in range(3):
+                        run_ref()
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        for _ in range(iters):
+                            run_ref()
+                    ms_ref = _time(graph.replay, 3, 1, world, dev) / iters
+                    del graph
+                    res[str(M)].update({"ref_us": ms_ref * 1e3, "ref_tflops": flops / ms_ref / 1e9})
+                except Exception:  # noqa: BLE001
+                    ref_mm = None
         out[name] = res
         del wqs, wq
         torch.cuda.empty_cache()
@@ -135,7 +172,10 @@ def gemm_sweep(args, ctx, peaks):
                            "consecutive launches exceed the 126 MB L2", "layers": out,
                            "hbm_peak_gbs": peaks["hbm_gbs"],
                            "fp8_peak_tflops": peaks.get("fp8_measured", 2 * peaks["bf16"]),
-                           "fp8_peak_source": "the same denominator as roofline.peak of this line"}}
+                           "fp8_peak_source": "the same denominator as roofline.peak of this line",
+                           "ref": "ref_us / ref_tflops: the reference's own CUDA kernel (sgl-kernel fp8_blockwise_scaled_mm, "
+                                  "compiled unmodified into oracle/_ref) timed right after this library's kernel on the same "
+                                  "inputs with the same protocol; absent where that library is not built"}}
 
 
 def config0_gpu(args, ctx, peaks):
@@ -311,7 +351,7 @@ def moe_layer(args, ctx, peaks):
         initialize_model_parallel(1, ep)
         gen = torch.Generator(device=dev).manual_seed(23 + rank)
         # (every rank holds the same number of tokens here, so decode-sized batches may take the gather form)
-        moe = FusedMoE(E, H, I, topk, quant_config=cfg, a2a_backend="nccl", device=dev, equal_tokens_gather_below=2048)
+        moe = FusedMoE(E, H, I, topk, quant_config=cfg, a2a_backend="nccl", device=dev, equal_tokens_gather_below=GATHER_BELOW)
         _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
         _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
         # the shared expert is a dense block-FP8 MLP replicated on every rank (models/deepseek_v2.py:826-882)
@@ -346,7 +386,7 @@ def moe_layer(args, ctx, peaks):
 
     # sizes that take the gather form at this rank count have no host synchronisation: they are replayed from CUDA
     # graphs as well, alone and expert-parallel (graph against graph)
-    graphed = [T for T in sizes if T <= 512 and (world == 1 or T * world <= 2048)]
+    graphed = [T for T in sizes if T <= 512 and (world == 1 or T * world <= GATHER_BELOW)]
     if world > 1:
         layer_for = build(1)
         for T in sizes:
@@ -379,7 +419,7 @@ def moe_layer(args, ctx, peaks):
     out = {"config": "BASELINE config 3: DeepSeek-V3 MoE, 256 routed experts + 1 shared, hidden 7168, "
                      "moe_intermediate 2048, top-8 grouped sigmoid routing (8 groups, top-4), "
                      "tokens per GPU as keyed; expert-parallel with NCCL all-to-all dispatch/combine (batches of at "
-                     "most 2048 tokens over all ranks: all-gather, local experts, reduce-scatter); ms_1gpu_eager = "
+                     f"most {GATHER_BELOW} tokens over all ranks: quantise, all-gather, local experts, reduce-scatter); ms_1gpu_eager = "
                      "the layer with all experts on one GPU of this box in this run",
            "ep": world, "scaling": "weak", "results": res}
     if reduced:
@@ -525,7 +565,7 @@ def moe_layer_skewed(args, ctx, peaks):
         initialize_model_parallel(1, ep)
         gen = torch.Generator(device=dev).manual_seed(41 + rank)
         moe = FusedMoE(E, H, I, topk, quant_config=Fp8Config(), a2a_backend="nccl", device=dev,
-                       equal_tokens_gather_below=2048, expert_location=location)
+                       equal_tokens_gather_below=GATHER_BELOW, expert_location=location)
         _fill_weight(moe.w13_weight.data, moe.w13_weight_scale_inv.data, gen)
         _fill_weight(moe.w2_weight.data, moe.w2_weight_scale_inv.data, gen)
         return moe
@@ -534,7 +574,7 @@ def moe_layer_skewed(args, ctx, peaks):
     gen_in = torch.Generator(device=dev).manual_seed(4100 + rank)
     for T in sizes:
         batches[T] = routing(T, gen_in)
-    graphed = [T for T in sizes if T <= 1024 and (world == 1 or T * world <= 2048)]  # (as in the config-3 section)
+    graphed = [T for T in sizes if T <= 1024 and (world == 1 or T * world <= GATHER_BELOW)]  # (as in the config-3 section)
     if world > 1:
         moe = build(1)
         for T in sizes:

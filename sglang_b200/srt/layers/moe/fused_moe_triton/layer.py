@@ -152,10 +152,22 @@ class FusedMoE(nn.Module):
         return out
 
     def _forward_gathered(self, hidden_states: torch.Tensor, topk_output: StandardTopKOutput) -> torch.Tensor:
+        """Every rank quantises its own tokens once and the codes travel (half the bytes of the bf16 rows, as in the
+        quantise-before-send of deepep.py:377-390); the local experts take the gathered (codes, scales) as they are."""
+        from ..... import ops as _ops
+        from .fused_moe import fused_experts_impl
+
         g = get_moe_ep_group()
-        x_all = g.all_gather(hidden_states, dim=0)
-        w_all = g.all_gather(topk_output[0], dim=0)
-        ids_all = g.all_gather(topk_output[1], dim=0)
-        dispatch_output = self.dispatcher.dispatch(x_all, StandardTopKOutput(w_all, ids_all, None))
-        out_all = self.dispatcher.combine(self.quant_method.apply(self, dispatch_output))
+        xq, xs = _ops.per_token_group_quant_fp8(hidden_states, self.quant_config.weight_block_size[1])
+        q_all = g.all_gather(xq.view(torch.uint8), dim=0).view(torch.float8_e4m3fn)
+        s_all = g.all_gather(xs, dim=0)
+        w_all = g.all_gather(topk_output[0].float(), dim=0)
+        ids_all = g.all_gather(topk_output[1].to(torch.int32), dim=0)
+        local = self.dispatcher.dispatch(q_all, StandardTopKOutput(w_all, ids_all, None)).topk_output
+        cfg = self.moe_runner_config
+        out_all = fused_experts_impl(
+            q_all, self.w13_weight, self.w2_weight, local.topk_weights, local.topk_ids, inplace=False,
+            use_fp8_w8a8=True, w1_scale=self.w13_weight_scale_inv, w2_scale=self.w2_weight_scale_inv,
+            block_shape=self.quant_config.weight_block_size, routed_scaling_factor=cfg.routed_scaling_factor,
+            a1_scale=s_all, out_dtype=hidden_states.dtype, has_filtered_ids=True)
         return g.reduce_scatter(out_all)
