@@ -271,7 +271,8 @@ int sglb200_fp8_blockwise_scaled_mm(const void* A, const void* B, const float* a
  *   (python/sglang/srt/layers/moe/fused_moe_triton/fused_moe_triton_kernels.py:307-583, 586-790) and
  *   torch.ops.sgl_kernel.fp8_blockwise_scaled_grouped_mm (sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:650-810).
  * A [max_rows, K] e4m3 (rows already in sorted order), a_s [max_rows, K/128] row-major,
- * B [E, N, K] e4m3, b_s [E, ceil(N/128), ceil(K/128)], block size of the sort must be 128.
+ * B [E, N, K] e4m3, b_s [E, ceil(N/128), ceil(K/128)], block size of the sort must be 128.  K % 16 == 0, K <= 65536,
+ * N % 8 == 0.
  */
 int sglb200_fp8_blockwise_grouped_mm(const void* A, const float* a_s, const void* B, const float* b_s, void* C,
                                      const int32_t* sorted_token_ids, const int32_t* expert_ids,
