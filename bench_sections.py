@@ -73,6 +73,14 @@ def _time_graph(fn, iters, warmup, dev, world=1):
     return ms
 
 
+def _time_graph_alone(fn, iters, warmup, world, dev):
+    """`_time_graph` of a call without collectives, timed by every rank for itself: the slowest rank's time, or None
+    if some rank could not capture."""
+    ms = _time_graph(fn, iters, warmup, dev)
+    worst = _max_ms(ms if ms is not None else float("inf"), world, dev)
+    return None if worst == float("inf") else worst
+
+
 def _fill_weight(dst_q, dst_s, gen, std=0.02, chunk=8):
     """Random N(0,std) weights quantised per 128x128 block, written expert-chunk by expert-chunk."""
     from bench import make_block_fp8_weight
@@ -277,14 +285,15 @@ def tp_layer(args, ctx, peaks):
             r = res[str(M)]
             r["ms"] = r["ms_eager"]
             if M <= 128:
-                r["ms"] = _time_graph(layer_for(M), 20, 3, dev)
-                r["launch"] = "cuda graph"
+                g_ms = _time_graph(layer_for(M), 20, 3, dev)
+                if g_ms is not None:
+                    r["ms"], r["launch"] = g_ms, "cuda graph"
     else:
         small = [M for M in sizes if M <= 128]  # launch-bound: also replayed from CUDA graphs, alone and sharded
         layer_for = build(1)  # the whole layer on this GPU alone: no collective, every rank times its own copy
         time_all(layer_for, "ms_1gpu_eager", world)
         for M in small:
-            res[str(M)]["ms_1gpu_graph"] = _max_ms(_time_graph(layer_for(M), 20, 3, dev), world, dev)
+            res[str(M)]["ms_1gpu_graph"] = _time_graph_alone(layer_for(M), 20, 3, world, dev)
         del layer_for
         torch.cuda.empty_cache()
         layer_for = build(world)
@@ -301,7 +310,7 @@ def tp_layer(args, ctx, peaks):
             r["ms"] = r["ms_fused"] if r["fused_all_reduce"] else r["ms_nccl"]
             r["ms_eager"] = r["ms"]
             r["efficiency_vs_1gpu"] = r["ms_1gpu_eager"] / (world * r["ms"])
-            if M in small and r.get("ms_nccl_graph") and not r["fused_all_reduce"]:
+            if M in small and r.get("ms_nccl_graph") and r.get("ms_1gpu_graph") and not r["fused_all_reduce"]:
                 # graph against graph: what a decode batch costs when both arms are served from CUDA graphs
                 r["launch"] = "cuda graph"
                 r["ms"] = r["ms_nccl_graph"]
@@ -392,7 +401,7 @@ def moe_layer(args, ctx, peaks):
         for T in sizes:
             res[str(T)]["ms_1gpu_eager"] = _time(layer_for(T), 10, 3, world, dev)
             if T in graphed:
-                res[str(T)]["ms_1gpu_graph"] = _max_ms(_time_graph(layer_for(T), 10, 3, dev), world, dev)
+                res[str(T)]["ms_1gpu_graph"] = _time_graph_alone(layer_for(T), 10, 3, world, dev)
         del layer_for
         torch.cuda.empty_cache()
     layer_for = build(world)
@@ -408,7 +417,7 @@ def moe_layer(args, ctx, peaks):
             if g_ms is not None:
                 r["launch"] = "cuda graph"
                 r["ms"] = g_ms
-                if world > 1:
+                if world > 1 and r.get("ms_1gpu_graph"):
                     r["efficiency_vs_1gpu"] = r["ms_1gpu_graph"] / g_ms
         flops = 6.0 * T * topk * H * I + 6.0 * T * H * I
         r.update({"tokens_per_s": world * T / r["ms"] * 1e3, "tflops_per_gpu": flops / r["ms"] / 1e9})
@@ -581,7 +590,7 @@ def moe_layer_skewed(args, ctx, peaks):
             x, top, _ = batches[T]
             res[str(T)]["ms_1gpu_eager"] = _time(lambda: moe(x, top), 10, 3, world, dev)
             if T in graphed:
-                res[str(T)]["ms_1gpu_graph"] = _max_ms(_time_graph(lambda: moe(x, top), 10, 3, dev), world, dev)
+                res[str(T)]["ms_1gpu_graph"] = _time_graph_alone(lambda: moe(x, top), 10, 3, world, dev)
         del moe
         torch.cuda.empty_cache()
     moe = build(world)
@@ -598,7 +607,7 @@ def moe_layer_skewed(args, ctx, peaks):
             if g_ms is not None:
                 r["launch"] = "cuda graph"
                 r["ms"] = g_ms
-                if world > 1:
+                if world > 1 and r.get("ms_1gpu_graph"):
                     r["efficiency_vs_1gpu"] = r["ms_1gpu_graph"] / g_ms
         # this rank alone, without the barrier-and-max: the gap to `ms` at EP > 1 is the wait for the busiest rank
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

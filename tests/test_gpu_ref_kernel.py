@@ -38,8 +38,7 @@ def _inputs(M, N, K, seed):
     return xq, xs, wq, ws.contiguous()
 
 
-# (from 512 rows on and beyond 12 K slabs, pairs of CTAs share 256-row tiles: 700 rows leave the last pair's second
-# CTA a partial block of rows, 520 rows leave it none)
+# (700 and 520 rows end in a partial 128-row block, of 60 and 8 rows; 130 and 513 rows in one of 2 and 1)
 @pytest.mark.parametrize("M,N,K", [(4096, 7168, 2048), (2048, 4608, 7168), (513, 1536, 1536), (130, 24576, 1536),
                                    (1024, 7168, 18432), (4, 512, 512), (128, 256, 128), (700, 1536, 2048),
                                    (520, 768, 2048), (8192, 1280, 3584)])
